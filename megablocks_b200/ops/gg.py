@@ -1,0 +1,256 @@
+"""Grouped GEMM: one matrix product per expert over a ragged batch of rows.
+
+This takes the place of the external ``grouped_gemm`` package the reference
+calls (call sites: megablocks/layers/mlp.py:414-523, glu.py:84-205).  Groups
+are described by ``bins``: an int32 device tensor holding the inclusive prefix
+sum of rows per expert, so no row count ever has to be copied to the host.
+
+Layouts (``n`` rows in total, ``E`` groups):
+
+=========  ======================  =========================  ============
+trans_a    a                       b                          result
+=========  ======================  =========================  ============
+False      ``[n, K]``              ``[E, K, N]`` (NN) or      ``[n, N]``
+                                   ``[E, N, K]`` (trans_b)
+True       ``[n, M]``              ``[n, N]``                 ``[E, M, N]``
+=========  ======================  =========================  ============
+
+With ``trans_a`` the contraction runs over each group's rows (ragged K); a
+group without rows yields a zero matrix.  On CUDA all of these run the
+tcgen05/TMEM kernel of ``csrc/grouped_gemm.cu``, optionally with a fused
+epilogue (activation, activation backward, GLU product, GLU backward).  On
+CPU they run per-group ``torch.matmul`` in fp32, which is also the oracle.
+"""
+
+from functools import partial
+from typing import Any, Callable, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from megablocks_b200._ext import ext
+
+# Epilogue kinds understood by the kernel.
+EPI_NONE = 0      # c = acc
+EPI_ACT = 1       # c = acc, out2 = act(acc)
+EPI_DACT = 2      # c = acc * act'(aux1), out2 = act(aux1)
+EPI_GLU = 3       # c = acc, out2 = act(aux1) * acc
+EPI_DGLU = 4      # c = acc * aux2 * act'(aux1), out2 = acc * act(aux1), out3 = act(aux1) * aux2
+EPI_ADD = 5       # c = acc + aux1
+
+ACT_IDENTITY = 0
+ACT_GELU_TANH = 1
+ACT_SILU = 2
+ACT_RELU = 3
+ACT_GELU_ERF = 4
+
+_ACT_NAMES = {
+    'identity': ACT_IDENTITY,
+    'gelu_tanh': ACT_GELU_TANH,
+    'silu': ACT_SILU,
+    'relu': ACT_RELU,
+    'gelu': ACT_GELU_ERF,
+}
+
+
+def activation_id(fn: Optional[Callable]) -> Optional[int]:
+    """Kernel id of a known activation callable; ``None`` for anything else."""
+    if fn is None:
+        return ACT_IDENTITY
+    if isinstance(fn, str):
+        return _ACT_NAMES.get(fn)
+    if isinstance(fn, partial):
+        if fn.func is F.gelu and not fn.args:
+            approx = fn.keywords.get('approximate', 'none')
+            if set(fn.keywords) <= {'approximate'}:
+                return ACT_GELU_TANH if approx == 'tanh' else ACT_GELU_ERF
+        return None
+    if fn is F.gelu:
+        return ACT_GELU_ERF
+    if fn is F.silu:
+        return ACT_SILU
+    if fn is F.relu or fn is torch.relu:
+        return ACT_RELU
+    if isinstance(fn, torch.nn.GELU):
+        return ACT_GELU_TANH if fn.approximate == 'tanh' else ACT_GELU_ERF
+    if isinstance(fn, torch.nn.SiLU):
+        return ACT_SILU
+    if isinstance(fn, torch.nn.ReLU):
+        return ACT_RELU
+    return None
+
+
+def act_forward(z: torch.Tensor, act: int) -> torch.Tensor:
+    if act == ACT_IDENTITY:
+        return z
+    if act == ACT_GELU_TANH:
+        return F.gelu(z, approximate='tanh')
+    if act == ACT_SILU:
+        return F.silu(z)
+    if act == ACT_RELU:
+        return F.relu(z)
+    if act == ACT_GELU_ERF:
+        return F.gelu(z)
+    raise ValueError(f'unknown activation id {act}')
+
+
+def act_derivative(z: torch.Tensor, act: int) -> torch.Tensor:
+    """d act(z) / dz evaluated in the dtype of ``z`` (callers pass fp32)."""
+    if act == ACT_IDENTITY:
+        return torch.ones_like(z)
+    if act == ACT_GELU_TANH:
+        c = 0.7978845608028654
+        inner = c * (z + 0.044715 * z * z * z)
+        t = torch.tanh(inner)
+        return 0.5 * (1 + t) + 0.5 * z * (1 - t * t) * c * (1 + 3 * 0.044715 * z * z)
+    if act == ACT_SILU:
+        s = torch.sigmoid(z)
+        return s * (1 + z * (1 - s))
+    if act == ACT_RELU:
+        return (z > 0).to(z.dtype)
+    if act == ACT_GELU_ERF:
+        cdf = 0.5 * (1 + torch.erf(z * 0.7071067811865476))
+        pdf = torch.exp(-0.5 * z * z) * 0.3989422804014327
+        return cdf + z * pdf
+    raise ValueError(f'unknown activation id {act}')
+
+
+def bins_from_batch_sizes(batch_sizes: torch.Tensor, device) -> torch.Tensor:
+    """Inclusive prefix sum (int32, on ``device``) of a per-group row count tensor."""
+    return torch.cumsum(batch_sizes.to(torch.int64), dim=0).to(dtype=torch.int32).to(device, non_blocking=True)
+
+
+# ----------------------------------------------------------------------------
+# CPU implementation (oracle).
+# ----------------------------------------------------------------------------
+def _bounds(bins: torch.Tensor):
+    ends = [int(v) for v in bins.tolist()]
+    starts = [0] + ends[:-1]
+    return list(zip(starts, ends))
+
+
+def _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups):
+    if trans_a:
+        out = torch.zeros(num_groups, a.shape[1], b.shape[1], dtype=torch.float32)
+        for e, (s, t) in enumerate(_bounds(bins)):
+            if t > s:
+                out[e] = a[s:t].float().t() @ b[s:t].float()
+        return out
+    n_out = b.shape[1] if trans_b else b.shape[2]
+    out = torch.zeros(a.shape[0], n_out, dtype=torch.float32)
+    for e, (s, t) in enumerate(_bounds(bins)):
+        if t > s:
+            w = b[e].float()
+            out[s:t] = a[s:t].float() @ (w.t() if trans_b else w)
+    return out
+
+
+def _cpu_epilogue(acc, epilogue, act, aux1, aux2, dtype):
+    if epilogue == EPI_NONE:
+        return acc.to(dtype), None, None
+    if epilogue == EPI_ACT:
+        c = acc.to(dtype)
+        return c, act_forward(c.float(), act).to(dtype), None
+    if epilogue == EPI_DACT:
+        z = aux1.float()
+        return (acc * act_derivative(z, act)).to(dtype), act_forward(z, act).to(dtype), None
+    if epilogue == EPI_GLU:
+        c = acc.to(dtype)
+        return c, (act_forward(aux1.float(), act) * c.float()).to(dtype), None
+    if epilogue == EPI_DGLU:
+        z1, z2 = aux1.float(), aux2.float()
+        a1 = act_forward(z1, act)
+        return ((acc * z2 * act_derivative(z1, act)).to(dtype), (acc * a1).to(dtype), (a1 * z2).to(dtype))
+    if epilogue == EPI_ADD:
+        return (acc + aux1.float()).to(dtype), None, None
+    raise ValueError(f'unknown epilogue {epilogue}')
+
+
+# ----------------------------------------------------------------------------
+# Raw (non-autograd) entry point.
+# ----------------------------------------------------------------------------
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_a: bool = False,
+                 trans_b: bool = False, epilogue: int = EPI_NONE, act: int = ACT_IDENTITY,
+                 aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
+                 want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
+                 c: Optional[torch.Tensor] = None):
+    """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
+
+    ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
+    allocates an upper bound); rows past ``bins[-1]`` are written as zero.
+    ``c`` optionally supplies the output buffer of the main result.
+    """
+    if num_groups is None:
+        num_groups = bins.numel()
+    if a.is_cuda:
+        return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
+                                  bool(want_out2), bool(want_out3), int(num_groups), c)
+    acc = _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups)
+    out, out2, out3 = _cpu_epilogue(acc, epilogue, act, aux1, aux2, a.dtype)
+    if not trans_a:
+        # Rows past the last bin belong to no group: defined as zero.
+        last = int(bins[-1])
+        for t in (out, out2, out3):
+            if t is not None and last < t.shape[0]:
+                t[last:] = 0
+    if c is not None:
+        c.copy_(out)
+        out = c
+    return out, (out2 if want_out2 else None), (out3 if want_out3 else None)
+
+
+# ----------------------------------------------------------------------------
+# Autograd-aware gmm with the call signature of the grouped_gemm package.
+# ----------------------------------------------------------------------------
+class _GroupedGemm(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, a, b, bins, trans_b):
+        ctx.save_for_backward(a, b, bins)
+        ctx.trans_b = trans_b
+        out, _, _ = grouped_gemm(a.contiguous(), b.contiguous(), bins, trans_b=trans_b)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, grad):
+        a, b, bins = ctx.saved_tensors
+        grad = grad.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da, _, _ = grouped_gemm(grad, b, bins, trans_b=not ctx.trans_b)
+        if ctx.needs_input_grad[1]:
+            if ctx.trans_b:   # b is [E, N, K]: db_e = grad_e^T @ a_e
+                db, _, _ = grouped_gemm(grad, a, bins, trans_a=True, num_groups=b.shape[0])
+            else:             # b is [E, K, N]: db_e = a_e^T @ grad_e
+                db, _, _ = grouped_gemm(a, grad, bins, trans_a=True, num_groups=b.shape[0])
+            db = db.to(b.dtype)
+        return da, db, None, None
+
+
+def gmm(a: torch.Tensor, b: torch.Tensor, batch_sizes: torch.Tensor, trans_b: bool = False) -> torch.Tensor:
+    """``grouped_gemm.ops.gmm`` replacement.
+
+    ``batch_sizes`` holds rows per group (any integer dtype, host or device);
+    pass a device tensor to stay free of host synchronisation.
+    """
+    bins = bins_from_batch_sizes(batch_sizes, a.device)
+    return _GroupedGemm.apply(a, b, bins, trans_b)
+
+
+def gmm_bins(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, trans_b: bool = False) -> torch.Tensor:
+    """Like :func:`gmm` but takes the inclusive prefix sum directly."""
+    return _GroupedGemm.apply(a, b, bins, trans_b)
+
+
+class _Backend:
+    """Mirror of ``grouped_gemm.backend``: raw, non-differentiable ``gmm``."""
+
+    @staticmethod
+    def gmm(a, b, batch_sizes, trans_a=False, trans_b=False, c=None):
+        bins = bins_from_batch_sizes(batch_sizes, a.device)
+        out, _, _ = grouped_gemm(a, b, bins, trans_a=trans_a, trans_b=trans_b, c=c,
+                                 num_groups=batch_sizes.numel())
+        return out
+
+
+backend = _Backend()

@@ -1,0 +1,138 @@
+"""Grouped GEMM (all layouts and fused epilogues) against per-group fp32 matmuls."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+from conftest import DEVICES
+
+from megablocks_b200.ops import gg as G
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=1e-4, atol=1e-4)
+
+
+def _dtype_for(device):
+    return torch.bfloat16 if device == 'cuda' else torch.float32
+
+
+def _sizes(z, m, device, zipf=False):
+    if zipf:
+        p = 1.0 / torch.arange(1, z + 1).float()**1.1
+        idx = torch.multinomial(p / p.sum(), m, replacement=True)
+    else:
+        idx = torch.randint(0, z, (m,))
+    counts = torch.bincount(idx, minlength=z)
+    return counts, torch.cumsum(counts, 0).int().to(device)
+
+
+def _ref_gmm(a, b, counts, trans_b):
+    out, start = [], 0
+    for e, c in enumerate(counts.tolist()):
+        w = b[e].float()
+        out.append(a[start:start + c].float() @ (w.t() if trans_b else w))
+        start += c
+    return torch.cat(out)
+
+
+SHAPES = [(1, 128, 128, 128), (8, 1024, 256, 512), (4, 777, 192, 320), (16, 4096, 768, 3072), (64, 8192, 768, 3072),
+          (3, 100, 64, 64)]
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('z,m,k,n', SHAPES)
+@pytest.mark.parametrize('trans_b', [False, True])
+def test_gmm_forward_backward(device, z, m, k, n, trans_b):
+    if device == 'cpu' and m * k * n > 2**31:
+        pytest.skip('large case is GPU-only')
+    dtype = _dtype_for(device)
+    counts, bins = _sizes(z, m, device, zipf=(z == 16))
+    a = (torch.randn(m, k) * 0.5).to(dtype).to(device).requires_grad_(True)
+    b = (torch.randn(z, n, k) if trans_b else torch.randn(z, k, n)).mul(0.1).to(dtype).to(device).requires_grad_(True)
+    out = G.gmm_bins(a, b, bins, trans_b)
+    a2 = a.detach().cpu().float().requires_grad_(True)
+    b2 = b.detach().cpu().float().requires_grad_(True)
+    ref = _ref_gmm(a2, b2, counts, trans_b)
+    torch.testing.assert_close(out.detach().cpu().float(), ref.detach(), **_tol(dtype))
+    probe = torch.randn(m, n)
+    (out.float() * probe.to(device)).sum().backward()
+    (ref * probe).sum().backward()
+    torch.testing.assert_close(a.grad.cpu().float(), a2.grad, **_tol(dtype))
+    gtol = dict(rtol=3e-2, atol=3e-1) if dtype != torch.float32 else _tol(dtype)
+    torch.testing.assert_close(b.grad.cpu().float(), b2.grad, **gtol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+def test_gmm_batch_sizes_signature(device):
+    dtype = _dtype_for(device)
+    counts = torch.tensor([3, 0, 5, 120])
+    a = torch.randn(128, 64).to(dtype).to(device)
+    b = torch.randn(4, 64, 128).mul(0.1).to(dtype).to(device)
+    out = G.gmm(a, b, counts)
+    torch.testing.assert_close(out.cpu().float(), _ref_gmm(a.cpu(), b.cpu(), counts, False), **_tol(dtype))
+    raw = G.backend.gmm(a, b, counts)
+    assert torch.equal(raw, out)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('act', [G.ACT_GELU_TANH, G.ACT_SILU, G.ACT_RELU, G.ACT_GELU_ERF, G.ACT_IDENTITY])
+def test_epilogues(device, act):
+    dtype = _dtype_for(device)
+    z, m, k, n = 4, 600, 128, 256
+    counts, bins = _sizes(z, m, device)
+    a = torch.randn(m, k).mul(0.5).to(dtype).to(device)
+    w = torch.randn(z, n, k).mul(0.2).to(dtype).to(device)
+    acc = _ref_gmm(a.cpu(), w.cpu(), counts, True)
+    tol = _tol(dtype)
+
+    c, h, _ = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_ACT, act=act)
+    torch.testing.assert_close(c.cpu().float(), acc, **tol)
+    torch.testing.assert_close(h.cpu().float(), G.act_forward(c.cpu().float(), act), **tol)
+
+    z1 = torch.randn(m, n).to(dtype).to(device)
+    z2 = torch.randn(m, n).to(dtype).to(device)
+    z1f, z2f = z1.cpu().float(), z2.cpu().float()
+    zz = z1f.clone().requires_grad_(True)
+    G.act_forward(zz, act).sum().backward()
+    dact = zz.grad
+
+    c, h, _ = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_DACT, act=act, aux1=z1)
+    torch.testing.assert_close(c.cpu().float(), acc * dact, **tol)
+    torch.testing.assert_close(h.cpu().float(), G.act_forward(z1f, act), **tol)
+
+    c, h, _ = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=z1)
+    torch.testing.assert_close(c.cpu().float(), acc, **tol)
+    torch.testing.assert_close(h.cpu().float(), G.act_forward(z1f, act) * c.cpu().float(), **tol)
+
+    c, d2, h = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_DGLU, act=act, aux1=z1, aux2=z2)
+    torch.testing.assert_close(c.cpu().float(), acc * z2f * dact, **tol)
+    torch.testing.assert_close(d2.cpu().float(), acc * G.act_forward(z1f, act), **tol)
+    torch.testing.assert_close(h.cpu().float(), G.act_forward(z1f, act) * z2f, **tol)
+
+    c, _, _ = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_ADD, aux1=z1)
+    torch.testing.assert_close(c.cpu().float(), acc + z1f, **tol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+def test_rows_past_last_bin_are_zero(device):
+    dtype = _dtype_for(device)
+    a = torch.randn(512, 128).to(dtype).to(device)
+    w = torch.randn(2, 128, 128).mul(0.1).to(dtype).to(device)
+    bins = torch.tensor([128, 256], dtype=torch.int32, device=device)
+    out, _, _ = G.grouped_gemm(a, w, bins)
+    assert not out[256:].any()
+    ref = _ref_gmm(a.cpu()[:256], w.cpu(), torch.tensor([128, 128]), False)
+    torch.testing.assert_close(out[:256].cpu().float(), ref, **_tol(dtype))
+
+
+def test_activation_id():
+    from functools import partial
+    assert G.activation_id(partial(F.gelu, approximate='tanh')) == G.ACT_GELU_TANH
+    assert G.activation_id(F.gelu) == G.ACT_GELU_ERF
+    assert G.activation_id(F.silu) == G.ACT_SILU
+    assert G.activation_id(torch.nn.ReLU()) == G.ACT_RELU
+    assert G.activation_id(lambda t: t * 2) is None
+    for act in (G.ACT_GELU_TANH, G.ACT_SILU, G.ACT_GELU_ERF):
+        zz = torch.randn(1000, dtype=torch.float64, requires_grad=True)
+        G.act_forward(zz, act).sum().backward()
+        torch.testing.assert_close(G.act_derivative(zz.detach(), act), zz.grad, rtol=1e-6, atol=1e-6)
