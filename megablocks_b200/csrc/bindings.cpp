@@ -1,0 +1,73 @@
+// Python bindings of the sm_100a extension (module megablocks_b200._C).
+#include <torch/extension.h>
+
+#include <vector>
+
+namespace mb {
+
+// torch_glue.cpp: metadata
+std::vector<at::Tensor> sort_pairs(const at::Tensor& x, int64_t end_bit);
+std::vector<at::Tensor> route_plan(const at::Tensor& top_experts, int64_t num_experts, int64_t block);
+at::Tensor histogram_op(const at::Tensor& x, int64_t num_bins);
+at::Tensor cumsum_op(const at::Tensor& x, bool exclusive);
+at::Tensor topology_op(const at::Tensor& padded_bins, int64_t block_size, int64_t rows, int64_t cols);
+at::Tensor replicate_forward(const at::Tensor& x, const at::Tensor& bins, int64_t num_outputs);
+at::Tensor replicate_backward(const at::Tensor& grad, const at::Tensor& bins);
+
+// torch_glue.cpp: permutation
+at::Tensor gather_rows_op(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& bin_ids,
+                       const c10::optional<at::Tensor>& weights, const at::Tensor& bins,
+                       const at::Tensor& padded_bins, int64_t top_k, int64_t out_rows);
+at::Tensor scatter_rows_op(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& bin_ids,
+                        const c10::optional<at::Tensor>& weights, const at::Tensor& bins,
+                        const at::Tensor& padded_bins, int64_t top_k, int64_t tokens);
+at::Tensor scatter_wgrad_op(const at::Tensor& x, const at::Tensor& grad, const at::Tensor& indices,
+                         const at::Tensor& bin_ids, const at::Tensor& bins, const at::Tensor& padded_bins,
+                         int64_t top_k);
+at::Tensor binned_gather_rows(const at::Tensor& x, const at::Tensor& indices,
+                              const c10::optional<at::Tensor>& weights, const at::Tensor& bins, int64_t capacity,
+                              int64_t top_k);
+at::Tensor binned_scatter_rows(const at::Tensor& x, const at::Tensor& indices,
+                               const c10::optional<at::Tensor>& weights, const at::Tensor& bins, int64_t top_k,
+                               int64_t tokens);
+at::Tensor binned_scatter_wgrad(const at::Tensor& x, const at::Tensor& grad, const at::Tensor& indices,
+                                const at::Tensor& bins, int64_t top_k);
+
+// torch_glue.cpp: router
+std::vector<at::Tensor> router_topk_forward(const at::Tensor& logits, int64_t top_k, double norm_p);
+at::Tensor router_topk_backward(const at::Tensor& scores, const at::Tensor& weights, const at::Tensor& experts,
+                                const at::Tensor& dscores, const at::Tensor& dweights, double norm_p);
+
+// torch_glue.cpp: grouped GEMM
+bool grouped_gemm_supported(const at::Tensor& a, const at::Tensor& b, bool trans_a, bool trans_b,
+                            int64_t num_groups);
+std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bins, bool trans_a,
+                                     bool trans_b, int64_t epilogue, int64_t act,
+                                     const c10::optional<at::Tensor>& aux1, const c10::optional<at::Tensor>& aux2,
+                                     bool want_out2, bool want_out3, int64_t num_groups,
+                                     const c10::optional<at::Tensor>& c_in);
+int64_t read_status(bool clear);
+
+}  // namespace mb
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "megablocks_b200 sm_100a kernels";
+  m.def("sort_pairs", &mb::sort_pairs);
+  m.def("route_plan", &mb::route_plan);
+  m.def("histogram", &mb::histogram_op);
+  m.def("cumsum", &mb::cumsum_op);
+  m.def("topology", &mb::topology_op);
+  m.def("replicate_forward", &mb::replicate_forward);
+  m.def("replicate_backward", &mb::replicate_backward);
+  m.def("gather_rows", &mb::gather_rows_op);
+  m.def("scatter_rows", &mb::scatter_rows_op);
+  m.def("scatter_wgrad", &mb::scatter_wgrad_op);
+  m.def("binned_gather_rows", &mb::binned_gather_rows);
+  m.def("binned_scatter_rows", &mb::binned_scatter_rows);
+  m.def("binned_scatter_wgrad", &mb::binned_scatter_wgrad);
+  m.def("router_topk_forward", &mb::router_topk_forward);
+  m.def("router_topk_backward", &mb::router_topk_backward);
+  m.def("grouped_gemm_supported", &mb::grouped_gemm_supported);
+  m.def("grouped_gemm", &mb::grouped_gemm);
+  m.def("read_status", &mb::read_status);
+}

@@ -1,0 +1,8 @@
+// Explicit instantiation of the grouped GEMM kernel: f16, layout NT.
+#include "grouped_gemm_kernel.cuh"
+
+namespace mb {
+namespace gemm {
+MB_GEMM_INSTANTIATE(__half, kNT)
+}  // namespace gemm
+}  // namespace mb

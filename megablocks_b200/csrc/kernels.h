@@ -1,0 +1,96 @@
+// Launch interface of the sm_100a kernels: plain pointers, sizes and a stream.
+// Every function enqueues work on `stream` and returns cudaGetLastError().
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace mb {
+
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kI16 = 3, kI32 = 4, kI64 = 5 };
+
+// ---- metadata.cu --------------------------------------------------------------
+constexpr int kMaxSortBins = 1024;   // one sort pass handles up to 10 key bits
+
+// Elements a warp owns in the sort passes, and the resulting number of warp chunks.
+int sort_warp_chunk(int64_t n);
+
+// One stable counting-sort pass on key bits [shift, shift + bits).  `partial`
+// ([2^bits * num_chunks] ints) and `totals` ([2^bits] ints) are scratch.  When
+// `tpe` is non-null the pass also writes the per-bin counts, their inclusive prefix
+// sums (`bins`) and the block-padded prefix sums (`padded_bins`) for the first
+// `num_real_bins` bins.  `vals_in == nullptr` means "values are 0..n-1".
+cudaError_t sort_pass(DType key_type, const void* keys, const void* vals_in, int64_t n, int shift, int bits,
+                      bool flip_sign, int chunk, int num_chunks, int* partial, int* totals, void* keys_out,
+                      void* vals_out, int* tpe, int* bins, int* padded_bins, int num_real_bins, int block,
+                      cudaStream_t stream);
+cudaError_t histogram(DType type, const void* x, int64_t batch, int64_t n, int num_bins, int* out_zeroed,
+                      int sms, cudaStream_t stream);
+cudaError_t cumsum(DType type, const void* x, void* out, int64_t rows, int64_t cols, bool exclusive,
+                   cudaStream_t stream);
+cudaError_t topology(const int* padded_bins, int num_bins, int block_size, int rows, int cols, int16_t* out,
+                     int sms, cudaStream_t stream);
+cudaError_t replicate_fwd(int elem_size, const void* x, const int* bins, int num_bins, int64_t batch,
+                          int64_t num_outputs, void* out, int sms, cudaStream_t stream);
+cudaError_t replicate_bwd(DType type, const void* grad, const int* bins, int num_bins, int64_t batch,
+                          int64_t num_inputs, void* out, cudaStream_t stream);
+
+// ---- permute.cu ---------------------------------------------------------------
+cudaError_t gather_rows(DType type, const void* x, const int* indices, const void* weights, const int* bins,
+                        const int* padded_bins, int num_bins, int top_k, int64_t out_rows, int cols, void* out,
+                        cudaStream_t stream);
+// inverse[copy] = row of the copy in the expert-ordered buffer, -1 when dropped.
+// capacity < 0: padded layout; capacity >= 0: binned layout [E, capacity].
+cudaError_t inverse_map(const int* indices, const int* bins, const int* padded_bins, int num_bins, int n,
+                        int capacity, int* inverse_filled_minus_one, cudaStream_t stream);
+cudaError_t combine_rows(DType type, const void* x, const int* inverse, const void* weights, int top_k,
+                         int64_t tokens, int cols, void* out, cudaStream_t stream);
+cudaError_t scatter_wgrad(DType type, const void* x, const void* grad, const int* inverse, int top_k,
+                          int64_t copies, int cols, void* wgrad, cudaStream_t stream);
+
+// ---- router.cu ----------------------------------------------------------------
+constexpr int kRouterMaxExperts = 1024;
+constexpr int kRouterMaxTopK = 8;
+cudaError_t router_topk_fwd(DType type, const void* logits, int64_t tokens, int num_experts, int top_k,
+                            float norm_p, void* scores, void* weights, int64_t* experts, cudaStream_t stream);
+cudaError_t router_topk_bwd(DType type, const void* scores, const int64_t* experts, const void* dscores,
+                            const void* dweights, int64_t tokens, int num_experts, int top_k, float norm_p,
+                            void* dlogits, cudaStream_t stream);
+
+// ---- grouped GEMM ---------------------------------------------------------------
+namespace gemm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;
+constexpr int kMaxGroups = 1024;
+
+enum Layout : int { kNT = 0, kNN = 1, kTN = 2 };
+enum Epilogue : int { kEpiNone = 0, kEpiAct = 1, kEpiDAct = 2, kEpiGlu = 3, kEpiDGlu = 4, kEpiAdd = 5 };
+enum Act : int { kActIdentity = 0, kActGeluTanh = 1, kActSilu = 2, kActRelu = 3, kActGeluErf = 4 };
+
+struct GemmParams {
+  const int* bins;  // [num_groups] inclusive prefix sum of rows per group
+  int num_groups;
+  int rows_total;   // rows of a (and of c for NT / NN)
+  int M;            // TN: rows of each output matrix
+  int N;            // output columns per group
+  int K;            // NT / NN: contraction length
+  void* c;
+  void* out2;
+  void* out3;
+  const void* aux1;
+  const void* aux2;
+  int epilogue;
+  int act;
+  int* status;      // device word that receives a code when a wait is abandoned
+};
+
+// block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit
+// matrices with 64-column boxes and 128-byte swizzle.
+cudaError_t launch(bool bf16, int layout, int block_n, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                   const GemmParams& params, int grid, cudaStream_t stream);
+
+}  // namespace gemm
+}  // namespace mb

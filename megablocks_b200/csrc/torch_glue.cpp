@@ -1,0 +1,523 @@
+// PyTorch-facing host code of the extension: argument checks, output allocation,
+// TMA tensor maps and calls into the torch-free kernel launchers of kernels.h.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAException.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "kernels.h"
+
+namespace mb {
+
+namespace {
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+#define MB_CHECK_CUDA(t) TORCH_CHECK((t).is_cuda(), #t " must be a CUDA tensor")
+#define MB_CHECK_CONTIG(t) TORCH_CHECK((t).is_contiguous(), #t " must be contiguous")
+#define MB_CUDA_OK(expr) C10_CUDA_CHECK(expr)
+
+int sm_count() {
+  return at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+}
+
+int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+DType float_code(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return kF32;
+    case at::kHalf: return kF16;
+    case at::kBFloat16: return kBF16;
+    default: TORCH_CHECK(false, "expected float32 / float16 / bfloat16, got ", t);
+  }
+}
+
+DType int_code(at::ScalarType t) {
+  switch (t) {
+    case at::kShort: return kI16;
+    case at::kInt: return kI32;
+    case at::kLong: return kI64;
+    default: TORCH_CHECK(false, "expected int16 / int32 / int64, got ", t);
+  }
+}
+
+int bits_for(int64_t values) {
+  int bits = 1;
+  while ((int64_t(1) << bits) < values) ++bits;
+  return bits;
+}
+
+struct SortScratch {
+  at::Tensor partial, totals;
+  int chunk, num_chunks;
+};
+
+SortScratch make_scratch(int64_t n, int nbins, const at::TensorOptions& opts) {
+  SortScratch s;
+  s.chunk = sort_warp_chunk(n);
+  s.num_chunks = std::max<int>(1, int(ceil_div(n, s.chunk)));
+  s.partial = at::empty({int64_t(nbins) * s.num_chunks}, opts.dtype(at::kInt));
+  s.totals = at::empty({nbins}, opts.dtype(at::kInt));
+  return s;
+}
+
+void check_index(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kInt && t.dim() == 1, name,
+              " must be a contiguous 1-D int32 CUDA tensor");
+}
+
+void check_weights(const c10::optional<at::Tensor>& weights, const at::Tensor& x, int64_t copies) {
+  if (!weights.has_value()) return;
+  TORCH_CHECK(weights->is_cuda() && weights->is_contiguous() && weights->numel() == copies,
+              "weights must be a contiguous CUDA tensor with one entry per routed copy");
+  TORCH_CHECK(weights->scalar_type() == x.scalar_type(), "weights must have the dtype of x");
+}
+
+const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+at::Tensor build_inverse(const at::Tensor& indices, const at::Tensor& bins, const at::Tensor& padded_bins,
+                         int capacity) {
+  const int n = int(indices.numel());
+  // Copies absent from every bin (possible only for malformed input) stay -1.
+  at::Tensor inverse = at::full({n}, -1, indices.options());
+  if (n == 0) return inverse;
+  MB_CUDA_OK(inverse_map(indices.data_ptr<int>(), bins.data_ptr<int>(), padded_bins.data_ptr<int>(),
+                         int(bins.numel()), n, capacity, inverse.data_ptr<int>(), stream()));
+  return inverse;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// sort / route plan
+// ---------------------------------------------------------------------------
+std::vector<at::Tensor> sort_pairs(const at::Tensor& x, int64_t end_bit) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 1, "sort expects a 1-D tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t n = x.numel();
+  at::Tensor keys_a = at::empty_like(x), vals_a = at::empty_like(x);
+  if (n == 0) return {keys_a, vals_a};
+  at::Tensor keys_b = at::empty_like(x), vals_b = at::empty_like(x);
+  const DType code = int_code(x.scalar_type());
+  const int width = int(x.element_size()) * 8;
+  const int total_bits = std::min<int>(std::max<int>(int(end_bit), 1), width);
+  const int passes = (total_bits + 7) / 8;
+  SortScratch s = make_scratch(n, 256, x.options());
+  const void* src_k = x.data_ptr();
+  const void* src_v = nullptr;
+  void* dst_k[2] = {keys_a.data_ptr(), keys_b.data_ptr()};
+  void* dst_v[2] = {vals_a.data_ptr(), vals_b.data_ptr()};
+  // Arrange the ping-pong so the last pass lands in (keys_a, vals_a).
+  int which = (passes % 2 == 1) ? 0 : 1;
+  for (int p = 0; p < passes; ++p) {
+    const int shift = p * 8;
+    const int bits = std::min(8, total_bits - shift);
+    const bool flip = (shift + bits == width);
+    MB_CUDA_OK(sort_pass(code, src_k, src_v, n, shift, bits, flip, s.chunk, s.num_chunks,
+                         s.partial.data_ptr<int>(), s.totals.data_ptr<int>(), dst_k[which], dst_v[which], nullptr,
+                         nullptr, nullptr, 0, 1, stream()));
+    src_k = dst_k[which];
+    src_v = dst_v[which];
+    which ^= 1;
+  }
+  return {keys_a, vals_a};
+}
+
+std::vector<at::Tensor> route_plan(const at::Tensor& top_experts, int64_t num_experts, int64_t block) {
+  MB_CHECK_CUDA(top_experts); MB_CHECK_CONTIG(top_experts);
+  TORCH_CHECK(top_experts.dim() == 1, "route_plan expects flattened expert ids");
+  TORCH_CHECK(num_experts >= 1 && block >= 1, "bad route_plan arguments");
+  c10::cuda::CUDAGuard guard(top_experts.device());
+  const int64_t n = top_experts.numel();
+  auto iopts = top_experts.options().dtype(at::kInt);
+  at::Tensor indices = at::empty({n}, iopts), bin_ids = at::empty({n}, iopts);
+  at::Tensor bins = at::zeros({num_experts}, iopts), padded_bins = at::zeros({num_experts}, iopts);
+  at::Tensor tpe = at::zeros({num_experts}, iopts);
+  if (n == 0) return {indices, bin_ids, bins, padded_bins, tpe};
+  // torch.topk yields int64 ids: narrow once, then a single counting-sort pass.
+  at::Tensor e32 = top_experts.scalar_type() == at::kInt ? top_experts : top_experts.to(at::kInt);
+  if (num_experts <= kMaxSortBins) {
+    const int bits = bits_for(num_experts);
+    SortScratch s = make_scratch(n, 1 << bits, top_experts.options());
+    MB_CUDA_OK(sort_pass(kI32, e32.data_ptr(), nullptr, n, 0, bits, false, s.chunk, s.num_chunks,
+                         s.partial.data_ptr<int>(), s.totals.data_ptr<int>(), bin_ids.data_ptr(),
+                         indices.data_ptr(), tpe.data_ptr<int>(), bins.data_ptr<int>(),
+                         padded_bins.data_ptr<int>(), int(num_experts), int(block), stream()));
+    return {indices, bin_ids, bins, padded_bins, tpe};
+  }
+  // More than 1024 experts: generic multi-pass sort, then histogram and scans.
+  auto sorted = sort_pairs(e32, bits_for(num_experts));
+  at::Tensor counts = at::bincount(e32, {}, num_experts).to(at::kInt);
+  at::Tensor padded = at::floor_divide(counts + (block - 1), block) * block;
+  return {sorted[1], sorted[0], at::cumsum(counts, 0).to(at::kInt), at::cumsum(padded, 0).to(at::kInt), counts};
+}
+
+// ---------------------------------------------------------------------------
+// histogram / cumsum / topology / replicate
+// ---------------------------------------------------------------------------
+at::Tensor histogram_op(const at::Tensor& x, int64_t num_bins) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 2, "histogram expects [batch, n]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t batch = x.size(0), n = x.size(1);
+  at::Tensor out = at::zeros({batch, num_bins}, x.options().dtype(at::kInt));
+  if (n == 0 || batch == 0) return out;
+  MB_CUDA_OK(histogram(int_code(x.scalar_type()), x.data_ptr(), batch, n, int(num_bins), out.data_ptr<int>(),
+                       sm_count(), stream()));
+  return out;
+}
+
+at::Tensor cumsum_op(const at::Tensor& x, bool exclusive) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 2, "cumsum expects a 2-D tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty_like(x);
+  if (x.numel() == 0) return out;
+  MB_CUDA_OK(cumsum(int_code(x.scalar_type()), x.data_ptr(), out.data_ptr(), x.size(0), x.size(1), exclusive,
+                    stream()));
+  return out;
+}
+
+at::Tensor topology_op(const at::Tensor& padded_bins, int64_t block_size, int64_t rows, int64_t cols) {
+  check_index(padded_bins, "padded_bins");
+  c10::cuda::CUDAGuard guard(padded_bins.device());
+  at::Tensor out = at::empty({rows * cols}, padded_bins.options().dtype(at::kShort));
+  if (out.numel() == 0) return out;
+  MB_CUDA_OK(topology(padded_bins.data_ptr<int>(), int(padded_bins.numel()), int(block_size), int(rows), int(cols),
+                      out.data_ptr<int16_t>(), sm_count(), stream()));
+  return out;
+}
+
+at::Tensor replicate_forward(const at::Tensor& x, const at::Tensor& bins, int64_t num_outputs) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  check_index(bins, "bins");
+  TORCH_CHECK(x.dim() == 2 && x.size(1) == bins.numel(), "replicate expects x[batch, num_bins]");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({x.size(0), num_outputs}, x.options());
+  if (out.numel() == 0) return out;
+  MB_CUDA_OK(replicate_fwd(int(x.element_size()), x.data_ptr(), bins.data_ptr<int>(), int(bins.numel()), x.size(0),
+                           num_outputs, out.data_ptr(), sm_count(), stream()));
+  return out;
+}
+
+at::Tensor replicate_backward(const at::Tensor& grad, const at::Tensor& bins) {
+  MB_CHECK_CUDA(grad); MB_CHECK_CONTIG(grad);
+  check_index(bins, "bins");
+  c10::cuda::CUDAGuard guard(grad.device());
+  const int num_bins = int(bins.numel());
+  at::Tensor out = at::empty({grad.size(0), num_bins}, grad.options());
+  if (out.numel() == 0) return out;
+  MB_CUDA_OK(replicate_bwd(float_code(grad.scalar_type()), grad.data_ptr(), bins.data_ptr<int>(), num_bins,
+                           grad.size(0), grad.size(1), out.data_ptr(), stream()));
+  return out;
+}
+
+// ---------------------------------------------------------------------------
+// permutation
+// ---------------------------------------------------------------------------
+at::Tensor gather_rows_op(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& bin_ids,
+                          const c10::optional<at::Tensor>& weights, const at::Tensor& bins,
+                          const at::Tensor& padded_bins, int64_t top_k, int64_t out_rows) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 2, "gather expects x[tokens, hidden]");
+  check_index(indices, "indices"); check_index(bins, "bins"); check_index(padded_bins, "padded_bins");
+  check_weights(weights, x, indices.numel());
+  (void)bin_ids;
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({out_rows, x.size(1)}, x.options());
+  if (out.numel() == 0) return out;
+  MB_CUDA_OK(gather_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
+                         bins.data_ptr<int>(), padded_bins.data_ptr<int>(), int(bins.numel()), int(top_k), out_rows,
+                         int(x.size(1)), out.data_ptr(), stream()));
+  return out;
+}
+
+at::Tensor scatter_rows_op(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& bin_ids,
+                           const c10::optional<at::Tensor>& weights, const at::Tensor& bins,
+                           const at::Tensor& padded_bins, int64_t top_k, int64_t tokens) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 2, "scatter expects x[rows, hidden]");
+  check_index(indices, "indices"); check_index(bins, "bins"); check_index(padded_bins, "padded_bins");
+  check_weights(weights, x, indices.numel());
+  (void)bin_ids;
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({tokens, x.size(1)}, x.options());
+  if (out.numel() == 0) return out;
+  at::Tensor inverse = build_inverse(indices, bins, padded_bins, -1);
+  MB_CUDA_OK(combine_rows(float_code(x.scalar_type()), x.data_ptr(), inverse.data_ptr<int>(), opt_ptr(weights),
+                          int(top_k), tokens, int(x.size(1)), out.data_ptr(), stream()));
+  return out;
+}
+
+at::Tensor scatter_wgrad_op(const at::Tensor& x, const at::Tensor& grad, const at::Tensor& indices,
+                            const at::Tensor& bin_ids, const at::Tensor& bins, const at::Tensor& padded_bins,
+                            int64_t top_k) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CUDA(grad); MB_CHECK_CONTIG(grad);
+  TORCH_CHECK(x.scalar_type() == grad.scalar_type() && x.size(1) == grad.size(1), "x / grad mismatch");
+  check_index(indices, "indices"); check_index(bins, "bins"); check_index(padded_bins, "padded_bins");
+  (void)bin_ids;
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t copies = indices.numel();
+  at::Tensor out = at::empty({copies}, x.options());
+  if (copies == 0) return out;
+  at::Tensor inverse = build_inverse(indices, bins, padded_bins, -1);
+  MB_CUDA_OK(scatter_wgrad(float_code(x.scalar_type()), x.data_ptr(), grad.data_ptr(), inverse.data_ptr<int>(),
+                           int(top_k), copies, int(x.size(1)), out.data_ptr(), stream()));
+  return out;
+}
+
+// Binned layout [E, capacity, h]: the padded gather with uniform padded bins
+// (e + 1) * capacity; copies past the capacity have no destination row.
+at::Tensor binned_gather_rows(const at::Tensor& x, const at::Tensor& indices,
+                              const c10::optional<at::Tensor>& weights, const at::Tensor& bins, int64_t capacity,
+                              int64_t top_k) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  check_index(indices, "indices"); check_index(bins, "bins");
+  check_weights(weights, x, indices.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t experts = bins.numel();
+  at::Tensor out = at::empty({experts, capacity, x.size(1)}, x.options());
+  if (out.numel() == 0) return out;
+  at::Tensor uniform = (at::arange(1, experts + 1, bins.options().dtype(at::kLong)) * capacity).to(at::kInt);
+  MB_CUDA_OK(gather_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
+                         bins.data_ptr<int>(), uniform.data_ptr<int>(), int(experts), int(top_k),
+                         experts * capacity, int(x.size(1)), out.data_ptr(), stream()));
+  return out;
+}
+
+at::Tensor binned_scatter_rows(const at::Tensor& x, const at::Tensor& indices,
+                               const c10::optional<at::Tensor>& weights, const at::Tensor& bins, int64_t top_k,
+                               int64_t tokens) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 3, "binned_scatter expects x[experts, capacity, hidden]");
+  check_index(indices, "indices"); check_index(bins, "bins");
+  check_weights(weights, x, indices.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({tokens, x.size(2)}, x.options());
+  if (out.numel() == 0) return out;
+  at::Tensor inverse = build_inverse(indices, bins, bins, int(x.size(1)));
+  MB_CUDA_OK(combine_rows(float_code(x.scalar_type()), x.data_ptr(), inverse.data_ptr<int>(), opt_ptr(weights),
+                          int(top_k), tokens, int(x.size(2)), out.data_ptr(), stream()));
+  return out;
+}
+
+at::Tensor binned_scatter_wgrad(const at::Tensor& x, const at::Tensor& grad, const at::Tensor& indices,
+                                const at::Tensor& bins, int64_t top_k) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CUDA(grad); MB_CHECK_CONTIG(grad);
+  TORCH_CHECK(x.dim() == 3 && x.scalar_type() == grad.scalar_type() && x.size(2) == grad.size(1),
+              "x / grad mismatch");
+  check_index(indices, "indices"); check_index(bins, "bins");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t copies = indices.numel();
+  at::Tensor out = at::empty({copies}, x.options());
+  if (copies == 0) return out;
+  at::Tensor inverse = build_inverse(indices, bins, bins, int(x.size(1)));
+  MB_CUDA_OK(scatter_wgrad(float_code(x.scalar_type()), x.data_ptr(), grad.data_ptr(), inverse.data_ptr<int>(),
+                           int(top_k), copies, int(x.size(2)), out.data_ptr(), stream()));
+  return out;
+}
+
+// ---------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------
+std::vector<at::Tensor> router_topk_forward(const at::Tensor& logits, int64_t top_k, double norm_p) {
+  MB_CHECK_CUDA(logits); MB_CHECK_CONTIG(logits);
+  TORCH_CHECK(logits.dim() == 2, "router_topk expects logits[tokens, experts]");
+  const int64_t tokens = logits.size(0), num_experts = logits.size(1);
+  TORCH_CHECK(num_experts <= kRouterMaxExperts && top_k >= 1 && top_k <= kRouterMaxTopK && top_k <= num_experts,
+              "router_topk supports up to 1024 experts and top_k <= 8");
+  c10::cuda::CUDAGuard guard(logits.device());
+  at::Tensor scores = at::empty_like(logits);
+  at::Tensor weights = at::empty({tokens, top_k}, logits.options());
+  at::Tensor experts = at::empty({tokens, top_k}, logits.options().dtype(at::kLong));
+  if (tokens == 0) return {scores, weights, experts};
+  MB_CUDA_OK(router_topk_fwd(float_code(logits.scalar_type()), logits.data_ptr(), tokens, int(num_experts),
+                             int(top_k), float(norm_p), scores.data_ptr(), weights.data_ptr(),
+                             experts.data_ptr<int64_t>(), stream()));
+  return {scores, weights, experts};
+}
+
+at::Tensor router_topk_backward(const at::Tensor& scores, const at::Tensor& weights, const at::Tensor& experts,
+                                const at::Tensor& dscores, const at::Tensor& dweights, double norm_p) {
+  MB_CHECK_CUDA(scores); MB_CHECK_CONTIG(scores); MB_CHECK_CONTIG(dscores); MB_CHECK_CONTIG(dweights);
+  MB_CHECK_CONTIG(experts);
+  (void)weights;
+  TORCH_CHECK(dscores.scalar_type() == scores.scalar_type() && dweights.scalar_type() == scores.scalar_type(),
+              "router gradients must have the dtype of the scores");
+  const int64_t tokens = scores.size(0), num_experts = scores.size(1), top_k = experts.size(1);
+  c10::cuda::CUDAGuard guard(scores.device());
+  at::Tensor dlogits = at::empty_like(scores);
+  if (tokens == 0) return dlogits;
+  MB_CUDA_OK(router_topk_bwd(float_code(scores.scalar_type()), scores.data_ptr(), experts.data_ptr<int64_t>(),
+                             dscores.data_ptr(), dweights.data_ptr(), tokens, int(num_experts), int(top_k),
+                             float(norm_p), dlogits.data_ptr(), stream()));
+  return dlogits;
+}
+
+// ---------------------------------------------------------------------------
+// grouped GEMM
+// ---------------------------------------------------------------------------
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result));
+    TORCH_CHECK(result == cudaDriverEntryPointSuccess && ptr != nullptr, "cuTensorMapEncodeTiled is unavailable");
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Row-major [rows, cols] 16-bit tensor, box = box_rows x 64 columns, 128-byte swizzle.
+CUtensorMap make_tensor_map(const void* base, bool bf16, int64_t rows, int64_t cols, int box_rows) {
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "grouped_gemm operands must be 16-byte aligned");
+  TORCH_CHECK(cols % 8 == 0, "grouped_gemm operands need a row length that is a multiple of 8 elements");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(std::max<int64_t>(rows, 1))};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult rc = encode_tiled_fn()(
+      &map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+      dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(rc == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", int(rc));
+  return map;
+}
+
+at::Tensor& status_word(const at::Device& device) {
+  // Leaked on purpose: freeing CUDA tensors during static destruction races with
+  // the teardown of the CUDA context.
+  static auto* words = new std::vector<at::Tensor>(64);
+  const int idx = device.index();
+  if (!(*words)[idx].defined()) (*words)[idx] = at::zeros({4}, at::TensorOptions().device(device).dtype(at::kInt));
+  return (*words)[idx];
+}
+
+}  // namespace
+
+// True when the tcgen05 kernel can run this problem; the Python caller falls back
+// to per-group library matmuls otherwise (odd sizes, fp32 inputs).
+bool grouped_gemm_supported(const at::Tensor& a, const at::Tensor& b, bool trans_a, bool trans_b,
+                            int64_t num_groups) {
+  if (!(a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf)) return false;
+  if (a.scalar_type() != b.scalar_type() || num_groups > gemm::kMaxGroups || num_groups < 1) return false;
+  if (a.dim() != 2) return false;
+  if (trans_a) {
+    if (b.dim() != 2 || a.size(0) != b.size(0)) return false;
+    const int64_t M = a.size(1), N = b.size(1);
+    return M % 8 == 0 && N % 8 == 0 && M >= 64 && N >= 64;
+  }
+  if (b.dim() != 3 || b.size(0) != num_groups) return false;
+  const int64_t K = a.size(1);
+  const int64_t N = trans_b ? b.size(1) : b.size(2);
+  const int64_t Kb = trans_b ? b.size(2) : b.size(1);
+  return K == Kb && K % 8 == 0 && N % 8 == 0 && N >= 64 && K >= 8;
+}
+
+std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bins, bool trans_a,
+                                     bool trans_b, int64_t epilogue, int64_t act,
+                                     const c10::optional<at::Tensor>& aux1, const c10::optional<at::Tensor>& aux2,
+                                     bool want_out2, bool want_out3, int64_t num_groups,
+                                     const c10::optional<at::Tensor>& c_in) {
+  using namespace gemm;
+  MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
+  MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
+  TORCH_CHECK(bins.scalar_type() == at::kInt && bins.dim() == 1 && bins.numel() == num_groups,
+              "bins must be int32 with one entry per group");
+  TORCH_CHECK(grouped_gemm_supported(a, b, trans_a, trans_b, num_groups), "unsupported grouped_gemm problem");
+  c10::cuda::CUDAGuard guard(a.device());
+  const bool bf16 = a.scalar_type() == at::kBFloat16;
+  const int layout = trans_a ? kTN : (trans_b ? kNT : kNN);
+
+  GemmParams p{};
+  p.bins = bins.data_ptr<int>();
+  p.num_groups = int(num_groups);
+  p.rows_total = int(a.size(0));
+  at::Tensor c;
+  if (layout == kTN) {
+    p.M = int(a.size(1));
+    p.N = int(b.size(1));
+    p.K = 0;
+    c = c_in.has_value() ? *c_in : at::empty({num_groups, p.M, p.N}, a.options());
+  } else {
+    p.K = int(a.size(1));
+    p.N = int(trans_b ? b.size(1) : b.size(2));
+    p.M = 0;
+    c = c_in.has_value() ? *c_in : at::empty({a.size(0), p.N}, a.options());
+  }
+  TORCH_CHECK(c.is_contiguous() && c.scalar_type() == a.scalar_type(), "bad output buffer");
+  const int64_t out_numel = c.numel();
+  auto check_aux = [&](const c10::optional<at::Tensor>& t, const char* name) {
+    TORCH_CHECK(t.has_value() && t->is_cuda() && t->is_contiguous() && t->numel() == out_numel &&
+                    t->scalar_type() == a.scalar_type(),
+                name, " must match the output in shape and dtype");
+  };
+  at::Tensor out2, out3;
+  p.epilogue = int(epilogue);
+  p.act = int(act);
+  if (epilogue == kEpiDAct || epilogue == kEpiGlu || epilogue == kEpiDGlu || epilogue == kEpiAdd) {
+    check_aux(aux1, "aux1");
+    p.aux1 = aux1->data_ptr();
+  }
+  if (epilogue == kEpiDGlu) {
+    check_aux(aux2, "aux2");
+    p.aux2 = aux2->data_ptr();
+  }
+  if (epilogue != kEpiNone && epilogue != kEpiAdd && want_out2) {
+    out2 = at::empty_like(c);
+    p.out2 = out2.data_ptr();
+  }
+  if (epilogue == kEpiDGlu && want_out3) {
+    out3 = at::empty_like(c);
+    p.out3 = out3.data_ptr();
+  }
+  p.c = c.data_ptr();
+  p.status = status_word(a.device()).data_ptr<int>();
+  if (out_numel == 0) return {c, out2, out3};
+
+  const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
+  CUtensorMap ta, tb;
+  int64_t tiles_bound;
+  const int64_t num_nb = ceil_div(p.N, block_n);
+  if (layout == kNT) {
+    ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
+    tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n);
+    tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * num_nb;
+  } else if (layout == kNN) {
+    ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
+    tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.K, p.N, 64);
+    tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * num_nb;
+  } else {
+    ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.M, 64);
+    tb = make_tensor_map(b.data_ptr(), bf16, b.size(0), p.N, 64);
+    tiles_bound = num_groups * ceil_div(p.M, kBlockM) * num_nb;
+  }
+  const int grid = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count())));
+  MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, grid, stream()));
+  return {c, out2, out3};
+}
+
+// Reads (and optionally clears) the status word of the current device; nonzero means
+// a kernel abandoned a wait.  Synchronises the device.
+int64_t read_status(bool clear) {
+  int dev = 0;
+  C10_CUDA_CHECK(cudaGetDevice(&dev));
+  at::Tensor& word = status_word(at::Device(at::kCUDA, dev));
+  const int64_t value = word[0].item<int>();
+  if (clear && value != 0) word.zero_();
+  return value;
+}
+
+}  // namespace mb

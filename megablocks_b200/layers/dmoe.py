@@ -89,7 +89,7 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         top_experts = top_experts.flatten()
         with torch.no_grad():
             indices, bin_ids, bins, padded_bins, tokens_per_expert = self.indices_and_padded_bins(top_experts)
-        x = x.view(-1, x.shape[-1])
+        x = x.reshape(-1, x.shape[-1])
         x = ops.padded_gather(x, indices, bin_ids, bins, padded_bins, self.top_k,
                               num_rows=self.padded_rows_bound(indices.numel()))
         with torch.no_grad():
@@ -104,7 +104,7 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         with torch.no_grad():
             padded = ops.round_up(tokens_per_expert, self.blocking)
             padded_bins = promote_scalar(ops.inclusive_cumsum(padded, 0))
-        x = x.view(-1, x.shape[-1])
+        x = x.reshape(-1, x.shape[-1])
         x = ops.padded_gather(x, indices, bin_ids, bins, padded_bins, top_k,
                               num_rows=self.padded_rows_bound(indices.numel()))
         with torch.no_grad():
@@ -124,7 +124,7 @@ class ParallelDroplessMLP(moe.ParallelMLP):
 
     def grouped_permute_and_compute(self, x, tokens_per_expert, indices, bin_ids, expert_weights, bins,
                                     expert_capactiy, top_k):
-        x = x.view(-1, x.shape[-1])
+        x = x.reshape(-1, x.shape[-1])
         x = ops.gather(x, indices, bin_ids, bins, top_k)
         x = self.mlp(x, tokens_per_expert)
         return ops.scatter(x, indices, bin_ids, expert_weights, bins, top_k)

@@ -120,7 +120,7 @@ class ParallelMLP(torch.nn.Module):
     # -- single device --------------------------------------------------------
     def permute_and_compute(self, x, tokens_per_expert, indices, bin_ids, expert_weights, bins, expert_capacity,
                             top_k):
-        x = x.view(-1, x.shape[-1])
+        x = x.reshape(-1, x.shape[-1])
         x = ops.binned_gather(x, indices, bins, expert_capacity, top_k)
         x = self.mlp(x)
         return ops.binned_scatter(x, indices, expert_weights, bins, top_k)
@@ -169,7 +169,7 @@ class ParallelMLP(torch.nn.Module):
             recv_tpe = torch.empty_like(send_tpe)
             count_handle = dist.all_to_all_single(recv_tpe, send_tpe, group=group, async_op=True)
 
-        x = x.view(-1, x.shape[-1])
+        x = x.reshape(-1, x.shape[-1])
         x = ops.gather(x, indices, bin_ids, bins, self.top_k)
 
         with torch.no_grad():

@@ -131,7 +131,7 @@ class LearnedRouter(torch.nn.Module):
     def forward(self, x: torch.Tensor):
         if self.training and self.args.moe_jitter_eps is not None:
             x = x * self.jitter(x)
-        logits = self.layer(x.view(-1, x.shape[-1]))
+        logits = self.layer(x.reshape(-1, x.shape[-1]))
         _save_router_logits(logits, self.args)
         scores, weights, experts = self._select(logits)
         if self.args.uniform_expert_assignment:

@@ -1,0 +1,267 @@
+"""Decoder-only transformers whose feed-forward blocks are dMoE / MoE layers.
+
+The reference ships no model code: its experiment scripts train GPT-2 style
+models through a Megatron-LM fork that replaces every FFN with a dMoE layer
+(exp/dmoe/dmoe_125m_8gpu.sh:53-72,143-148).  This module provides that model
+family natively so the library can be trained and benchmarked stand-alone:
+
+* ``gpt2`` flavour: LayerNorm, learned positions, GELU experts, tied LM head;
+* ``mixtral`` flavour: RMSNorm, rotary positions, grouped-query attention,
+  SwiGLU experts (``mlp_type='glu'``), untied LM head.
+
+Attention uses the library fused attention (``scaled_dot_product_attention``);
+everything MoE runs this library's kernels.  Inputs are ``[batch, seq]`` token ids.
+"""
+
+import dataclasses
+import math
+from functools import partial
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from megablocks_b200.layers.arguments import Arguments
+from megablocks_b200.layers.dmoe import dMoE
+from megablocks_b200.layers.moe import MoE, batched_load_balancing_loss, clear_load_balancing_loss
+from megablocks_b200.layers.router import batched_router_zloss, clear_router_zloss
+
+
+@dataclasses.dataclass
+class TransformerConfig:
+    flavour: str = 'gpt2'               # 'gpt2' | 'mixtral'
+    vocab_size: int = 51200
+    max_seq_len: int = 1024
+    num_layers: int = 12
+    hidden_size: int = 768
+    num_heads: int = 12
+    num_kv_heads: Optional[int] = None  # grouped-query attention when < num_heads
+    ffn_hidden_size: int = 3072
+    moe_num_experts: int = 64
+    moe_top_k: int = 1
+    moe_loss_weight: float = 0.1
+    moe_zloss_weight: float = 0.0
+    moe_capacity_factor: int = 1
+    dropless: bool = True
+    mlp_impl: str = 'grouped'
+    memory_optimized_mlp: bool = True
+    rope_theta: float = 10000.0
+    init_std: float = 0.02
+    activation_checkpointing: bool = False
+    dtype: torch.dtype = torch.bfloat16
+    device: Optional[torch.device] = None
+    # expert parallelism
+    expert_parallel_group: Optional[object] = None
+    ep_fused_comm: Optional[bool] = None
+
+    @property
+    def kv_heads(self) -> int:
+        return self.num_kv_heads or self.num_heads
+
+    def moe_arguments(self) -> Arguments:
+        glu = self.flavour == 'mixtral'
+        return Arguments(
+            hidden_size=self.hidden_size,
+            ffn_hidden_size=self.ffn_hidden_size,
+            num_layers=self.num_layers,
+            bias=not glu,
+            return_bias=False,
+            activation_fn=F.silu if glu else partial(F.gelu, approximate='tanh'),
+            moe_num_experts=self.moe_num_experts,
+            moe_top_k=self.moe_top_k,
+            moe_capacity_factor=self.moe_capacity_factor,
+            moe_loss_weight=self.moe_loss_weight,
+            moe_zloss_weight=self.moe_zloss_weight,
+            moe_lbl_in_fp32=True,
+            moe_normalize_expert_weights=1 if glu else None,
+            moe_expert_model_parallelism=self.expert_parallel_group is not None,
+            expert_parallel_group=self.expert_parallel_group,
+            memory_optimized_mlp=self.memory_optimized_mlp,
+            mlp_type='glu' if glu else 'mlp',
+            mlp_impl=self.mlp_impl,
+            fp16=self.dtype == torch.float16,
+            bf16=self.dtype == torch.bfloat16,
+            device=self.device if self.device is not None else torch.device('cpu'),
+            init_method=partial(nn.init.normal_, mean=0.0, std=self.init_std),
+            output_layer_init_method=partial(nn.init.normal_, mean=0.0,
+                                             std=self.init_std / math.sqrt(2.0 * self.num_layers)),
+            ep_fused_comm=self.ep_fused_comm,
+        )
+
+
+# Named configurations: the dMoE family trained by the reference's experiment
+# scripts (exp/dmoe/*.sh: 64 experts, top-1, ffn = 4 x hidden, seq 1024) and a
+# Mixtral-8x7B-shaped model.
+PRESETS = {
+    'dmoe-46m': dict(num_layers=6, hidden_size=512, num_heads=8, ffn_hidden_size=2048),
+    'dmoe-125m': dict(num_layers=12, hidden_size=768, num_heads=12, ffn_hidden_size=3072),
+    'dmoe-356m': dict(num_layers=24, hidden_size=1024, num_heads=16, ffn_hidden_size=4096),
+    'dmoe-760m': dict(num_layers=24, hidden_size=1536, num_heads=16, ffn_hidden_size=6144),
+    'mixtral-8x7b': dict(flavour='mixtral', vocab_size=32000, max_seq_len=4096, num_layers=32, hidden_size=4096,
+                         num_heads=32, num_kv_heads=8, ffn_hidden_size=14336, moe_num_experts=8, moe_top_k=2,
+                         rope_theta=1e6),
+    'tiny': dict(vocab_size=512, max_seq_len=64, num_layers=2, hidden_size=128, num_heads=4, ffn_hidden_size=256,
+                 moe_num_experts=8, moe_top_k=2),
+    'tiny-mixtral': dict(flavour='mixtral', vocab_size=512, max_seq_len=64, num_layers=2, hidden_size=128,
+                         num_heads=4, num_kv_heads=2, ffn_hidden_size=256, moe_num_experts=4, moe_top_k=2),
+}
+
+
+def preset(name: str, **overrides) -> TransformerConfig:
+    cfg = dict(PRESETS[name])
+    cfg.update(overrides)
+    return TransformerConfig(**cfg)
+
+
+class RMSNorm(nn.Module):
+
+    def __init__(self, dim: int, eps: float = 1e-5, device=None, dtype=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+
+def _rope_tables(seq_len: int, head_dim: int, theta: float, device):
+    inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
+    return ang.cos(), ang.sin()
+
+
+def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    # x: [batch, heads, seq, head_dim]; rotate pairs (i, i + d/2).
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d].float(), x[..., d:].float()
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class Attention(nn.Module):
+
+    def __init__(self, cfg: TransformerConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.head_dim = cfg.hidden_size // cfg.num_heads
+        kw = dict(device=cfg.device, dtype=cfg.dtype)
+        bias = cfg.flavour == 'gpt2'
+        qkv_out = (cfg.num_heads + 2 * cfg.kv_heads) * self.head_dim
+        self.qkv = nn.Linear(cfg.hidden_size, qkv_out, bias=bias, **kw)
+        self.proj = nn.Linear(cfg.hidden_size, cfg.hidden_size, bias=bias, **kw)
+        nn.init.normal_(self.qkv.weight, std=cfg.init_std)
+        nn.init.normal_(self.proj.weight, std=cfg.init_std / math.sqrt(2.0 * cfg.num_layers))
+        if bias:
+            nn.init.zeros_(self.qkv.bias)
+            nn.init.zeros_(self.proj.bias)
+
+    def forward(self, x: torch.Tensor, rope) -> torch.Tensor:
+        b, s, _ = x.shape
+        cfg = self.cfg
+        qkv = self.qkv(x)
+        q_dim, kv_dim = cfg.num_heads * self.head_dim, cfg.kv_heads * self.head_dim
+        q, k, v = qkv.split([q_dim, kv_dim, kv_dim], dim=-1)
+        q = q.view(b, s, cfg.num_heads, self.head_dim).transpose(1, 2)
+        k = k.view(b, s, cfg.kv_heads, self.head_dim).transpose(1, 2)
+        v = v.view(b, s, cfg.kv_heads, self.head_dim).transpose(1, 2)
+        if rope is not None:
+            q, k = _apply_rope(q, *rope), _apply_rope(k, *rope)
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=cfg.kv_heads != cfg.num_heads)
+        return self.proj(out.transpose(1, 2).reshape(b, s, -1))
+
+
+class Block(nn.Module):
+
+    def __init__(self, cfg: TransformerConfig, moe_args: Arguments):
+        super().__init__()
+        kw = dict(device=cfg.device, dtype=cfg.dtype)
+        norm = RMSNorm if cfg.flavour == 'mixtral' else nn.LayerNorm
+        self.ln1 = norm(cfg.hidden_size, **kw)
+        self.attn = Attention(cfg)
+        self.ln2 = norm(cfg.hidden_size, **kw)
+        self.moe = (dMoE if cfg.dropless else MoE)(moe_args)
+
+    def forward(self, x: torch.Tensor, rope) -> torch.Tensor:
+        x = x + self.attn(self.ln1(x), rope)
+        # The MoE layer is token-wise: it flattens every leading dimension, so the
+        # [batch, seq, hidden] activations go in as they are (no transpose copy).
+        return x + self.moe(self.ln2(x))
+
+
+class MoETransformer(nn.Module):
+    """Token ids ``[batch, seq]`` -> logits ``[batch, seq, vocab]`` (and the training loss)."""
+
+    def __init__(self, cfg: TransformerConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.moe_args = cfg.moe_arguments()
+        kw = dict(device=cfg.device, dtype=cfg.dtype)
+        self.wte = nn.Embedding(cfg.vocab_size, cfg.hidden_size, **kw)
+        nn.init.normal_(self.wte.weight, std=cfg.init_std)
+        self.wpe = None
+        if cfg.flavour == 'gpt2':
+            self.wpe = nn.Embedding(cfg.max_seq_len, cfg.hidden_size, **kw)
+            nn.init.normal_(self.wpe.weight, std=cfg.init_std)
+        self.blocks = nn.ModuleList([Block(cfg, self.moe_args) for _ in range(cfg.num_layers)])
+        norm = RMSNorm if cfg.flavour == 'mixtral' else nn.LayerNorm
+        self.ln_f = norm(cfg.hidden_size, **kw)
+        self.lm_head = None
+        if cfg.flavour == 'mixtral':
+            self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, **kw)
+            nn.init.normal_(self.lm_head.weight, std=cfg.init_std)
+        self._rope = None
+
+    def _rope_for(self, seq: int, device):
+        if self.cfg.flavour != 'mixtral':
+            return None
+        if self._rope is None or self._rope[0].shape[0] < seq or self._rope[0].device != device:
+            head_dim = self.cfg.hidden_size // self.cfg.num_heads
+            self._rope = _rope_tables(max(seq, self.cfg.max_seq_len), head_dim, self.cfg.rope_theta, device)
+        return self._rope[0][:seq], self._rope[1][:seq]
+
+    def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
+        b, s = tokens.shape
+        x = self.wte(tokens)
+        if self.wpe is not None:
+            x = x + self.wpe(torch.arange(s, device=tokens.device))
+        rope = self._rope_for(s, tokens.device)
+        for block in self.blocks:
+            if self.cfg.activation_checkpointing and self.training:
+                x = checkpoint(block, x, rope, use_reentrant=False)
+            else:
+                x = block(x, rope)
+        return self.ln_f(x)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        weight = self.lm_head.weight if self.lm_head is not None else self.wte.weight
+        return F.linear(hidden, weight)
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        return self.logits(self.hidden_states(tokens))
+
+    def loss(self, tokens: torch.Tensor, targets: torch.Tensor):
+        """Next-token cross entropy plus the MoE auxiliary losses.
+
+        Returns ``(total, lm_loss)``.  Clears the per-step loss accumulators.
+        """
+        hidden = self.hidden_states(tokens)
+        logits = self.logits(hidden)
+        lm = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1))
+        total = lm
+        if self.training and self.moe_args.moe_loss_weight > 0:
+            total = total + batched_load_balancing_loss(self.moe_args)
+        if self.training and self.moe_args.moe_zloss_weight > 0:
+            total = total + batched_router_zloss(self.moe_args).sum()
+        clear_load_balancing_loss()
+        clear_router_zloss()
+        return total, lm.detach()
+
+    def num_parameters(self, only_active: bool = False) -> int:
+        total = 0
+        for name, p in self.named_parameters():
+            n = p.numel()
+            if only_active and '.moe.experts.mlp.' in name:
+                n = n * self.cfg.moe_top_k // max(1, p.shape[0] // self.cfg.ffn_hidden_size)
+            total += n
+        return total

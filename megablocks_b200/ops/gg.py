@@ -131,13 +131,13 @@ def _bounds(bins: torch.Tensor):
 
 def _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups):
     if trans_a:
-        out = torch.zeros(num_groups, a.shape[1], b.shape[1], dtype=torch.float32)
+        out = torch.zeros(num_groups, a.shape[1], b.shape[1], dtype=torch.float32, device=a.device)
         for e, (s, t) in enumerate(_bounds(bins)):
             if t > s:
                 out[e] = a[s:t].float().t() @ b[s:t].float()
         return out
     n_out = b.shape[1] if trans_b else b.shape[2]
-    out = torch.zeros(a.shape[0], n_out, dtype=torch.float32)
+    out = torch.zeros(a.shape[0], n_out, dtype=torch.float32, device=a.device)
     for e, (s, t) in enumerate(_bounds(bins)):
         if t > s:
             w = b[e].float()
@@ -182,9 +182,12 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     """
     if num_groups is None:
         num_groups = bins.numel()
-    if a.is_cuda:
+    if a.is_cuda and ext().grouped_gemm_supported(a, b, bool(trans_a), bool(trans_b), int(num_groups)):
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
                                   bool(want_out2), bool(want_out3), int(num_groups), c)
+    # Shapes or dtypes the tensor-core kernel does not take (fp32 inputs, rows that
+    # are not a multiple of 8 elements, more than 1024 groups) and every CPU tensor:
+    # per-group matmuls in fp32.  On CUDA this reads the group sizes back to the host.
     acc = _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups)
     out, out2, out3 = _cpu_epilogue(acc, epilogue, act, aux1, aux2, a.dtype)
     if not trans_a:

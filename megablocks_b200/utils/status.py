@@ -1,0 +1,35 @@
+"""Device-side error reporting.
+
+Kernels that wait on a barrier, a flag or a peer bound every wait; a wait that
+runs out records a code in a per-device status word instead of trapping or
+spinning forever.  :func:`check` reads that word (one device synchronisation)
+and raises if a kernel gave up.
+"""
+
+import torch
+
+from megablocks_b200._ext import ext
+
+_MESSAGES = {
+    1: 'grouped GEMM: TMA producer timed out waiting for a free shared-memory stage',
+    2: 'grouped GEMM: MMA warp timed out waiting for a TMA tile',
+    3: 'grouped GEMM: MMA warp timed out waiting for a free accumulator',
+    4: 'grouped GEMM: epilogue timed out waiting for an accumulator',
+}
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A kernel abandoned a bounded wait; its outputs are not valid."""
+
+
+def read(clear: bool = True) -> int:
+    """Status word of the current CUDA device (0 = no error)."""
+    if not torch.cuda.is_available():
+        return 0
+    return int(ext().read_status(clear))
+
+
+def check() -> None:
+    code = read(clear=True)
+    if code:
+        raise DeviceWaitTimeout(_MESSAGES.get(code, f'device wait timed out (code {code})'))

@@ -33,6 +33,9 @@ def _seed():
     if torch.cuda.is_available():
         torch.cuda.manual_seed_all(1234)
     yield
+    if torch.cuda.is_available():
+        from megablocks_b200.utils import status
+        status.check()   # no kernel may have abandoned a wait
     from megablocks_b200.layers import moe, router
     moe.clear_load_balancing_loss()
     router.clear_router_zloss()

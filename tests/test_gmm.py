@@ -12,6 +12,15 @@ def _tol(dtype):
     return dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=1e-4, atol=1e-4)
 
 
+def _close(out, ref, dtype):
+    """Compare against an fp32 reference; a 16-bit result carries one rounding of its own magnitude."""
+    out, ref = out.detach().cpu().float(), ref.detach().cpu().float()
+    if dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+    else:
+        torch.testing.assert_close(out, ref, rtol=2e-2, atol=1e-2 * float(ref.abs().max()) + 1e-3)
+
+
 def _dtype_for(device):
     return torch.bfloat16 if device == 'cuda' else torch.float32
 
@@ -53,13 +62,12 @@ def test_gmm_forward_backward(device, z, m, k, n, trans_b):
     a2 = a.detach().cpu().float().requires_grad_(True)
     b2 = b.detach().cpu().float().requires_grad_(True)
     ref = _ref_gmm(a2, b2, counts, trans_b)
-    torch.testing.assert_close(out.detach().cpu().float(), ref.detach(), **_tol(dtype))
-    probe = torch.randn(m, n)
+    _close(out, ref, dtype)
+    probe = torch.randn(m, n).to(dtype).float()
     (out.float() * probe.to(device)).sum().backward()
     (ref * probe).sum().backward()
-    torch.testing.assert_close(a.grad.cpu().float(), a2.grad, **_tol(dtype))
-    gtol = dict(rtol=3e-2, atol=3e-1) if dtype != torch.float32 else _tol(dtype)
-    torch.testing.assert_close(b.grad.cpu().float(), b2.grad, **gtol)
+    _close(a.grad, a2.grad, dtype)
+    _close(b.grad, b2.grad, dtype)
 
 
 @pytest.mark.parametrize('device', DEVICES)
