@@ -1,0 +1,150 @@
+"""Reference arm of bench.py: the UNMODIFIED reference library on the same model and step.
+
+Everything MoE here is the reference's own code, imported from ``baseline/_ref``
+(``pip install --target`` of the reference tree) through its public API
+(``megablocks.layers.arguments.Arguments`` + ``megablocks.layers.dmoe.dMoE``), on its
+stock ``mlp_impl='grouped'`` path.  Two packages the reference imports cannot be
+installed offline; ``baseline/shims`` provides import-level stand-ins for them
+(``grouped_gemm``: the package's default per-expert cuBLAS loop; ``stk``: container
+and decorators only).  The surrounding GPT-2 backbone, data-parallel all-reduce and
+mixed-precision Adam are plain PyTorch written here, standing in for the Megatron-LM
+fork the reference's scripts use (exp/dmoe/dmoe_125m_8gpu.sh of the reference): bf16
+parameters, fp32 main parameters, Adam, clip-grad 1.0, local (non-overlapped) DDP.
+Nothing from ``megablocks_b200`` is imported on this path.
+"""
+
+import math
+import os
+import sys
+from functools import partial
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def import_reference():
+    """Put the installed reference (and the two shims) first on sys.path and import it."""
+    ref = os.path.join(HERE, '_ref')
+    if not os.path.isdir(os.path.join(ref, 'megablocks')):
+        raise ImportError('baseline/_ref/megablocks is missing: the reference is not installed')
+    for path in (os.path.join(HERE, 'shims'), ref):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    import megablocks  # noqa: F401
+    from megablocks.layers import dmoe, moe
+    from megablocks.layers.arguments import Arguments
+    return Arguments, dmoe, moe
+
+
+class RefAttention(nn.Module):
+
+    def __init__(self, hidden, heads, layers, device, dtype):
+        super().__init__()
+        self.heads = heads
+        self.qkv = nn.Linear(hidden, 3 * hidden, device=device, dtype=dtype)
+        self.proj = nn.Linear(hidden, hidden, device=device, dtype=dtype)
+        nn.init.normal_(self.qkv.weight, std=0.02)
+        nn.init.normal_(self.proj.weight, std=0.02 / math.sqrt(2.0 * layers))
+        nn.init.zeros_(self.qkv.bias)
+        nn.init.zeros_(self.proj.bias)
+
+    def forward(self, x):
+        b, s, h = x.shape
+        q, k, v = self.qkv(x).split(h, dim=-1)
+        q, k, v = (t.view(b, s, self.heads, h // self.heads).transpose(1, 2) for t in (q, k, v))
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.proj(out.transpose(1, 2).reshape(b, s, h))
+
+
+class RefBlock(nn.Module):
+
+    def __init__(self, cfg, moe_args, dmoe_mod, device, dtype):
+        super().__init__()
+        self.ln1 = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+        self.attn = RefAttention(cfg['hidden'], cfg['heads'], cfg['layers'], device, dtype)
+        self.ln2 = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+        self.moe = dmoe_mod.dMoE(moe_args)
+
+    def forward(self, x):
+        x = x + self.attn(self.ln1(x))
+        return x + self.moe(self.ln2(x))
+
+
+class RefGPT(nn.Module):
+
+    def __init__(self, cfg, device, ep_group=None):
+        super().__init__()
+        Arguments, dmoe_mod, self.moe_mod = import_reference()
+        dtype = torch.bfloat16
+        self.moe_args = Arguments(
+            hidden_size=cfg['hidden'], ffn_hidden_size=cfg['ffn'], num_layers=cfg['layers'], bias=True,
+            return_bias=False, activation_fn=partial(F.gelu, approximate='tanh'),
+            moe_num_experts=cfg['experts'], moe_top_k=cfg['top_k'], moe_loss_weight=0.1, moe_lbl_in_fp32=True,
+            moe_expert_model_parallelism=ep_group is not None, expert_parallel_group=ep_group,
+            memory_optimized_mlp=True, mlp_type='mlp', mlp_impl='grouped', fp16=False, bf16=True, device=device,
+            init_method=partial(nn.init.normal_, mean=0.0, std=0.02),
+            output_layer_init_method=partial(nn.init.normal_, mean=0.0, std=0.02 / math.sqrt(2.0 * cfg['layers'])))
+        self.wte = nn.Embedding(cfg['vocab'], cfg['hidden'], device=device, dtype=dtype)
+        self.wpe = nn.Embedding(cfg['seq'], cfg['hidden'], device=device, dtype=dtype)
+        nn.init.normal_(self.wte.weight, std=0.02)
+        nn.init.normal_(self.wpe.weight, std=0.02)
+        self.blocks = nn.ModuleList(
+            [RefBlock(cfg, self.moe_args, dmoe_mod, device, dtype) for _ in range(cfg['layers'])])
+        self.ln_f = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+
+    def loss(self, tokens, targets):
+        b, s = tokens.shape
+        x = self.wte(tokens) + self.wpe(torch.arange(s, device=tokens.device))
+        for block in self.blocks:
+            x = block(x)
+        logits = F.linear(self.ln_f(x), self.wte.weight)
+        lm = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1))
+        total = lm + self.moe_mod.batched_load_balancing_loss(self.moe_args)
+        self.moe_mod.clear_load_balancing_loss()
+        return total, lm.detach()
+
+
+class RefTrainer:
+    """bf16 model parameters, fp32 main parameters, Adam, clip-grad 1.0, local DDP."""
+
+    def __init__(self, model, lr=6e-4, world=1, group=None):
+        self.model, self.world, self.group = model, world, group
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        self.dense = [p for p in self.params if not getattr(p, 'expert_model_parallel', False)]
+        self.main = [p.detach().clone().float().requires_grad_(True) for p in self.params]
+        self.opt = torch.optim.Adam(self.main, lr=lr, betas=(0.9, 0.95), eps=1e-8, fused=True)
+        self.device = self.params[0].device
+
+    def step(self, tokens, targets):
+        self.model.train()
+        for p in self.params:
+            p.grad = None
+        total, lm = self.model.loss(tokens, targets)
+        total.backward()
+        if self.world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in self.dense])
+            dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
+            off = 0
+            for p in self.dense:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p))
+                off += p.numel()
+        for m, p in zip(self.main, self.params):
+            m.grad = p.grad.float()
+        sq = torch.stack([g.grad.square().sum() * (1.0 if getattr(p, 'expert_model_parallel', False) or
+                                                    self.world == 1 else 1.0 / self.world)
+                          for g, p in zip(self.main, self.params)]).sum()
+        if self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        coeff = torch.clamp(1.0 / (sq.sqrt() + 1e-6), max=1.0)
+        torch._foreach_mul_([m.grad for m in self.main], coeff)
+        self.opt.step()
+        torch._foreach_copy_(self.params, self.main)
+        return lm
+
+    def step_from_host(self, batch):
+        dev = batch.to(self.device, non_blocking=True)
+        return float(self.step(dev[:, :-1], dev[:, 1:]).item())

@@ -1,0 +1,265 @@
+"""Headline benchmark: dMoE training throughput (tokens/s per box, max over ranks).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N ...             # the unmodified reference
+
+Model and step are the reference's 125M dMoE experiment (exp/dmoe/dmoe_125m_8gpu.sh
+of the reference): GPT-2 backbone with 12 layers, d_model 768, 12 heads, seq 1024,
+vocab 51200, every FFN a dMoE with 64 experts, top-1, ffn 3072, tanh-GELU; bf16
+compute with fp32 master weights, Adam, clip-grad 1.0; micro-batch 32 per GPU;
+expert-parallel degree = number of GPUs with the non-expert parameters
+data-parallel.  Tokens are uniform-random ids, weights are randomly initialised.
+
+For N > 1 the script expects to be started once per GPU (``python -m
+torch.distributed.run --nproc-per-node N bench.py --gpus N ...``) and reads
+RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment.
+
+Two numbers are measured back to back, both with CUDA events between a barrier +
+device synchronisation on each side and reduced with MAX over ranks:
+``value`` with inputs already on the device and no host synchronisation inside the
+timed region, and ``e2e`` through ``Trainer.step_from_host`` where every step copies
+its token batch from pinned host memory and reads the loss back.  Rank 0 prints one
+JSON line.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = 'dMoE train tokens/s per box (max over ranks)'
+MODEL = dict(layers=12, hidden=768, heads=12, seq=1024, vocab=51200, experts=64, top_k=1, ffn=3072)
+MICRO_BATCH = 32
+# Throughput derived from the reference's published training-time plot for this model
+# on 8x A100-80GB (0.19 days for 20000 steps x 512 x 1024 tokens): 80k tokens/s per GPU.
+PUBLISHED_TOKENS_PER_S_PER_GPU = 80_000.0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+             'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits', '-lms', '200', '-i',
+                 str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[4:8]):
+                if flag.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'samples': len(sm), 'reasons': sorted(reasons)}
+
+
+def _dist_setup(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != n_gpus:
+        raise SystemExit(f'--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run '
+                         f'--nproc-per-node {n_gpus}')
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        os.environ.setdefault('MASTER_PORT', '29511')
+        dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', local))
+    return rank, world, local
+
+
+def _measure(trainer, world, rank, local, steps, warmup, launch_counter):
+    """Returns (device-timed ms/step, e2e ms/step, clocks, launches, h2d bytes, d2h bytes)."""
+    import torch
+    import torch.distributed as dist
+
+    device = torch.device('cuda', local)
+    gen = torch.Generator().manual_seed(1234 + rank)
+    seq, vocab = MODEL['seq'], MODEL['vocab']
+    host_batches = [torch.randint(0, vocab, (MICRO_BATCH, seq + 1), generator=gen).pin_memory() for _ in range(4)]
+    dev_batches = [b.to(device) for b in host_batches]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(warmup):
+        b = dev_batches[i % len(dev_batches)]
+        trainer.step(b[:, :-1], b[:, 1:])
+    barrier()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = launch_counter()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        b = dev_batches[i % len(dev_batches)]
+        trainer.step(b[:, :-1], b[:, 1:])
+    end.record()
+    barrier()
+    launches = launch_counter() - launches0
+    device_ms = max_over_ranks(start.elapsed_time(end) / steps)
+
+    # End to end: host-resident batch in, loss value out, every step.
+    trainer.step_from_host(host_batches[0])
+    barrier()
+    start2, end2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start2.record()
+    last = None
+    for i in range(steps):
+        last = trainer.step_from_host(host_batches[i % len(host_batches)])
+    end2.record()
+    barrier()
+    clocks = sampler.stop()
+    e2e_ms = max_over_ranks(start2.elapsed_time(end2) / steps)
+    h2d = host_batches[0].numel() * host_batches[0].element_size()
+    return device_ms, e2e_ms, clocks, launches, h2d, 4, last
+
+
+def _emit(impl, n_gpus, steps, warmup, device_ms, e2e_ms, clocks, launches, h2d, d2h, loss, extra_config=None):
+    tokens_per_step = n_gpus * MICRO_BATCH * MODEL['seq']
+    value = tokens_per_step / (device_ms / 1e3)
+    e2e = tokens_per_step / (e2e_ms / 1e3)
+    config = {
+        'model': 'dMoE-XS: GPT-2 125M backbone (12L, d768, 12 heads), every FFN a dMoE 64 experts top-1 ffn 3072 GELU',
+        'global_batch': n_gpus * MICRO_BATCH, 'micro_batch_per_gpu': MICRO_BATCH, 'seq_len': MODEL['seq'],
+        'vocab': MODEL['vocab'], 'parallelism': f'ep{n_gpus}' + (f'+dp{n_gpus}(non-expert)' if n_gpus > 1 else ''),
+        'optimizer': 'Adam, fp32 master weights, clip-grad 1.0',
+        'l2': 'no flush needed: one step touches tens of GB, far beyond the 126 MB L2',
+        'vs_baseline_denominator': 'reference plot-derived 80k tokens/s per A100 GPU x n_gpus',
+        'last_loss': loss,
+    }
+    config.update(extra_config or {})
+    line = {
+        'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': n_gpus, 'steps': steps, 'warmup': warmup,
+        'ms_per_step': device_ms, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': value / (PUBLISHED_TOKENS_PER_S_PER_GPU * n_gpus), 'dtype': 'bf16',
+        'data': 'synthetic uniform-random token ids, random-init weights', 'impl': impl, 'config': config,
+        'clocks': clocks,
+        'e2e': {'value': e2e, 'unit': 'tokens/s', 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
+                'd2h_bytes_per_step': d2h},
+        'gpu_launches': launches,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = _dist_setup(args.gpus)
+    from megablocks_b200._ext import ext
+    from megablocks_b200.models.transformer import MoETransformer, preset
+    from megablocks_b200.train import Trainer, TrainerConfig
+    from megablocks_b200.utils import status
+
+    torch.manual_seed(1234)
+    group = dist.group.WORLD if world > 1 else None
+    cfg = preset('dmoe-125m', device=torch.device('cuda', local), expert_parallel_group=group,
+                 mlp_impl=args.mlp_impl, memory_optimized_mlp=True)
+    model = MoETransformer(cfg)
+    trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000), dp_group=group)
+    out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count)
+    status.check()
+    if rank == 0:
+        _emit('megablocks_b200', args.gpus, args.steps, args.warmup, *out,
+              extra_config={'mlp_impl': args.mlp_impl,
+                            'ep_comm': 'fused peer-memory kernels' if getattr(model.blocks[0].moe.experts,
+                                                                             '_fused_ep', None) else
+                            ('nccl all_to_all' if world > 1 else 'none')})
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    try:
+        import torch
+        import torch.distributed as dist
+        sys.path.insert(0, os.path.join(ROOT, 'baseline'))
+        import ref_arm
+        ref_arm.import_reference()
+    except Exception as exc:  # the reference (or its CUDA extension) is not installed on this box
+        if int(os.environ.get('RANK', '0')) == 0:
+            print(json.dumps({'impl': 'reference', 'unavailable': f'{type(exc).__name__}: {exc}'.splitlines()[0]}),
+                  flush=True)
+        return
+    rank, world, local = _dist_setup(args.gpus)
+    torch.manual_seed(1234)
+    group = dist.group.WORLD if world > 1 else None
+    model = ref_arm.RefGPT(MODEL, torch.device('cuda', local), ep_group=group)
+    trainer = ref_arm.RefTrainer(model, world=world, group=group)
+    out = _measure(trainer, world, rank, local, args.steps, args.warmup, lambda: 0)
+    if rank == 0:
+        _emit('reference', args.gpus, args.steps, args.warmup, *out,
+              extra_config={'mlp_impl': 'grouped', 'ep_comm': 'nccl all_to_all' if world > 1 else 'none',
+                            'note': 'unmodified reference library from baseline/_ref; grouped_gemm and stk '
+                                    'are import shims (per-expert cuBLAS loop), backbone/optimizer plain PyTorch'})
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=8)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
+    ap.add_argument('--mlp-impl', dest='mlp_impl', choices=['grouped', 'sparse'], default='grouped')
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

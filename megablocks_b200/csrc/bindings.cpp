@@ -47,6 +47,16 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool want_out2, bool want_out3, int64_t num_groups,
                                      const c10::optional<at::Tensor>& c_in);
 int64_t read_status(bool clear);
+int64_t launch_count();
+
+// torch_glue.cpp: optimizer
+int64_t adam_record_size();
+void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t param_code,
+                  int64_t grad_code, double lr, double beta1, double beta2, double eps, double weight_decay,
+                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale);
+void grad_sqnorm_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t grad_code,
+                    at::Tensor out_accum);
+void clip_coeff_op(const at::Tensor& sqnorm, double max_norm, double extra_scale, at::Tensor out);
 
 }  // namespace mb
 
@@ -70,4 +80,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm_supported", &mb::grouped_gemm_supported);
   m.def("grouped_gemm", &mb::grouped_gemm);
   m.def("read_status", &mb::read_status);
+  m.def("launch_count", &mb::launch_count);
+  m.def("adam_record_size", &mb::adam_record_size);
+  m.def("adam_step", &mb::adam_step_op);
+  m.def("grad_sqnorm", &mb::grad_sqnorm_op);
+  m.def("clip_coeff", &mb::clip_coeff_op);
 }

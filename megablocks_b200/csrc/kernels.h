@@ -59,6 +59,25 @@ cudaError_t router_topk_bwd(DType type, const void* scores, const int64_t* exper
                             const void* dweights, int64_t tokens, int num_experts, int top_k, float norm_p,
                             void* dlogits, cudaStream_t stream);
 
+// ---- optim.cu -----------------------------------------------------------------
+struct AdamTensor {
+  void* param;        // 16-bit (or fp32) shadow weights the model computes with
+  const void* grad;
+  float* master;      // fp32 weights
+  float* exp_avg;
+  float* exp_avg_sq;
+  int64_t numel;
+  float norm_weight;  // weight of this tensor in the squared gradient norm
+  int pad_;
+};
+// `blocks[i] = {tensor index, chunk index}`; every CTA updates `chunk` elements.
+cudaError_t adam_step(DType param_type, DType grad_type, const AdamTensor* tensors, const int2* blocks,
+                      int num_blocks, int chunk, float lr, float beta1, float beta2, float eps, float weight_decay,
+                      float bias1, float bias2, const float* grad_scale, cudaStream_t stream);
+cudaError_t grad_sqnorm(DType grad_type, const AdamTensor* tensors, const int2* blocks, int num_blocks, int chunk,
+                        float* out_accum, cudaStream_t stream);
+cudaError_t clip_coeff(const float* sqnorm, float max_norm, float extra_scale, float* out, cudaStream_t stream);
+
 // ---- grouped GEMM ---------------------------------------------------------------
 namespace gemm {
 

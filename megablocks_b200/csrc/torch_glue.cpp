@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include <algorithm>
+#include <atomic>
 #include <vector>
 
 #include "kernels.h"
@@ -20,6 +21,10 @@ cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 #define MB_CHECK_CUDA(t) TORCH_CHECK((t).is_cuda(), #t " must be a CUDA tensor")
 #define MB_CHECK_CONTIG(t) TORCH_CHECK((t).is_contiguous(), #t " must be contiguous")
 #define MB_CUDA_OK(expr) C10_CUDA_CHECK(expr)
+
+// Number of kernels of this extension enqueued so far by this process.
+std::atomic<int64_t> g_launches{0};
+#define MB_LAUNCHED(n) g_launches.fetch_add((n), std::memory_order_relaxed)
 
 int sm_count() {
   return at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
@@ -87,6 +92,7 @@ at::Tensor build_inverse(const at::Tensor& indices, const at::Tensor& bins, cons
   if (n == 0) return inverse;
   MB_CUDA_OK(inverse_map(indices.data_ptr<int>(), bins.data_ptr<int>(), padded_bins.data_ptr<int>(),
                          int(bins.numel()), n, capacity, inverse.data_ptr<int>(), stream()));
+  MB_LAUNCHED(1);
   return inverse;
 }
 
@@ -121,6 +127,7 @@ std::vector<at::Tensor> sort_pairs(const at::Tensor& x, int64_t end_bit) {
     MB_CUDA_OK(sort_pass(code, src_k, src_v, n, shift, bits, flip, s.chunk, s.num_chunks,
                          s.partial.data_ptr<int>(), s.totals.data_ptr<int>(), dst_k[which], dst_v[which], nullptr,
                          nullptr, nullptr, 0, 1, stream()));
+    MB_LAUNCHED(3);
     src_k = dst_k[which];
     src_v = dst_v[which];
     which ^= 1;
@@ -148,6 +155,7 @@ std::vector<at::Tensor> route_plan(const at::Tensor& top_experts, int64_t num_ex
                          s.partial.data_ptr<int>(), s.totals.data_ptr<int>(), bin_ids.data_ptr(),
                          indices.data_ptr(), tpe.data_ptr<int>(), bins.data_ptr<int>(),
                          padded_bins.data_ptr<int>(), int(num_experts), int(block), stream()));
+    MB_LAUNCHED(3);
     return {indices, bin_ids, bins, padded_bins, tpe};
   }
   // More than 1024 experts: generic multi-pass sort, then histogram and scans.
@@ -169,6 +177,7 @@ at::Tensor histogram_op(const at::Tensor& x, int64_t num_bins) {
   if (n == 0 || batch == 0) return out;
   MB_CUDA_OK(histogram(int_code(x.scalar_type()), x.data_ptr(), batch, n, int(num_bins), out.data_ptr<int>(),
                        sm_count(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -180,6 +189,7 @@ at::Tensor cumsum_op(const at::Tensor& x, bool exclusive) {
   if (x.numel() == 0) return out;
   MB_CUDA_OK(cumsum(int_code(x.scalar_type()), x.data_ptr(), out.data_ptr(), x.size(0), x.size(1), exclusive,
                     stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -190,6 +200,7 @@ at::Tensor topology_op(const at::Tensor& padded_bins, int64_t block_size, int64_
   if (out.numel() == 0) return out;
   MB_CUDA_OK(topology(padded_bins.data_ptr<int>(), int(padded_bins.numel()), int(block_size), int(rows), int(cols),
                       out.data_ptr<int16_t>(), sm_count(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -202,6 +213,7 @@ at::Tensor replicate_forward(const at::Tensor& x, const at::Tensor& bins, int64_
   if (out.numel() == 0) return out;
   MB_CUDA_OK(replicate_fwd(int(x.element_size()), x.data_ptr(), bins.data_ptr<int>(), int(bins.numel()), x.size(0),
                            num_outputs, out.data_ptr(), sm_count(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -214,6 +226,7 @@ at::Tensor replicate_backward(const at::Tensor& grad, const at::Tensor& bins) {
   if (out.numel() == 0) return out;
   MB_CUDA_OK(replicate_bwd(float_code(grad.scalar_type()), grad.data_ptr(), bins.data_ptr<int>(), num_bins,
                            grad.size(0), grad.size(1), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -234,6 +247,7 @@ at::Tensor gather_rows_op(const at::Tensor& x, const at::Tensor& indices, const 
   MB_CUDA_OK(gather_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
                          bins.data_ptr<int>(), padded_bins.data_ptr<int>(), int(bins.numel()), int(top_k), out_rows,
                          int(x.size(1)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -251,6 +265,7 @@ at::Tensor scatter_rows_op(const at::Tensor& x, const at::Tensor& indices, const
   at::Tensor inverse = build_inverse(indices, bins, padded_bins, -1);
   MB_CUDA_OK(combine_rows(float_code(x.scalar_type()), x.data_ptr(), inverse.data_ptr<int>(), opt_ptr(weights),
                           int(top_k), tokens, int(x.size(1)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -268,6 +283,7 @@ at::Tensor scatter_wgrad_op(const at::Tensor& x, const at::Tensor& grad, const a
   at::Tensor inverse = build_inverse(indices, bins, padded_bins, -1);
   MB_CUDA_OK(scatter_wgrad(float_code(x.scalar_type()), x.data_ptr(), grad.data_ptr(), inverse.data_ptr<int>(),
                            int(top_k), copies, int(x.size(1)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -287,6 +303,7 @@ at::Tensor binned_gather_rows(const at::Tensor& x, const at::Tensor& indices,
   MB_CUDA_OK(gather_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
                          bins.data_ptr<int>(), uniform.data_ptr<int>(), int(experts), int(top_k),
                          experts * capacity, int(x.size(1)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -303,6 +320,7 @@ at::Tensor binned_scatter_rows(const at::Tensor& x, const at::Tensor& indices,
   at::Tensor inverse = build_inverse(indices, bins, bins, int(x.size(1)));
   MB_CUDA_OK(combine_rows(float_code(x.scalar_type()), x.data_ptr(), inverse.data_ptr<int>(), opt_ptr(weights),
                           int(top_k), tokens, int(x.size(2)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -319,6 +337,7 @@ at::Tensor binned_scatter_wgrad(const at::Tensor& x, const at::Tensor& grad, con
   at::Tensor inverse = build_inverse(indices, bins, bins, int(x.size(1)));
   MB_CUDA_OK(scatter_wgrad(float_code(x.scalar_type()), x.data_ptr(), grad.data_ptr(), inverse.data_ptr<int>(),
                            int(top_k), copies, int(x.size(2)), out.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return out;
 }
 
@@ -339,6 +358,7 @@ std::vector<at::Tensor> router_topk_forward(const at::Tensor& logits, int64_t to
   MB_CUDA_OK(router_topk_fwd(float_code(logits.scalar_type()), logits.data_ptr(), tokens, int(num_experts),
                              int(top_k), float(norm_p), scores.data_ptr(), weights.data_ptr(),
                              experts.data_ptr<int64_t>(), stream()));
+  MB_LAUNCHED(1);
   return {scores, weights, experts};
 }
 
@@ -356,6 +376,7 @@ at::Tensor router_topk_backward(const at::Tensor& scores, const at::Tensor& weig
   MB_CUDA_OK(router_topk_bwd(float_code(scores.scalar_type()), scores.data_ptr(), experts.data_ptr<int64_t>(),
                              dscores.data_ptr(), dweights.data_ptr(), tokens, int(num_experts), int(top_k),
                              float(norm_p), dlogits.data_ptr(), stream()));
+  MB_LAUNCHED(1);
   return dlogits;
 }
 
@@ -506,8 +527,73 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   const int grid = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count())));
   MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, grid, stream()));
+  MB_LAUNCHED(1);
   return {c, out2, out3};
 }
+
+// ---------------------------------------------------------------------------
+// optimizer
+// ---------------------------------------------------------------------------
+namespace {
+
+const AdamTensor* table_ptr(const at::Tensor& table) {
+  TORCH_CHECK(table.is_cuda() && table.is_contiguous() && table.scalar_type() == at::kByte &&
+                  table.numel() % sizeof(AdamTensor) == 0,
+              "tensor table must be a contiguous CUDA uint8 tensor of AdamTensor records");
+  return reinterpret_cast<const AdamTensor*>(table.data_ptr());
+}
+
+const int2* blocks_ptr(const at::Tensor& blocks) {
+  TORCH_CHECK(blocks.is_cuda() && blocks.is_contiguous() && blocks.scalar_type() == at::kInt && blocks.dim() == 2 &&
+                  blocks.size(1) == 2,
+              "block table must be a contiguous CUDA int32 [n, 2] tensor");
+  return reinterpret_cast<const int2*>(blocks.data_ptr());
+}
+
+DType code_of(int64_t code) {
+  TORCH_CHECK(code >= kF32 && code <= kBF16, "bad dtype code");
+  return static_cast<DType>(code);
+}
+
+}  // namespace
+
+int64_t adam_record_size() { return sizeof(AdamTensor); }
+
+void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t param_code,
+                  int64_t grad_code, double lr, double beta1, double beta2, double eps, double weight_decay,
+                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale) {
+  c10::cuda::CUDAGuard guard(table.device());
+  const float* scale = nullptr;
+  if (grad_scale.has_value()) {
+    TORCH_CHECK(grad_scale->is_cuda() && grad_scale->scalar_type() == at::kFloat, "grad_scale must be CUDA float32");
+    scale = grad_scale->data_ptr<float>();
+  }
+  MB_CUDA_OK(adam_step(code_of(param_code), code_of(grad_code), table_ptr(table), blocks_ptr(blocks),
+                       int(blocks.size(0)), int(chunk), float(lr), float(beta1), float(beta2), float(eps),
+                       float(weight_decay), float(bias1), float(bias2), scale, stream()));
+  MB_LAUNCHED(1);
+}
+
+void grad_sqnorm_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t grad_code,
+                    at::Tensor out_accum) {
+  c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(out_accum.is_cuda() && out_accum.scalar_type() == at::kFloat, "accumulator must be CUDA float32");
+  MB_CUDA_OK(grad_sqnorm(code_of(grad_code), table_ptr(table), blocks_ptr(blocks), int(blocks.size(0)), int(chunk),
+                         out_accum.data_ptr<float>(), stream()));
+  MB_LAUNCHED(1);
+}
+
+void clip_coeff_op(const at::Tensor& sqnorm, double max_norm, double extra_scale, at::Tensor out) {
+  c10::cuda::CUDAGuard guard(sqnorm.device());
+  TORCH_CHECK(sqnorm.is_cuda() && sqnorm.scalar_type() == at::kFloat && out.is_cuda() &&
+                  out.scalar_type() == at::kFloat && out.numel() >= 2,
+              "clip_coeff expects CUDA float32 tensors (out with >= 2 elements)");
+  MB_CUDA_OK(clip_coeff(sqnorm.data_ptr<float>(), float(max_norm), float(extra_scale), out.data_ptr<float>(),
+                        stream()));
+  MB_LAUNCHED(1);
+}
+
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 // Reads (and optionally clears) the status word of the current device; nonzero means
 // a kernel abandoned a wait.  Synchronises the device.

@@ -1,0 +1,181 @@
+"""Fused Adam(W) with fp32 master weights for 16-bit parameters.
+
+The model computes with bf16/fp16 parameters; the optimizer keeps an fp32 copy
+and the two Adam moments in flat buffers and updates everything - moments,
+master weights and the 16-bit shadow - in ONE kernel launch per parameter
+group (``csrc/optim.cu``), reading the gradient-clipping coefficient from
+device memory so a step never synchronises with the host.  On CPU tensors the
+same arithmetic runs in PyTorch (used by the CPU tests and as the oracle).
+
+This is the optimizer the reference delegates to Megatron-LM (bf16 parameters,
+fp32 main copies, Adam, ``--clip-grad 1.0``: exp/dmoe/dmoe_125m_8gpu.sh:65-72,144).
+"""
+
+import math
+from typing import Iterable, List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from megablocks_b200._ext import ext
+
+_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+_RECORD = np.dtype([('param', '<u8'), ('grad', '<u8'), ('master', '<u8'), ('exp_avg', '<u8'), ('exp_avg_sq', '<u8'),
+                    ('numel', '<i8'), ('norm_weight', '<f4'), ('pad', '<i4')])
+_CHUNK = 65536
+
+
+def _align(n: int, to: int = 8) -> int:
+    return (n + to - 1) // to * to
+
+
+class FusedAdam:
+    """Adam / AdamW over a list of tensors with flat fp32 state.
+
+    ``params`` are the tensors the model uses (any float dtype); ``grads_of``
+    returns the matching gradient tensors at step time (default: ``p.grad``).
+    ``norm_weights`` weights each tensor's contribution to the global gradient
+    norm (e.g. ``1/replicas`` for tensors replicated over a group whose squared
+    norms are summed).
+    """
+
+    def __init__(self, params: Iterable[torch.Tensor], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, norm_weights: Optional[Sequence[float]] = None):
+        self.params: List[torch.Tensor] = [p for p in params]
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.step_count = 0
+        self.norm_weights = list(norm_weights) if norm_weights is not None else [1.0] * len(self.params)
+        if not self.params:
+            self.device = torch.device('cpu')
+            return
+        self.device = self.params[0].device
+        self.dtype = self.params[0].dtype
+        assert all(p.device == self.device and p.dtype == self.dtype for p in self.params)
+        offsets, total = [], 0
+        for p in self.params:
+            offsets.append(total)
+            total += _align(p.numel())
+        self.offsets = offsets
+        self.master = torch.zeros(total, dtype=torch.float32, device=self.device)
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        for p, off in zip(self.params, offsets):
+            self.master[off:off + p.numel()].copy_(p.detach().reshape(-1))
+        if self.device.type == 'cuda':
+            self._init_tables()
+
+    # -- tables (CUDA) ----------------------------------------------------------
+    def _init_tables(self):
+        assert ext().adam_record_size() == _RECORD.itemsize
+        rec = np.zeros(len(self.params), dtype=_RECORD)
+        blocks = []
+        for i, (p, off) in enumerate(zip(self.params, self.offsets)):
+            rec[i]['param'] = p.data_ptr()
+            rec[i]['master'] = self.master.data_ptr() + 4 * off
+            rec[i]['exp_avg'] = self.exp_avg.data_ptr() + 4 * off
+            rec[i]['exp_avg_sq'] = self.exp_avg_sq.data_ptr() + 4 * off
+            rec[i]['numel'] = p.numel()
+            rec[i]['norm_weight'] = self.norm_weights[i]
+            for c in range((p.numel() + _CHUNK - 1) // _CHUNK):
+                blocks.append((i, c))
+        self._records = rec
+        self._blocks = torch.tensor(blocks, dtype=torch.int32).reshape(-1, 2).to(self.device)
+        self._host_ring = [torch.empty(rec.nbytes, dtype=torch.uint8).pin_memory() for _ in range(4)]
+        self._table = torch.empty(rec.nbytes, dtype=torch.uint8, device=self.device)
+        self._ring_pos = 0
+
+    def _upload_table(self, grads: Sequence[torch.Tensor]):
+        rec = self._records
+        for i, (p, g) in enumerate(zip(self.params, grads)):
+            assert g.is_contiguous() and g.numel() == p.numel()
+            rec[i]['grad'] = g.data_ptr()
+            rec[i]['param'] = p.data_ptr()
+        host = self._host_ring[self._ring_pos]
+        self._ring_pos = (self._ring_pos + 1) % len(self._host_ring)
+        host.numpy()[:] = rec.view(np.uint8).reshape(-1)
+        self._table.copy_(host, non_blocking=True)
+
+    # -- public -------------------------------------------------------------------
+    def grads(self) -> List[torch.Tensor]:
+        out = []
+        for p in self.params:
+            if p.grad is None:
+                raise RuntimeError('FusedAdam.step: a parameter has no gradient')
+            out.append(p.grad)
+        return out
+
+    def add_sqnorm(self, accum: torch.Tensor, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        """Add this group's weighted squared gradient norm to the fp32 scalar tensor ``accum[0]``."""
+        if not self.params:
+            return
+        grads = self.grads() if grads is None else grads
+        if self.device.type == 'cuda':
+            self._upload_table(grads)
+            ext().grad_sqnorm(self._table, self._blocks, _CHUNK, _CODES[grads[0].dtype], accum)
+            self._table_fresh = True
+        else:
+            for g, w in zip(grads, self.norm_weights):
+                accum[0] += w * g.float().square().sum()
+
+    def step(self, grad_scale: Optional[torch.Tensor] = None, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        """One update.  ``grad_scale`` is an optional fp32 device scalar multiplied into every gradient."""
+        if not self.params:
+            return
+        grads = self.grads() if grads is None else grads
+        self.step_count += 1
+        b1, b2 = self.betas
+        bias1 = 1.0 - b1**self.step_count
+        bias2 = 1.0 - b2**self.step_count
+        if self.device.type == 'cuda':
+            if not getattr(self, '_table_fresh', False):
+                self._upload_table(grads)
+            self._table_fresh = False
+            ext().adam_step(self._table, self._blocks, _CHUNK, _CODES[self.dtype], _CODES[grads[0].dtype], self.lr, b1,
+                            b2, self.eps, self.weight_decay, bias1, bias2, grad_scale)
+            return
+        scale = float(grad_scale[0]) if grad_scale is not None else 1.0
+        for p, g, off in zip(self.params, grads, self.offsets):
+            n = p.numel()
+            w, m, v = (t[off:off + n] for t in (self.master, self.exp_avg, self.exp_avg_sq))
+            gf = g.detach().reshape(-1).float() * scale
+            m.mul_(b1).add_(gf, alpha=1 - b1)
+            v.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+            denom = (v / bias2).sqrt_().add_(self.eps)
+            w.sub_(self.lr * ((m / bias1) / denom + self.weight_decay * w))
+            p.data.copy_(w.view_as(p))
+
+    def state_dict(self):
+        return {'step': self.step_count, 'master': self.master, 'exp_avg': self.exp_avg,
+                'exp_avg_sq': self.exp_avg_sq, 'lr': self.lr}
+
+    def load_state_dict(self, state):
+        self.step_count = int(state['step'])
+        self.lr = state.get('lr', self.lr)
+        for name in ('master', 'exp_avg', 'exp_avg_sq'):
+            getattr(self, name).copy_(state[name])
+        for p, off in zip(self.params, self.offsets):
+            p.data.copy_(self.master[off:off + p.numel()].view_as(p))
+
+
+def clip_coefficient(sqnorm: torch.Tensor, max_norm: float, extra_scale: float = 1.0) -> torch.Tensor:
+    """``[coeff, norm]`` on the device of ``sqnorm``: ``coeff = min(1, max_norm / norm) * extra_scale``."""
+    out = torch.empty(2, dtype=torch.float32, device=sqnorm.device)
+    if sqnorm.is_cuda:
+        ext().clip_coeff(sqnorm, float(max_norm), float(extra_scale), out)
+        return out
+    norm = float(sqnorm[0].sqrt())
+    coeff = min(1.0, max_norm / (norm + 1e-6)) if max_norm > 0 else 1.0
+    if not math.isfinite(norm):
+        coeff = 0.0
+    out[0], out[1] = coeff * extra_scale, norm
+    return out
+
+
+def cosine_lr(step: int, total_steps: int, peak: float, floor: float, warmup_fraction: float = 0.01) -> float:
+    """Linear warm-up then cosine decay (the schedule of the reference's experiment scripts)."""
+    warm = max(1, int(total_steps * warmup_fraction))
+    if step < warm:
+        return peak * (step + 1) / warm
+    frac = min(1.0, (step - warm) / max(1, total_steps - warm))
+    return floor + 0.5 * (peak - floor) * (1.0 + math.cos(math.pi * frac))

@@ -1,0 +1,170 @@
+"""Data-parallel gradient reduction overlapped with backward, and ZeRO-1 sharding.
+
+The reference leaves data parallelism to its outer trainer (Megatron-LM
+``--DDP-impl local``, exp/dmoe/dmoe_125m_8gpu.sh:145) and only tags expert
+weights with ``expert_model_parallel`` so that trainer can skip them
+(megablocks/layers/mpu.py:31-52).  This module is the native counterpart:
+
+* :class:`FlatBuffer` re-homes the replicated ("dense") parameters and their
+  gradients in two contiguous buffers, laid out in reverse registration order
+  so the gradients that backward produces first sit at the front;
+* :class:`GradReducer` cuts the buffer into buckets and, from autograd's
+  post-accumulate hooks, launches each bucket's collective on a side stream the
+  moment its last gradient lands - all-reduce (plain DP) or reduce-scatter
+  (ZeRO-1: every rank then owns one slice of every bucket);
+* with ZeRO-1 the optimizer updates only the owned slices and the updated
+  parameters are all-gathered bucket by bucket.
+
+Buckets are sized for launch latency and overlap (NVSwitch gives every pair of
+GPUs full bandwidth, so there is no per-link reason to make them large).
+"""
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def _align(n: int, to: int) -> int:
+    return (n + to - 1) // to * to
+
+
+class FlatBuffer:
+    """Contiguous parameter and gradient storage for a list of same-dtype parameters."""
+
+    def __init__(self, params: Sequence[torch.nn.Parameter], granule: int = 8):
+        self.params = list(reversed(list(params)))   # backward order
+        assert self.params, 'FlatBuffer needs at least one parameter'
+        dtype, device = self.params[0].dtype, self.params[0].device
+        self.offsets, total = [], 0
+        for p in self.params:
+            assert p.dtype == dtype and p.device == device
+            self.offsets.append(total)
+            total += _align(p.numel(), 8)
+        self.numel = _align(total, granule)
+        self.param = torch.zeros(self.numel, dtype=dtype, device=device)
+        self.grad = torch.zeros(self.numel, dtype=dtype, device=device)
+        for p, off in zip(self.params, self.offsets):
+            view = self.param[off:off + p.numel()].view_as(p)
+            view.copy_(p.data)
+            p.data = view
+            p.grad = self.grad[off:off + p.numel()].view_as(p)
+
+    def zero_grad(self) -> None:
+        self.grad.zero_()
+        for p, off in zip(self.params, self.offsets):   # re-attach in case something dropped the view
+            if p.grad is None or p.grad.data_ptr() != self.grad.data_ptr() + off * self.grad.element_size():
+                p.grad = self.grad[off:off + p.numel()].view_as(p)
+
+
+class GradReducer:
+    """Bucketed gradient collective launched from backward hooks on a side stream."""
+
+    def __init__(self, flat: FlatBuffer, group: Optional[dist.ProcessGroup], bucket_bytes: int = 32 << 20,
+                 shard: bool = False):
+        self.flat, self.group, self.shard = flat, group, shard
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        elem = flat.grad.element_size()
+        granule = self.world * 8
+        target = max(granule, _align(bucket_bytes // elem, granule))
+        # Bucket boundaries fall on parameter boundaries (a hook fires per parameter).
+        self.buckets: List[List[int]] = []   # [start, end, first param idx, last param idx + 1]
+        start, first = 0, 0
+        for i, (p, off) in enumerate(zip(flat.params, flat.offsets)):
+            end = off + _align(p.numel(), 8)
+            last = i == len(flat.params) - 1
+            if end - start >= target or last:
+                end = flat.numel if last else end
+                self.buckets.append([start, end, first, i + 1])
+                start, first = end, i + 1
+        if shard:
+            for b in self.buckets:
+                assert (b[1] - b[0]) % granule == 0 or b is self.buckets[-1]
+            assert flat.numel % granule == 0
+        self._bucket_of = {}
+        for bi, (_, _, lo, hi) in enumerate(self.buckets):
+            for i in range(lo, hi):
+                self._bucket_of[i] = bi
+        self._pending = [hi - lo for (_, _, lo, hi) in self.buckets]
+        self._remaining = list(self._pending)
+        self._launched = [False] * len(self.buckets)
+        self._stream = torch.cuda.Stream() if flat.grad.is_cuda else None
+        self._works = []
+        for i, p in enumerate(flat.params):
+            p.register_post_accumulate_grad_hook(self._make_hook(i))
+
+    # -- shard geometry (ZeRO-1) --------------------------------------------------
+    def shard_range(self, bucket: int):
+        s, e = self.buckets[bucket][:2]
+        n = (e - s) // self.world
+        return s + self.rank * n, s + (self.rank + 1) * n
+
+    def _make_hook(self, index: int):
+        def hook(_param):
+            bi = self._bucket_of[index]
+            self._remaining[bi] -= 1
+            if self._remaining[bi] == 0:
+                self._launch(bi)
+        return hook
+
+    def _launch(self, bi: int) -> None:
+        if self._launched[bi]:
+            return
+        self._launched[bi] = True
+        s, e = self.buckets[bi][:2]
+        grad = self.flat.grad[s:e]
+        if self._stream is not None:
+            self._stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(self._stream)
+        else:
+            ctx = _NullContext()
+        with ctx:
+            if self.shard:
+                lo, hi = self.shard_range(bi)
+                out = self.flat.grad[lo:hi]
+                work = dist.reduce_scatter_tensor(out, grad, op=_avg_op(grad), group=self.group, async_op=True)
+            else:
+                work = dist.all_reduce(grad, op=_avg_op(grad), group=self.group, async_op=True)
+            self._works.append((work, grad))
+            if not _has_avg(grad):
+                # gloo has no AVG: divide after the sum completes.
+                work.wait()
+                (self.flat.grad[self.shard_range(bi)[0]:self.shard_range(bi)[1]] if self.shard else grad).div_(
+                    self.world)
+
+    def finish(self) -> None:
+        """Launch whatever backward did not trigger, then make the current stream wait for all buckets."""
+        for bi in range(len(self.buckets)):
+            self._launch(bi)
+        for work, _ in self._works:
+            work.wait()
+        if self._stream is not None:
+            torch.cuda.current_stream().wait_stream(self._stream)
+        self._works.clear()
+        self._remaining = list(self._pending)
+        self._launched = [False] * len(self.buckets)
+
+    def gather_params(self) -> None:
+        """ZeRO-1: all-gather the updated parameter slices of every bucket."""
+        assert self.shard
+        for bi, (s, e, _, _) in enumerate(self.buckets):
+            lo, hi = self.shard_range(bi)
+            dist.all_gather_into_tensor(self.flat.param[s:e], self.flat.param[lo:hi].clone(), group=self.group)
+
+
+def _has_avg(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def _avg_op(t: torch.Tensor):
+    return dist.ReduceOp.AVG if _has_avg(t) else dist.ReduceOp.SUM
+
+
+class _NullContext:
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

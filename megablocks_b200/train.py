@@ -1,0 +1,143 @@
+"""Stand-alone trainer for the dMoE transformer family.
+
+Takes the place of the Megatron-LM fork the reference's experiment scripts
+launch (exp/dmoe/dmoe_125m_8gpu.sh:159-167): bf16 parameters with fp32 master
+weights, Adam, gradient clipping, cosine schedule, expert parallelism over the
+whole job with the non-expert parameters data-parallel (gradient reduction
+overlapped with backward, optionally ZeRO-1 sharded), synthetic or
+caller-supplied token batches.
+
+    trainer = Trainer(model, TrainerConfig(lr=6e-4), dp_group=group)
+    loss = trainer.step(tokens, targets)            # device tensors
+    loss = trainer.step_from_host(batch_cpu)        # pinned host tokens -> float
+
+One process drives one GPU; ``torch.distributed`` (NCCL) connects them.
+"""
+
+import dataclasses
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from megablocks_b200.layers import mpu
+from megablocks_b200.optim import FusedAdam, clip_coefficient, cosine_lr
+from megablocks_b200.parallel.dp import FlatBuffer, GradReducer
+
+
+@dataclasses.dataclass
+class TrainerConfig:
+    lr: float = 6e-4
+    min_lr: float = 6e-5
+    betas: tuple = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    max_grad_norm: float = 1.0
+    total_steps: int = 20000
+    warmup_fraction: float = 0.01
+    zero1: bool = False              # shard optimizer state of the replicated parameters
+    bucket_mb: int = 32
+    schedule: bool = True
+
+
+class Trainer:
+
+    def __init__(self, model: torch.nn.Module, cfg: TrainerConfig, dp_group: Optional[dist.ProcessGroup] = None):
+        self.model, self.cfg, self.dp_group = model, cfg, dp_group
+        self.world = dist.get_world_size(dp_group) if (dist.is_initialized() and dp_group is not None) else 1
+        params = [p for p in model.parameters() if p.requires_grad]
+        self.expert_params = [p for p in params if mpu.param_is_expert_model_parallel(p)]
+        self.dense_params = [p for p in params if not mpu.param_is_expert_model_parallel(p)]
+        self.device = params[0].device
+        self.flat = self.reducer = None
+        kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
+        if self.world > 1:
+            self.flat = FlatBuffer(self.dense_params, granule=self.world * 8)
+            self.reducer = GradReducer(self.flat, dp_group, cfg.bucket_mb << 20, shard=cfg.zero1)
+        if self.world > 1 and cfg.zero1:
+            # One optimizer "tensor" per owned bucket slice; disjoint across ranks.
+            self._shard_params, self._shard_grads = [], []
+            for bi in range(len(self.reducer.buckets)):
+                lo, hi = self.reducer.shard_range(bi)
+                self._shard_params.append(self.flat.param[lo:hi])
+                self._shard_grads.append(self.flat.grad[lo:hi])
+            self.dense_opt = FusedAdam(self._shard_params, **kw)
+        else:
+            # Replicated tensors: count their norm once across the group.
+            self.dense_opt = FusedAdam(self.dense_params, norm_weights=[1.0 / self.world] * len(self.dense_params),
+                                       **kw)
+        self.expert_opt = FusedAdam(self.expert_params, **kw)
+        self._sqnorm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.step_count = 0
+        self.last_grad_norm = None
+        self._h2d = None
+
+    # -- one optimisation step ---------------------------------------------------------
+    def _zero_grad(self):
+        if self.flat is not None:
+            self.flat.zero_grad()
+        else:
+            for p in self.dense_params:
+                p.grad = None
+        for p in self.expert_params:
+            p.grad = None
+
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Forward, backward, gradient reduction, clipping and the optimizer update.
+
+        Returns the language-model loss as a device scalar (no host sync).
+        """
+        cfg = self.cfg
+        self.model.train()
+        self._zero_grad()
+        total, lm = self.model.loss(tokens, targets)
+        total.backward()
+        if self.reducer is not None:
+            self.reducer.finish()
+        lr = cosine_lr(self.step_count, cfg.total_steps, cfg.lr, cfg.min_lr, cfg.warmup_fraction) if cfg.schedule \
+            else cfg.lr
+        self.dense_opt.lr = self.expert_opt.lr = lr
+
+        dense_grads = self._shard_grads if (self.world > 1 and cfg.zero1) else None
+        self._sqnorm.zero_()
+        self.dense_opt.add_sqnorm(self._sqnorm, dense_grads)
+        self.expert_opt.add_sqnorm(self._sqnorm)
+        if self.world > 1:
+            dist.all_reduce(self._sqnorm, group=self.dp_group)
+        coeff = clip_coefficient(self._sqnorm, cfg.max_grad_norm)
+        self.last_grad_norm = coeff[1:2]
+        self.dense_opt.step(coeff[0:1], dense_grads)
+        self.expert_opt.step(coeff[0:1])
+        if self.world > 1 and cfg.zero1:
+            self.reducer.gather_params()
+        self.step_count += 1
+        return lm
+
+    # -- end-to-end step from host memory ---------------------------------------------
+    def step_from_host(self, batch: torch.Tensor) -> float:
+        """``batch`` is a pinned int64 host tensor ``[micro_batch, seq + 1]``.
+
+        Copies it to the device, trains one step on (batch[:, :-1] -> batch[:, 1:])
+        and reads the loss back to the host.
+        """
+        dev = batch.to(self.device, non_blocking=True)
+        loss = self.step(dev[:, :-1], dev[:, 1:])
+        return float(loss.item())
+
+    def state_dict(self):
+        return {'model': self.model.state_dict(), 'dense_opt': self.dense_opt.state_dict(),
+                'expert_opt': self.expert_opt.state_dict(), 'step': self.step_count}
+
+    def load_state_dict(self, state):
+        self.model.load_state_dict(state['model'])
+        self.dense_opt.load_state_dict(state['dense_opt'])
+        self.expert_opt.load_state_dict(state['expert_opt'])
+        self.step_count = int(state['step'])
+
+
+def synthetic_batch(micro_batch: int, seq_len: int, vocab_size: int, generator: Optional[torch.Generator] = None,
+                    pin: bool = True) -> torch.Tensor:
+    """Uniform-random token ids ``[micro_batch, seq_len + 1]`` in (pinned) host memory."""
+    batch = torch.randint(0, vocab_size, (micro_batch, seq_len + 1), generator=generator, dtype=torch.int64)
+    return batch.pin_memory() if pin and torch.cuda.is_available() else batch
