@@ -142,7 +142,8 @@ class RefTrainer:
         coeff = torch.clamp(1.0 / (sq.sqrt() + 1e-6), max=1.0)
         torch._foreach_mul_([m.grad for m in self.main], coeff)
         self.opt.step()
-        torch._foreach_copy_(self.params, self.main)
+        with torch.no_grad():
+            torch._foreach_copy_(self.params, self.main)
         return lm
 
     def step_from_host(self, batch):
