@@ -45,9 +45,31 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool trans_b, int64_t epilogue, int64_t act,
                                      const c10::optional<at::Tensor>& aux1, const c10::optional<at::Tensor>& aux2,
                                      bool want_out2, bool want_out3, int64_t num_groups,
-                                     const c10::optional<at::Tensor>& c_in);
+                                     const c10::optional<at::Tensor>& c_in, bool zero_tail,
+                                     const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
+                                     int64_t wait_stride, int64_t wait_seq);
 int64_t read_status(bool clear);
 int64_t launch_count();
+
+// torch_glue.cpp: symmetric heap and expert-parallel exchange
+std::vector<at::Tensor> symm_alloc(int64_t nbytes);
+int64_t symm_open(const at::Tensor& handle);
+void symm_close(int64_t ptr);
+void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
+                           int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
+                           int64_t off_count_flags, int64_t seq, at::Tensor counts_out, at::Tensor recv_bins,
+                           at::Tensor scratch);
+void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
+                     const at::Tensor& bins, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+                     int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
+                     int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
+                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done);
+void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+                       int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
+                       int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
+                       int64_t off_flags, int64_t seq, at::Tensor done);
+void ep_set_flag_op(at::Tensor flag, int64_t value);
+void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code);
 
 // torch_glue.cpp: optimizer
 int64_t adam_record_size();
@@ -81,6 +103,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &mb::grouped_gemm);
   m.def("read_status", &mb::read_status);
   m.def("launch_count", &mb::launch_count);
+  m.def("symm_alloc", &mb::symm_alloc);
+  m.def("symm_open", &mb::symm_open);
+  m.def("symm_close", &mb::symm_close);
+  m.def("ep_exchange_counts", &mb::ep_exchange_counts_op);
+  m.def("ep_push_rows", &mb::ep_push_rows_op);
+  m.def("ep_return_rows", &mb::ep_return_rows_op);
+  m.def("ep_wait_flags", &mb::ep_wait_flags_op);
+  m.def("ep_set_flag", &mb::ep_set_flag_op);
   m.def("adam_record_size", &mb::adam_record_size);
   m.def("adam_step", &mb::adam_step_op);
   m.def("grad_sqnorm", &mb::grad_sqnorm_op);

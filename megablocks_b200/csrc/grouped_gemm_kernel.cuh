@@ -48,7 +48,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 
 // Status codes written on an abandoned wait.
-constexpr int kErrProducer = 1, kErrMmaFull = 2, kErrMmaTmem = 3, kErrEpilogue = 4;
+constexpr int kErrProducer = 1, kErrMmaFull = 2, kErrMmaTmem = 3, kErrEpilogue = 4, kErrPeerRows = 18;
 
 template <int BLOCK_N>
 struct Config {
@@ -320,9 +320,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int arrived_group = -1;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const Tile tile = decode(t);
         const int num_kb = (tile.k_len + kBlockK - 1) / kBlockK;
+        if (LAYOUT != kTN && p.wait_flags != nullptr && tile.group != arrived_group) {
+          // Rows of this group are stored by peer GPUs; each source releases one flag
+          // per group when its last row has landed.
+          for (int s = 0; s < p.wait_count && ok; ++s) {
+            const int* flag = p.wait_flags + s * p.wait_stride + tile.group;
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys_s32(flag) < p.wait_seq) {
+              if ((++spins & 63u) == 0u) {
+                if (*abort_flag != 0) { ok = false; break; }
+                if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                  *abort_flag = 1;
+                  atomicCAS(p.status, 0, kErrPeerRows);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+          }
+          if (!ok) break;
+          arrived_group = tile.group;
+          fence_proxy_async_all();   // the acquire above must precede the TMA (async proxy) reads
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, kErrProducer, kWaitLimitNs);
           if (!ok) break;
@@ -457,7 +481,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
     }
     // Rows past the last group belong to nobody: defined as zero (NT / NN only).
-    if constexpr (LAYOUT != kTN) {
+    if (LAYOUT != kTN && p.zero_tail) {
       const int last = G > 0 ? s_row_end[G - 1] : 0;
       const int64_t begin = int64_t(last) * p.N, end = int64_t(p.rows_total) * p.N;
       const int64_t tid = int64_t(blockIdx.x) * 128 + (threadIdx.x - 64);

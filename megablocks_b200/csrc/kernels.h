@@ -78,6 +78,37 @@ cudaError_t grad_sqnorm(DType grad_type, const AdamTensor* tensors, const int2* 
                         float* out_accum, cudaStream_t stream);
 cudaError_t clip_coeff(const float* sqnorm, float max_norm, float extra_scale, float* out, cudaStream_t stream);
 
+// ---- ep_comm.cu ---------------------------------------------------------------
+// Geometry of one expert-parallel workspace.  `peer_base[r]` is the address at which
+// rank r's symmetric heap is mapped in this process (device array of `world` entries);
+// offsets are byte offsets inside the heap, identical on every rank.
+struct EpLayout {
+  const uint64_t* peer_base;
+  int world;
+  int rank;
+  int num_experts;
+  int experts_per_rank;
+  int capacity_rows;        // rows the receive buffers can hold
+  int64_t off_counts;       // int32 [2][world][num_experts]
+  int64_t off_count_flags;  // int32 [world]
+};
+constexpr int kEpErrCounts = 16, kEpErrOverflow = 17, kEpErrGemmWait = 18, kEpErrReturnWait = 19,
+              kEpErrBufferBusy = 20;
+
+cudaError_t ep_exchange_counts(const int* tpe, const EpLayout& layout, int seq, int* counts_out, int* recv_bins,
+                               int* scratch_zero, int scratch_ints, int* status, cudaStream_t stream);
+// `data_base[r]` is the mapping of the heap that holds the row buffers (it may differ
+// from the heap of the flags); `off_free < 0` skips the buffer-free handshake.
+cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const void* weights, const int* bins,
+                         const int* counts, const EpLayout& layout, const uint64_t* data_base, int64_t off_recv,
+                         int64_t off_flags, int64_t off_free, int seq, int top_k, int n, int cols, int* done,
+                         int* status, int sms, cudaStream_t stream);
+cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const EpLayout& layout,
+                           const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
+                           int rows_bound, int* done, int sms, cudaStream_t stream);
+cudaError_t ep_set_flag(int* flag, int value, cudaStream_t stream);
+cudaError_t ep_wait_flags(const int* flags, int count, int seq, int* status, int code, cudaStream_t stream);
+
 // ---- grouped GEMM ---------------------------------------------------------------
 namespace gemm {
 
@@ -104,6 +135,14 @@ struct GemmParams {
   int epilogue;
   int act;
   int* status;      // device word that receives a code when a wait is abandoned
+  int zero_tail;    // NT / NN: write zeros to the rows of c past the last group
+  // Optional arrival flags (expert-parallel receive buffer): before the first load of
+  // a tile of group g the producer waits until wait_flags[s * wait_stride + g] >=
+  // wait_seq for every s in [0, wait_count).  Null = no wait.
+  const int* wait_flags;
+  int wait_count;
+  int wait_stride;
+  int wait_seq;
 };
 
 // block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit

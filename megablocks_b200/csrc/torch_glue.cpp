@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstring>
 #include <vector>
 
 #include "kernels.h"
@@ -451,7 +452,9 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool trans_b, int64_t epilogue, int64_t act,
                                      const c10::optional<at::Tensor>& aux1, const c10::optional<at::Tensor>& aux2,
                                      bool want_out2, bool want_out3, int64_t num_groups,
-                                     const c10::optional<at::Tensor>& c_in) {
+                                     const c10::optional<at::Tensor>& c_in, bool zero_tail,
+                                     const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
+                                     int64_t wait_stride, int64_t wait_seq) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -506,6 +509,15 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   p.c = c.data_ptr();
   p.status = status_word(a.device()).data_ptr<int>();
+  p.zero_tail = zero_tail ? 1 : 0;
+  if (wait_flags.has_value()) {
+    TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == at::kInt && layout != kTN,
+                "wait_flags must be a CUDA int32 tensor (NT / NN layouts only)");
+    p.wait_flags = wait_flags->data_ptr<int>();
+    p.wait_count = int(wait_count);
+    p.wait_stride = int(wait_stride);
+    p.wait_seq = int(wait_seq);
+  }
   if (out_numel == 0) return {c, out2, out3};
 
   const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
@@ -590,6 +602,134 @@ void clip_coeff_op(const at::Tensor& sqnorm, double max_norm, double extra_scale
               "clip_coeff expects CUDA float32 tensors (out with >= 2 elements)");
   MB_CUDA_OK(clip_coeff(sqnorm.data_ptr<float>(), float(max_norm), float(extra_scale), out.data_ptr<float>(),
                         stream()));
+  MB_LAUNCHED(1);
+}
+
+// ---------------------------------------------------------------------------
+// symmetric heap (CUDA IPC) and expert-parallel exchange
+// ---------------------------------------------------------------------------
+// Allocates `nbytes` of zeroed device memory that peers can map, and returns it as a
+// uint8 tensor together with its IPC handle (a 64-byte CPU uint8 tensor).  The memory
+// comes straight from cudaMalloc: IPC handles refer to whole allocations, which rules
+// out sub-blocks of the caching allocator.
+std::vector<at::Tensor> symm_alloc(int64_t nbytes) {
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaMalloc(&ptr, static_cast<size_t>(nbytes)));
+  C10_CUDA_CHECK(cudaMemset(ptr, 0, static_cast<size_t>(nbytes)));
+  cudaIpcMemHandle_t handle;
+  C10_CUDA_CHECK(cudaIpcGetMemHandle(&handle, ptr));
+  int dev = 0;
+  C10_CUDA_CHECK(cudaGetDevice(&dev));
+  at::Tensor local = at::from_blob(
+      ptr, {nbytes}, [](void* p) { cudaFree(p); },
+      at::TensorOptions().device(at::Device(at::kCUDA, dev)).dtype(at::kByte));
+  at::Tensor h = at::empty({static_cast<int64_t>(sizeof(handle))}, at::TensorOptions().dtype(at::kByte));
+  std::memcpy(h.data_ptr(), &handle, sizeof(handle));
+  return {local, h};
+}
+
+// Maps a peer's allocation into this process; returns the device address.
+int64_t symm_open(const at::Tensor& handle) {
+  TORCH_CHECK(!handle.is_cuda() && handle.scalar_type() == at::kByte &&
+                  handle.numel() == static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)),
+              "symm_open expects the 64-byte CPU handle produced by symm_alloc");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle.data_ptr(), sizeof(h));
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void symm_close(int64_t ptr) { C10_CUDA_CHECK(cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr))); }
+
+namespace {
+
+EpLayout make_layout(const at::Tensor& peer_base, int64_t world, int64_t rank, int64_t num_experts,
+                     int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts, int64_t off_count_flags) {
+  TORCH_CHECK(peer_base.is_cuda() && peer_base.scalar_type() == at::kLong && peer_base.numel() == world,
+              "peer_base must be a CUDA int64 tensor with one address per rank");
+  EpLayout L;
+  L.peer_base = reinterpret_cast<const uint64_t*>(peer_base.data_ptr<int64_t>());
+  L.world = int(world);
+  L.rank = int(rank);
+  L.num_experts = int(num_experts);
+  L.experts_per_rank = int(experts_per_rank);
+  L.capacity_rows = int(capacity_rows);
+  L.off_counts = off_counts;
+  L.off_count_flags = off_count_flags;
+  return L;
+}
+
+int* status_ptr(const at::Tensor& t) { return status_word(t.device()).data_ptr<int>(); }
+
+}  // namespace
+
+void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
+                           int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
+                           int64_t off_count_flags, int64_t seq, at::Tensor counts_out, at::Tensor recv_bins,
+                           at::Tensor scratch) {
+  check_index(tpe, "tokens_per_expert");
+  c10::cuda::CUDAGuard guard(tpe.device());
+  TORCH_CHECK(counts_out.numel() == world * num_experts && recv_bins.numel() == experts_per_rank &&
+                  counts_out.scalar_type() == at::kInt && recv_bins.scalar_type() == at::kInt &&
+                  scratch.scalar_type() == at::kInt,
+              "bad ep_exchange_counts outputs");
+  const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
+                                 off_count_flags);
+  MB_CUDA_OK(ep_exchange_counts(tpe.data_ptr<int>(), L, int(seq), counts_out.data_ptr<int>(),
+                                recv_bins.data_ptr<int>(), scratch.data_ptr<int>(), int(scratch.numel()),
+                                status_ptr(tpe), stream()));
+  MB_LAUNCHED(1);
+}
+
+void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
+                     const at::Tensor& bins, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+                     int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
+                     int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
+                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  check_index(indices, "indices"); check_index(bins, "bins");
+  check_weights(weights, x, indices.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
+                                 off_count_flags);
+  TORCH_CHECK(data_base.is_cuda() && data_base.scalar_type() == at::kLong && data_base.numel() == world,
+              "data_base must be a CUDA int64 tensor with one address per rank");
+  MB_CUDA_OK(ep_push_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
+                          bins.data_ptr<int>(), counts.data_ptr<int>(), L,
+                          reinterpret_cast<const uint64_t*>(data_base.data_ptr<int64_t>()), off_recv, off_flags,
+                          off_free, int(seq), int(top_k), int(indices.numel()), int(x.size(1)),
+                          done.data_ptr<int>(), status_ptr(x), sm_count(), stream()));
+  MB_LAUNCHED(1);
+}
+
+void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+                       int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
+                       int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
+                       int64_t off_flags, int64_t seq, at::Tensor done) {
+  MB_CHECK_CUDA(y); MB_CHECK_CONTIG(y);
+  c10::cuda::CUDAGuard guard(y.device());
+  const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
+                                 off_count_flags);
+  TORCH_CHECK(data_base.is_cuda() && data_base.scalar_type() == at::kLong && data_base.numel() == world,
+              "data_base must be a CUDA int64 tensor with one address per rank");
+  MB_CUDA_OK(ep_return_rows(float_code(y.scalar_type()), y.data_ptr(), counts.data_ptr<int>(), L,
+                            reinterpret_cast<const uint64_t*>(data_base.data_ptr<int64_t>()), off_ret, off_flags,
+                            int(seq), int(y.size(1)), int(y.size(0)), done.data_ptr<int>(), sm_count(), stream()));
+  MB_LAUNCHED(1);
+}
+
+void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= count, "bad flags tensor");
+  c10::cuda::CUDAGuard guard(flags.device());
+  MB_CUDA_OK(ep_wait_flags(flags.data_ptr<int>(), int(count), int(seq), status_ptr(flags), int(code), stream()));
+  MB_LAUNCHED(1);
+}
+
+void ep_set_flag_op(at::Tensor flag, int64_t value) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && flag.numel() >= 1, "bad flag tensor");
+  c10::cuda::CUDAGuard guard(flag.device());
+  MB_CUDA_OK(ep_set_flag(flag.data_ptr<int>(), int(value), stream()));
   MB_LAUNCHED(1);
 }
 

@@ -35,6 +35,10 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         self.ffn_hidden_size = mpu.features_per_rank(args)
         max_column_index = (self.ffn_hidden_size * self.num_experts) // self.blocking
         self.transpose_sort_end_bit = max(int(max_column_index - 1).bit_length(), 1)
+        self._ep_workspace = None
+        self._ep_workspace_key = None
+        if args.moe_expert_model_parallelism:
+            self.forward_fn = self.parallel_forward_once
 
     def _build_experts(self, args: Arguments) -> torch.nn.Module:
         return dmlp_registry.get(args)
@@ -128,6 +132,47 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         x = ops.gather(x, indices, bin_ids, bins, top_k)
         x = self.mlp(x, tokens_per_expert)
         return ops.scatter(x, indices, bin_ids, expert_weights, bins, top_k)
+
+    # -- expert parallel over peer memory ----------------------------------------
+    def _use_fused_ep(self, x: torch.Tensor) -> bool:
+        want = self.args.ep_fused_comm
+        if want is False:
+            return False
+        from megablocks_b200.parallel import ep
+        ok = ep.fused_path_available(self.args, x)
+        if want is True and not ok:
+            raise RuntimeError('ep_fused_comm=True but the peer-memory route cannot serve this layer '
+                               '(needs CUDA 16-bit activations, a kernel-known activation, world <= experts, '
+                               'hidden and ffn multiples of 64)')
+        return ok
+
+    def parallel_forward_once(self, x, expert_weights, top_experts):
+        if not self._use_fused_ep(x):
+            return super().parallel_forward_once(x, expert_weights, top_experts)
+        from megablocks_b200.ops import gg
+        from megablocks_b200.parallel import ep
+        args = self.args
+        x2d = x.reshape(-1, x.shape[-1])
+        expert_weights = expert_weights.flatten()
+        with torch.no_grad():
+            indices, bin_ids, bins, tokens_per_expert = self.indices_and_bins(top_experts.flatten())
+        copies = indices.numel()
+        key = (copies, x2d.dtype)
+        if self._ep_workspace is None or self._ep_workspace_key != key:
+            self._ep_workspace = ep.EpWorkspace(args.expert_parallel_group, self.num_experts, copies,
+                                                args.hidden_size, x2d.dtype, x2d.device)
+            self._ep_workspace_key = key
+        mlp = self.mlp
+        w1, w2 = mlp._weights()
+        v1 = None
+        if args.mlp_type == 'glu':
+            w1, v1, w2 = mlp._glu_weights()
+            v1 = mlp._grouped_view(v1)
+        out = ep.fused_expert_parallel(x2d, expert_weights.to(x2d.dtype), mlp._grouped_view(w1),
+                                       mlp._grouped_view(w2), v1, self._ep_workspace, indices, bin_ids, bins,
+                                       tokens_per_expert, self.top_k, gg.activation_id(args.activation_fn),
+                                       args.memory_optimized_mlp)
+        return out, tokens_per_expert
 
     # -- dispatch --------------------------------------------------------------
     def forward_once(self, x, expert_weights, top_experts):

@@ -27,62 +27,75 @@ import torch
 from megablocks_b200.ops import gg as G
 
 
+def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tail: bool = True):
+    """Forward GEMMs.  Returns ``(y, saved)`` where ``saved = (z1, z2, h or None)``."""
+    kw = dict(zero_tail=zero_tail)
+    if v1 is not None:
+        z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=True, wait=wait, **kw)
+        z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=z1, **kw)
+    else:
+        z1, h, _ = G.grouped_gemm(x, w1, bins, trans_b=True, epilogue=G.EPI_ACT, act=act, wait=wait, **kw)
+        z2 = None
+    y, _, _ = G.grouped_gemm(h, w2, bins, **kw)
+    return y, (z1, z2, h if keep_h else None)
+
+
+def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True):
+    """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded)."""
+    z1, z2, h = saved
+    num_experts = w1.shape[0]
+    kw = dict(zero_tail=zero_tail)
+    if v1 is not None:
+        dz1, dz2, h_new = G.grouped_gemm(dy, w2, bins, trans_b=True, epilogue=G.EPI_DGLU, act=act, aux1=z1,
+                                         aux2=z2, want_out3=h is None, wait=wait, **kw)
+    else:
+        dz1, h_new, _ = G.grouped_gemm(dy, w2, bins, trans_b=True, epilogue=G.EPI_DACT, act=act, aux1=z1,
+                                       want_out2=h is None, wait=wait, **kw)
+        dz2 = None
+    if h is None:
+        h = h_new
+    dx = dw1 = dw2 = dv1 = None
+    if needs[2]:
+        dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts)
+    if needs[1]:
+        dw1, _, _ = G.grouped_gemm(dz1, x, bins, trans_a=True, num_groups=num_experts)
+    if v1 is not None and needs[3]:
+        dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts)
+    if needs[0]:
+        dx, _, _ = G.grouped_gemm(dz1, w1, bins, **kw)
+        if v1 is not None:
+            dx, _, _ = G.grouped_gemm(dz2, v1, bins, epilogue=G.EPI_ADD, aux1=dx, **kw)
+    return dx, dw1, dw2, dv1
+
+
 class _ExpertMLP(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, x, w1, w2, v1, bins, act: int, memory_optimized: bool):
         x = x.contiguous()
-        glu = v1 is not None
-        if glu:
-            z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=True)
-            z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=z1)
-        else:
-            z1, h, _ = G.grouped_gemm(x, w1, bins, trans_b=True, epilogue=G.EPI_ACT, act=act)
-            z2 = None
-        y, _, _ = G.grouped_gemm(h, w2, bins)
+        y, (z1, z2, h) = mlp_forward(x, w1, w2, v1, bins, act, keep_h=not memory_optimized)
         saved = [x, w1, w2, bins, z1]
-        if glu:
+        if v1 is not None:
             saved += [v1, z2]
-        if not memory_optimized:
+        if h is not None:
             saved.append(h)
         ctx.save_for_backward(*saved)
-        ctx.glu = glu
+        ctx.glu = v1 is not None
         ctx.act = act
-        ctx.keep_h = not memory_optimized
+        ctx.keep_h = h is not None
         return y
 
     @staticmethod
     def backward(ctx: Any, dy):
-        dy = dy.contiguous()
         saved = list(ctx.saved_tensors)
         x, w1, w2, bins, z1 = saved[:5]
         v1 = z2 = None
         if ctx.glu:
             v1, z2 = saved[5:7]
         h = saved[-1] if ctx.keep_h else None
-        num_experts = w1.shape[0]
-
-        if ctx.glu:
-            dz1, dz2, h_new = G.grouped_gemm(dy, w2, bins, trans_b=True, epilogue=G.EPI_DGLU, act=ctx.act,
-                                             aux1=z1, aux2=z2, want_out3=h is None)
-        else:
-            dz1, h_new, _ = G.grouped_gemm(dy, w2, bins, trans_b=True, epilogue=G.EPI_DACT, act=ctx.act,
-                                           aux1=z1, want_out2=h is None)
-            dz2 = None
-        if h is None:
-            h = h_new
-
-        dw1 = dw2 = dv1 = dx = None
-        if ctx.needs_input_grad[2]:
-            dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts)
-        if ctx.needs_input_grad[1]:
-            dw1, _, _ = G.grouped_gemm(dz1, x, bins, trans_a=True, num_groups=num_experts)
-        if ctx.glu and ctx.needs_input_grad[3]:
-            dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts)
-        if ctx.needs_input_grad[0]:
-            dx, _, _ = G.grouped_gemm(dz1, w1, bins)
-            if ctx.glu:
-                dx, _, _ = G.grouped_gemm(dz2, v1, bins, epilogue=G.EPI_ADD, aux1=dx)
+        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2],
+                 ctx.glu and ctx.needs_input_grad[3])
+        dx, dw1, dw2, dv1 = mlp_backward(dy.contiguous(), x, w1, w2, v1, bins, ctx.act, (z1, z2, h), needs)
         return dx, dw1, dw2, dv1, None, None, None
 
 

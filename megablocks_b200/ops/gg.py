@@ -173,18 +173,26 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  trans_b: bool = False, epilogue: int = EPI_NONE, act: int = ACT_IDENTITY,
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
-                 c: Optional[torch.Tensor] = None):
+                 c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
     allocates an upper bound); rows past ``bins[-1]`` are written as zero.
-    ``c`` optionally supplies the output buffer of the main result.
+    ``c`` optionally supplies the output buffer of the main result.  ``zero_tail=False``
+    leaves those trailing rows untouched (used with worst-case sized buffers).
+    ``wait = (flags, count, stride, seq)`` makes the kernel's load warp wait, per
+    group ``g``, until ``flags[s * stride + g] >= seq`` for every ``s < count``: the
+    rows of ``a`` are then being delivered by peer GPUs (expert-parallel dispatch).
     """
     if num_groups is None:
         num_groups = bins.numel()
     if a.is_cuda and ext().grouped_gemm_supported(a, b, bool(trans_a), bool(trans_b), int(num_groups)):
+        flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
-                                  bool(want_out2), bool(want_out3), int(num_groups), c)
+                                  bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
+                                  int(count), int(stride), int(seq))
+    if wait is not None:
+        raise RuntimeError('grouped_gemm: peer-arrival waits need the CUDA kernel (unsupported shape or dtype)')
     # Shapes or dtypes the tensor-core kernel does not take (fp32 inputs, rows that
     # are not a multiple of 8 elements, more than 1024 groups) and every CPU tensor:
     # per-group matmuls in fp32.  On CUDA this reads the group sizes back to the host.
