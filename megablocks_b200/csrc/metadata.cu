@@ -8,6 +8,9 @@
 // 8-bit digit), so a sort is a histogram, a scan and one stable placement pass,
 // and the histogram / prefix sums the caller wants next fall out of the same passes.
 #include "common.cuh"
+#include "route_plan_noalloc.h"
+
+#include <cstdio>
 
 namespace mb {
 
@@ -395,4 +398,74 @@ cudaError_t replicate_bwd(DType type, const void* grad, const int* bins, int num
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free route plan (see route_plan_noalloc.h)
+// ---------------------------------------------------------------------------
+namespace {
+
+// Scratch of one counting-sort pass at the stated maxima: per-chunk histograms
+// [1024 bins][512 chunks] followed by the 1024 bin totals.
+constexpr int kNoAllocMaxChunks = MB_NOALLOC_MAX_COPIES / 2048;
+constexpr int kNoAllocPartialInts = MB_NOALLOC_MAX_EXPERTS * kNoAllocMaxChunks;
+constexpr int kNoAllocScratchInts = kNoAllocPartialInts + MB_NOALLOC_MAX_EXPERTS;
+
+static __device__ __align__(256) int g_noalloc_scratch[kNoAllocScratchInts];
+
+// Device address of the scratch array per device.  The array's name is only a
+// host-side handle; kernels need the address cudaGetSymbolAddress reports.
+int* g_noalloc_scratch_addr[64] = {nullptr};
+
+cudaError_t noalloc_scratch(int** out) {
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return rc;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    rc = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (rc != cudaSuccess) return rc;
+    g_noalloc_scratch_addr[dev] = static_cast<int*>(ptr);
+  }
+  *out = g_noalloc_scratch_addr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
 }  // namespace mb
+
+extern "C" cudaError_t mb_route_plan_noalloc(const int32_t* top_experts, int64_t n, int num_experts, int block,
+                                             int32_t* indices, int32_t* bin_ids, int32_t* bins,
+                                             int32_t* padded_bins, int32_t* tokens_per_expert,
+                                             cudaStream_t stream) {
+  using namespace mb;
+  if (n < 0 || n > MB_NOALLOC_MAX_COPIES || num_experts < 1 || num_experts > MB_NOALLOC_MAX_EXPERTS || block < 1) {
+    std::fprintf(stderr,
+                 "mb_route_plan_noalloc: n=%lld experts=%d block=%d is outside the supported range "
+                 "(n <= %d, 1 <= experts <= %d, block >= 1)\n",
+                 static_cast<long long>(n), num_experts, block, MB_NOALLOC_MAX_COPIES, MB_NOALLOC_MAX_EXPERTS);
+    return cudaErrorInvalidValue;
+  }
+  int* scratch = nullptr;
+  cudaError_t rc = noalloc_scratch(&scratch);
+  if (rc != cudaSuccess) return rc;
+  int bits = 1;
+  while ((1 << bits) < num_experts) ++bits;
+  const int chunk = sort_warp_chunk(n);
+  const int num_chunks = n > 0 ? ceil_div(n, chunk) : 1;
+  if (int64_t(1 << bits) * num_chunks > kNoAllocPartialInts) return cudaErrorInvalidValue;
+  int* partial = scratch;
+  int* totals = scratch + kNoAllocPartialInts;
+  if (n == 0) {
+    // No copies: the counts and both prefix sums are all zero.
+    rc = cudaMemsetAsync(tokens_per_expert, 0, sizeof(int) * num_experts, stream);
+    if (rc == cudaSuccess) rc = cudaMemsetAsync(bins, 0, sizeof(int) * num_experts, stream);
+    if (rc == cudaSuccess) rc = cudaMemsetAsync(padded_bins, 0, sizeof(int) * num_experts, stream);
+    return rc;
+  }
+  // One stable pass over the expert-id bits.  Every scratch word that the scan and
+  // placement kernels read is written by the histogram kernel of this same call, so
+  // nothing needs clearing.
+  return sort_pass(kI32, top_experts, nullptr, n, 0, bits, false, chunk, num_chunks, partial, totals, bin_ids,
+                   indices, tokens_per_expert, bins, padded_bins, num_experts, block, stream);
+}
