@@ -202,8 +202,9 @@ def run_ours(args):
 
     torch.manual_seed(1234)
     group = dist.group.WORLD if world > 1 else None
+    fused = {'auto': None, 'fused': True, 'nccl': False}[args.ep_comm]
     cfg = preset('dmoe-125m', device=torch.device('cuda', local), expert_parallel_group=group,
-                 mlp_impl=args.mlp_impl, memory_optimized_mlp=True)
+                 mlp_impl=args.mlp_impl, memory_optimized_mlp=True, ep_fused_comm=fused)
     model = MoETransformer(cfg)
     trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000), dp_group=group)
     out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count)
@@ -211,9 +212,10 @@ def run_ours(args):
     if rank == 0:
         _emit('megablocks_b200', args.gpus, args.steps, args.warmup, *out,
               extra_config={'mlp_impl': args.mlp_impl,
-                            'ep_comm': 'fused peer-memory kernels' if getattr(model.blocks[0].moe.experts,
-                                                                             '_fused_ep', None) else
-                            ('nccl all_to_all' if world > 1 else 'none')})
+                            'ep_comm': ('none' if world == 1 else
+                                        'fused peer-memory kernels (remote stores + flags, no NCCL all-to-all)'
+                                        if model.blocks[0].moe.experts._ep_workspace is not None else
+                                        'nccl all_to_all')})
     if world > 1:
         dist.destroy_process_group()
 
@@ -252,6 +254,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     ap.add_argument('--mlp-impl', dest='mlp_impl', choices=['grouped', 'sparse'], default='grouped')
+    ap.add_argument('--ep-comm', dest='ep_comm', choices=['auto', 'fused', 'nccl'], default='auto',
+                    help='expert-parallel exchange: peer-memory kernels (auto/fused) or NCCL all-to-all')
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -71,6 +71,15 @@ void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::
 void ep_set_flag_op(at::Tensor flag, int64_t value);
 void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code);
 
+// torch_glue.cpp: fused row-wise ops
+std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at::Tensor& targets);
+void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
+                             const c10::optional<at::Tensor>& scale, double scale_mul);
+std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
+                                          double eps);
+std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
+                                           const at::Tensor& mean, const at::Tensor& rstd);
+
 // torch_glue.cpp: optimizer
 int64_t adam_record_size();
 void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t param_code,
@@ -103,6 +112,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &mb::grouped_gemm);
   m.def("read_status", &mb::read_status);
   m.def("launch_count", &mb::launch_count);
+  m.def("cross_entropy_forward", &mb::cross_entropy_forward);
+  m.def("cross_entropy_backward_", &mb::cross_entropy_backward_);
+  m.def("layernorm_forward", &mb::layernorm_forward);
+  m.def("layernorm_backward", &mb::layernorm_backward);
   m.def("symm_alloc", &mb::symm_alloc);
   m.def("symm_open", &mb::symm_open);
   m.def("symm_close", &mb::symm_close);

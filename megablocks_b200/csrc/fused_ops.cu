@@ -1,0 +1,261 @@
+// Row-wise fused kernels for the transformer around the MoE layers (sm_100a):
+// softmax cross-entropy (forward and in-place backward, no fp32 copy of the logits)
+// and LayerNorm (forward; backward with the weight / bias gradients reduced through
+// shared memory and one small second pass).  The reference has no model code; these
+// serve this library's own training model (models/transformer.py), where the eager
+// PyTorch versions cost more HBM traffic than the whole MoE stack.
+#include "common.cuh"
+
+namespace mb {
+
+namespace {
+
+constexpr int kCeThreads = 512;
+
+template <typename T, int N>
+struct alignas(16) Pack {
+  T v[N];
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  return v;
+}
+
+// lse[t] = log sum_j exp(x[t, j]);  loss[t] = lse[t] - x[t, target[t]].
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ targets, int64_t vocab,
+                         float* __restrict__ lse_out, float* __restrict__ loss_out) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float red_m[kCeThreads / 32], red_s[kCeThreads / 32];
+  const T* row = logits + int64_t(blockIdx.x) * vocab;
+  float m = -INFINITY, s = 0.f;
+  const bool vec_ok = (vocab % VEC == 0) && (reinterpret_cast<uintptr_t>(row) % 16 == 0);
+  auto add = [&](float x) {
+    if (x > m) { s = s * __expf(m - x) + 1.f; m = x; } else { s += __expf(x - m); }
+  };
+  if (vec_ok) {
+    for (int64_t i = int64_t(threadIdx.x) * VEC; i < vocab; i += kCeThreads * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(row + i);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) add(to_float(p.v[k]));
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < vocab; i += kCeThreads) add(to_float(row[i]));
+  }
+  // Combine (m, s) pairs: warp, then block.
+  const float wm = warp_max(m);
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+  if ((threadIdx.x & 31) == 0) { red_m[threadIdx.x >> 5] = wm; red_s[threadIdx.x >> 5] = s; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float mm = threadIdx.x < kCeThreads / 32 ? red_m[threadIdx.x] : -INFINITY;
+    float ss = threadIdx.x < kCeThreads / 32 ? red_s[threadIdx.x] : 0.f;
+    const float bm = warp_max(mm);
+    ss = warp_sum(mm == -INFINITY ? 0.f : ss * __expf(mm - bm));
+    if (threadIdx.x == 0) {
+      const float lse = bm + __logf(ss);
+      lse_out[blockIdx.x] = lse;
+      const int64_t tgt = targets[blockIdx.x];
+      loss_out[blockIdx.x] = (tgt >= 0 && tgt < vocab) ? lse - to_float(row[tgt]) : 0.f;
+    }
+  }
+}
+
+// grad[t, j] = (exp(x[t, j] - lse[t]) - [j == target[t]]) * scale[0], written over x.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict__ targets, const float* __restrict__ lse,
+                         const float* __restrict__ scale_ptr, float scale_mul, int64_t vocab) {
+  constexpr int VEC = 16 / sizeof(T);
+  T* row = logits + int64_t(blockIdx.x) * vocab;
+  const float l = lse[blockIdx.x];
+  const float scale = (scale_ptr != nullptr ? *scale_ptr : 1.f) * scale_mul;
+  const int64_t tgt = targets[blockIdx.x];
+  const bool valid = tgt >= 0 && tgt < vocab;
+  const bool vec_ok = (vocab % VEC == 0) && (reinterpret_cast<uintptr_t>(row) % 16 == 0);
+  if (vec_ok) {
+    for (int64_t i = int64_t(threadIdx.x) * VEC; i < vocab; i += kCeThreads * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(row + i);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float g = valid ? __expf(to_float(p.v[k]) - l) : 0.f;
+        if (i + k == tgt) g -= 1.f;
+        p.v[k] = from_float<T>(g * scale);
+      }
+      *reinterpret_cast<Pack<T, VEC>*>(row + i) = p;
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < vocab; i += kCeThreads) {
+      float g = valid ? __expf(to_float(row[i]) - l) : 0.f;
+      if (i == tgt) g -= 1.f;
+      row[i] = from_float<T>(g * scale);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm: one warp per row, rows strided over a persistent grid.
+// ---------------------------------------------------------------------------
+constexpr int kLnWarps = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, int64_t rows,
+                     int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
+                     float* __restrict__ rstd_out) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = int64_t(gridDim.x) * kLnWarps;
+  for (int64_t r = int64_t(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); r < rows; r += stride) {
+    const T* xr = x + r * cols;
+    float s = 0.f, ss = 0.f;
+    for (int c = lane * VEC; c < cols; c += 32 * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) { const float v = to_float(p.v[k]); s += v; ss += v * v; }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mean = s / cols;
+    const float rstd = rsqrtf(fmaxf(ss / cols - mean * mean, 0.f) + eps);
+    if (lane == 0) { mean_out[r] = mean; rstd_out[r] = rstd; }
+    T* yr = y + r * cols;
+    for (int c = lane * VEC; c < cols; c += 32 * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+      Pack<T, VEC> g = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+      Pack<T, VEC> b = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k)
+        p.v[k] = from_float<T>((to_float(p.v[k]) - mean) * rstd * to_float(g.v[k]) + to_float(b.v[k]));
+      *reinterpret_cast<Pack<T, VEC>*>(yr + c) = p;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                     const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
+                     T* __restrict__ dx, float* __restrict__ partial) {
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ float acc[];          // [2][cols]: dgamma, dbeta of this CTA
+  for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = int64_t(gridDim.x) * kLnWarps;
+  for (int64_t r = int64_t(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); r < rows; r += stride) {
+    const T* xr = x + r * cols;
+    const T* dr = dy + r * cols;
+    const float mu = mean[r], rs = rstd[r];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane * VEC; c < cols; c += 32 * VEC) {
+      Pack<T, VEC> px = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+      Pack<T, VEC> pd = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
+      Pack<T, VEC> pg = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float xhat = (to_float(px.v[k]) - mu) * rs;
+        const float d = to_float(pd.v[k]);
+        const float dg = d * to_float(pg.v[k]);
+        s1 += dg * xhat;
+        s2 += dg;
+        atomicAdd(&acc[c + k], d * xhat);
+        atomicAdd(&acc[cols + c + k], d);
+      }
+    }
+    s1 = warp_sum(s1) / cols;
+    s2 = warp_sum(s2) / cols;
+    T* dxr = dx + r * cols;
+    for (int c = lane * VEC; c < cols; c += 32 * VEC) {
+      Pack<T, VEC> px = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+      Pack<T, VEC> pd = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
+      Pack<T, VEC> pg = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float xhat = (to_float(px.v[k]) - mu) * rs;
+        const float dg = to_float(pd.v[k]) * to_float(pg.v[k]);
+        px.v[k] = from_float<T>(rs * (dg - s2 - xhat * s1));
+      }
+      *reinterpret_cast<Pack<T, VEC>*>(dxr + c) = px;
+    }
+  }
+  __syncthreads();
+  float* out = partial + int64_t(blockIdx.x) * 2 * cols;
+  for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) out[c] = acc[c];
+}
+
+// dgamma / dbeta = column sums of the per-CTA partials.
+template <typename T>
+__global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int cols,
+                                            T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * cols) return;
+  float s = 0.f;
+  for (int p = 0; p < num_partials; ++p) s += partial[int64_t(p) * 2 * cols + c];
+  if (c < cols) dgamma[c] = from_float<T>(s); else dbeta[c - cols] = from_float<T>(s);
+}
+
+}  // namespace
+
+cudaError_t cross_entropy_fwd(DType type, const void* logits, const int64_t* targets, int64_t rows, int64_t vocab,
+                              float* lse, float* loss, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  MB_SWITCH_FLOAT(type, T, {
+    cross_entropy_fwd_kernel<T><<<static_cast<unsigned>(rows), kCeThreads, 0, stream>>>(
+        static_cast<const T*>(logits), targets, vocab, lse, loss);
+  })
+  return cudaGetLastError();
+}
+
+cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, const float* lse,
+                              const float* scale_ptr, float scale_mul, int64_t rows, int64_t vocab,
+                              cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  MB_SWITCH_FLOAT(type, T, {
+    cross_entropy_bwd_kernel<T><<<static_cast<unsigned>(rows), kCeThreads, 0, stream>>>(
+        static_cast<T*>(logits), targets, lse, scale_ptr, scale_mul, vocab);
+  })
+  return cudaGetLastError();
+}
+
+int layernorm_grid(int64_t rows, int sms) { return max(1, min(ceil_div(rows, kLnWarps), sms * 2)); }
+
+cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
+                          float eps, void* y, float* mean, float* rstd, int sms, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  MB_SWITCH_FLOAT(type, T, {
+    if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
+    layernorm_fwd_kernel<T><<<layernorm_grid(rows, sms), kLnWarps * 32, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), rows, cols, eps,
+        static_cast<T*>(y), mean, rstd);
+  })
+  return cudaGetLastError();
+}
+
+cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
+                          const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
+                          float* partial, int sms, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  const int grid = layernorm_grid(rows, sms);
+  const size_t smem = size_t(2) * cols * sizeof(float);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  MB_SWITCH_FLOAT(type, T, {
+    if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
+    layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(
+        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
+        static_cast<T*>(dx), partial);
+    layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
+        partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
+  })
+  return cudaGetLastError();
+}
+
+}  // namespace mb

@@ -78,6 +78,20 @@ cudaError_t grad_sqnorm(DType grad_type, const AdamTensor* tensors, const int2* 
                         float* out_accum, cudaStream_t stream);
 cudaError_t clip_coeff(const float* sqnorm, float max_norm, float extra_scale, float* out, cudaStream_t stream);
 
+// ---- fused_ops.cu -------------------------------------------------------------
+cudaError_t cross_entropy_fwd(DType type, const void* logits, const int64_t* targets, int64_t rows, int64_t vocab,
+                              float* lse, float* loss, cudaStream_t stream);
+// Overwrites `logits` with (softmax - onehot) * scale_ptr[0] * scale_mul.
+cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, const float* lse,
+                              const float* scale_ptr, float scale_mul, int64_t rows, int64_t vocab,
+                              cudaStream_t stream);
+int layernorm_grid(int64_t rows, int sms);   // CTAs (= rows of `partial`) the backward uses
+cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
+                          float eps, void* y, float* mean, float* rstd, int sms, cudaStream_t stream);
+cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
+                          const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
+                          float* partial, int sms, cudaStream_t stream);
+
 // ---- ep_comm.cu ---------------------------------------------------------------
 // Geometry of one expert-parallel workspace.  `peer_base[r]` is the address at which
 // rank r's symmetric heap is mapped in this process (device array of `world` entries);

@@ -606,6 +606,72 @@ void clip_coeff_op(const at::Tensor& sqnorm, double max_norm, double extra_scale
 }
 
 // ---------------------------------------------------------------------------
+// fused row-wise ops: cross entropy, LayerNorm
+// ---------------------------------------------------------------------------
+std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at::Tensor& targets) {
+  MB_CHECK_CUDA(logits); MB_CHECK_CONTIG(logits); MB_CHECK_CUDA(targets); MB_CHECK_CONTIG(targets);
+  TORCH_CHECK(logits.dim() == 2 && targets.dim() == 1 && targets.scalar_type() == at::kLong &&
+                  targets.numel() == logits.size(0),
+              "cross_entropy expects logits[rows, vocab] and int64 targets[rows]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto fopts = logits.options().dtype(at::kFloat);
+  at::Tensor lse = at::empty({logits.size(0)}, fopts), loss = at::empty({logits.size(0)}, fopts);
+  MB_CUDA_OK(cross_entropy_fwd(float_code(logits.scalar_type()), logits.data_ptr(), targets.data_ptr<int64_t>(),
+                               logits.size(0), logits.size(1), lse.data_ptr<float>(), loss.data_ptr<float>(),
+                               stream()));
+  MB_LAUNCHED(1);
+  return {loss, lse};
+}
+
+// Overwrites `logits` with its gradient: (softmax - onehot) * scale[0] * scale_mul.
+void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
+                             const c10::optional<at::Tensor>& scale, double scale_mul) {
+  MB_CHECK_CUDA(logits); MB_CHECK_CONTIG(logits);
+  c10::cuda::CUDAGuard guard(logits.device());
+  const float* sp = nullptr;
+  if (scale.has_value()) {
+    TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == at::kFloat && scale->numel() >= 1,
+                "scale must be a CUDA float32 scalar");
+    sp = scale->data_ptr<float>();
+  }
+  MB_CUDA_OK(cross_entropy_bwd(float_code(logits.scalar_type()), logits.data_ptr(), targets.data_ptr<int64_t>(),
+                               lse.data_ptr<float>(), sp, float(scale_mul), logits.size(0), logits.size(1),
+                               stream()));
+  MB_LAUNCHED(1);
+}
+
+std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
+                                          double eps) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CONTIG(gamma); MB_CHECK_CONTIG(beta);
+  TORCH_CHECK(x.dim() == 2 && gamma.numel() == x.size(1) && beta.numel() == x.size(1) &&
+                  gamma.scalar_type() == x.scalar_type() && beta.scalar_type() == x.scalar_type(),
+              "layernorm expects x[rows, cols] and weight / bias of length cols in the dtype of x");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty_like(x);
+  auto fopts = x.options().dtype(at::kFloat);
+  at::Tensor mean = at::empty({x.size(0)}, fopts), rstd = at::empty({x.size(0)}, fopts);
+  MB_CUDA_OK(layernorm_fwd(float_code(x.scalar_type()), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), x.size(0),
+                           int(x.size(1)), float(eps), y.data_ptr(), mean.data_ptr<float>(),
+                           rstd.data_ptr<float>(), sm_count(), stream()));
+  MB_LAUNCHED(1);
+  return {y, mean, rstd};
+}
+
+std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
+                                           const at::Tensor& mean, const at::Tensor& rstd) {
+  MB_CHECK_CUDA(dy); MB_CHECK_CONTIG(dy); MB_CHECK_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor dx = at::empty_like(x), dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
+  const int grid = layernorm_grid(x.size(0), sm_count());
+  at::Tensor partial = at::empty({grid, 2 * x.size(1)}, x.options().dtype(at::kFloat));
+  MB_CUDA_OK(layernorm_bwd(float_code(x.scalar_type()), dy.data_ptr(), x.data_ptr(), gamma.data_ptr(),
+                           mean.data_ptr<float>(), rstd.data_ptr<float>(), x.size(0), int(x.size(1)), dx.data_ptr(),
+                           dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(), sm_count(), stream()));
+  MB_LAUNCHED(2);
+  return {dx, dgamma, dbeta};
+}
+
+// ---------------------------------------------------------------------------
 // symmetric heap (CUDA IPC) and expert-parallel exchange
 // ---------------------------------------------------------------------------
 // Allocates `nbytes` of zeroed device memory that peers can map, and returns it as a

@@ -27,6 +27,7 @@ from megablocks_b200.layers.arguments import Arguments
 from megablocks_b200.layers.dmoe import dMoE
 from megablocks_b200.layers.moe import MoE, batched_load_balancing_loss, clear_load_balancing_loss
 from megablocks_b200.layers.router import batched_router_zloss, clear_router_zloss
+from megablocks_b200.ops import fused
 
 
 @dataclasses.dataclass
@@ -176,7 +177,7 @@ class Block(nn.Module):
     def __init__(self, cfg: TransformerConfig, moe_args: Arguments):
         super().__init__()
         kw = dict(device=cfg.device, dtype=cfg.dtype)
-        norm = RMSNorm if cfg.flavour == 'mixtral' else nn.LayerNorm
+        norm = RMSNorm if cfg.flavour == 'mixtral' else fused.LayerNorm
         self.ln1 = norm(cfg.hidden_size, **kw)
         self.attn = Attention(cfg)
         self.ln2 = norm(cfg.hidden_size, **kw)
@@ -204,7 +205,7 @@ class MoETransformer(nn.Module):
             self.wpe = nn.Embedding(cfg.max_seq_len, cfg.hidden_size, **kw)
             nn.init.normal_(self.wpe.weight, std=cfg.init_std)
         self.blocks = nn.ModuleList([Block(cfg, self.moe_args) for _ in range(cfg.num_layers)])
-        norm = RMSNorm if cfg.flavour == 'mixtral' else nn.LayerNorm
+        norm = RMSNorm if cfg.flavour == 'mixtral' else fused.LayerNorm
         self.ln_f = norm(cfg.hidden_size, **kw)
         self.lm_head = None
         if cfg.flavour == 'mixtral':
@@ -247,7 +248,7 @@ class MoETransformer(nn.Module):
         """
         hidden = self.hidden_states(tokens)
         logits = self.logits(hidden)
-        lm = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1))
+        lm = fused.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
         total = lm
         if self.training and self.moe_args.moe_loss_weight > 0:
             total = total + batched_load_balancing_loss(self.moe_args)

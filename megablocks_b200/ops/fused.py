@@ -1,0 +1,77 @@
+"""Fused row-wise ops for the transformer around the MoE layers.
+
+* :func:`cross_entropy` - mean softmax cross-entropy over ``[rows, vocab]`` logits.
+  On CUDA the forward reads the 16-bit logits once (no fp32 copy) and the backward
+  overwrites the logits buffer with the gradient in place, so a 3.3 GB logits tensor
+  costs three passes instead of the dozen of the eager float() / log_softmax /
+  nll_loss chain.  The logits tensor must not be used after the loss (it is the
+  gradient afterwards).
+* :func:`layer_norm` - LayerNorm whose backward reduces the weight and bias
+  gradients through shared memory in the same pass that produces ``dx``.
+
+Both fall back to the PyTorch ops on CPU tensors.
+"""
+
+from typing import Any
+
+import torch
+import torch.nn.functional as F
+
+from megablocks_b200._ext import ext
+
+
+class _CrossEntropy(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, logits: torch.Tensor, targets: torch.Tensor):
+        loss, lse = ext().cross_entropy_forward(logits, targets)
+        ctx.save_for_backward(logits, targets, lse)
+        return loss.mean()
+
+    @staticmethod
+    def backward(ctx: Any, grad_out: torch.Tensor):
+        logits, targets, lse = ctx.saved_tensors
+        scale = grad_out.detach().float().reshape(1)
+        ext().cross_entropy_backward_(logits, targets, lse, scale, 1.0 / logits.shape[0])
+        return logits, None
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Mean cross entropy of ``logits[rows, vocab]`` against ``targets[rows]`` (int64)."""
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float16, torch.float32) and logits.is_contiguous():
+        return _CrossEntropy.apply(logits, targets.contiguous())
+    return F.cross_entropy(logits.float(), targets)
+
+
+class _LayerNorm(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        y, mean, rstd = ext().layernorm_forward(x2, weight, bias, eps)
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.shape = shape
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor):
+        x2, weight, mean, rstd = ctx.saved_tensors
+        dx, dw, db = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd)
+        return dx.view(ctx.shape), dw, db, None
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    cols = x.shape[-1]
+    fused = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and weight.dtype == x.dtype
+             and bias is not None and (cols * x.element_size()) % 16 == 0 and cols <= 6144)
+    if fused:
+        return _LayerNorm.apply(x, weight, bias, eps)
+    return F.layer_norm(x, (cols,), weight, bias, eps)
+
+
+class LayerNorm(torch.nn.LayerNorm):
+    """``nn.LayerNorm`` (same parameters and state dict) running the fused kernels on CUDA."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return layer_norm(x, self.weight, self.bias, self.eps)

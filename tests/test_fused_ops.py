@@ -1,0 +1,49 @@
+"""Fused cross-entropy and LayerNorm against the PyTorch ops in fp32."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+from conftest import DEVICES
+
+from megablocks_b200.ops import fused
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,vocab', [(64, 512), (257, 51200), (33, 1000), (8, 7)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_cross_entropy(device, rows, vocab, dtype):
+    logits = (torch.randn(rows, vocab) * 3).to(dtype).to(device).requires_grad_(True)
+    targets = torch.randint(0, vocab, (rows,), device=device)
+    ref_in = logits.detach().float().cpu().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, targets.cpu())
+    (ref * 1.7).backward()
+    loss = fused.cross_entropy(logits, targets)
+    torch.testing.assert_close(loss.float().cpu(), ref.detach(), rtol=1e-4, atol=1e-4)
+    (loss * 1.7).backward()
+    tol = dict(rtol=2e-2, atol=1e-4) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(logits.grad.float().cpu(), ref_in.grad, **tol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,cols', [(1000, 768), (77, 1024), (4096, 128), (5, 4096)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_layer_norm(device, rows, cols, dtype):
+    ln = fused.LayerNorm(cols).to(device=device, dtype=dtype)
+    with torch.no_grad():
+        ln.weight.copy_(torch.randn(cols) * 0.5 + 1)
+        ln.bias.copy_(torch.randn(cols) * 0.5)
+    x = (torch.randn(rows, cols) * 2 + 0.3).to(dtype).to(device).requires_grad_(True)
+    probe = torch.randn(rows, cols).to(dtype).to(device)
+    y = ln(x)
+    (y.float() * probe.float()).sum().backward()
+    xr = x.detach().float().cpu().requires_grad_(True)
+    wr = ln.weight.detach().float().cpu().requires_grad_(True)
+    br = ln.bias.detach().float().cpu().requires_grad_(True)
+    yr = F.layer_norm(xr, (cols,), wr, br, ln.eps)
+    (yr * probe.float().cpu()).sum().backward()
+    tol = dict(rtol=2e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(y.detach().float().cpu(), yr.detach(), **tol)
+    torch.testing.assert_close(x.grad.float().cpu(), xr.grad, **tol)
+    wtol = dict(rtol=3e-2, atol=3e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(ln.weight.grad.float().cpu(), wr.grad, **wtol)
+    torch.testing.assert_close(ln.bias.grad.float().cpu(), br.grad, **wtol)
