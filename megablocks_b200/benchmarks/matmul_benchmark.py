@@ -6,6 +6,7 @@ configurations.  Reports milliseconds, TFLOP/s and the fraction of the measured
 dense bf16 peak (``MEASURED_PEAKS.json`` at the repository root when present).
 
     python -m megablocks_b200.benchmarks.matmul_benchmark [--shape T H F E] [--iters N] [--zipf S]
+                                                          [--case PREFIX] [--warmup N]
 """
 
 import argparse
@@ -46,7 +47,7 @@ def routed_bins(tokens, experts, zipf, device):
     return torch.cumsum(counts, 0).to(torch.int32).to(device)
 
 
-def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16):
+def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16, only=None, warmup=5):
     dev = torch.device('cuda')
     peak, kind = measured_peak_tflops()
     bins = routed_bins(tokens, experts, zipf, dev)
@@ -65,7 +66,9 @@ def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16):
     }
     print(f'shape tokens={tokens} hidden={hidden} ffn={ffn} experts={experts} zipf={zipf}')
     for name, fn in cases.items():
-        mean, std = benchmark_function(fn, iterations=iters, warmup=5, flush_l2=True)
+        if only is not None and not name.startswith(only):
+            continue
+        mean, std = benchmark_function(fn, iterations=iters, warmup=warmup, flush_l2=True)
         tf = flops / mean / 1e9
         print(f'  {name:34s} {mean:8.3f} ms +- {std:5.3f}  {tf:8.1f} TFLOP/s  {tf / peak:5.2f} of {kind} bf16 peak')
 
@@ -75,10 +78,12 @@ def main():
     ap.add_argument('--shape', type=int, nargs=4, metavar=('TOKENS', 'HIDDEN', 'FFN', 'EXPERTS'))
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--zipf', type=float, default=0.0)
+    ap.add_argument('--case', type=str, default=None, help='run only the cases whose name starts with this')
+    ap.add_argument('--warmup', type=int, default=5)
     args = ap.parse_args()
     shapes = [tuple(args.shape)] if args.shape else SHAPES
     for shape in shapes:
-        run_shape(*shape, iters=args.iters, zipf=args.zipf)
+        run_shape(*shape, iters=args.iters, zipf=args.zipf, only=args.case, warmup=args.warmup)
 
 
 if __name__ == '__main__':

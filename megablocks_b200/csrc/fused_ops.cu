@@ -192,6 +192,88 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) out[c] = acc[c];
 }
 
+// Same, for rows of at most 32 * MAXV * VEC elements: every lane owns fixed columns, so
+// the weight / bias gradients accumulate in registers across the rows a warp visits and
+// meet in shared memory once at the end (no per-element atomics).
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                         const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
+                         T* __restrict__ dx, float* __restrict__ partial) {
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ float acc[];          // [2][cols]
+  for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  float dg_acc[MAXV][VEC], db_acc[MAXV][VEC], g_reg[MAXV][VEC];
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    Pack<T, VEC> pg;
+    if (c < cols) pg = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      dg_acc[j][k] = 0.f;
+      db_acc[j][k] = 0.f;
+      g_reg[j][k] = c < cols ? to_float(pg.v[k]) : 0.f;
+    }
+  }
+  const int64_t stride = int64_t(gridDim.x) * kLnWarps;
+  for (int64_t r = int64_t(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); r < rows; r += stride) {
+    const T* xr = x + r * cols;
+    const T* dr = dy + r * cols;
+    const float mu = mean[r], rs = rstd[r];
+    float xhat[MAXV][VEC], dgv[MAXV][VEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) {
+        Pack<T, VEC> px = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+        Pack<T, VEC> pd = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const float xh = (to_float(px.v[k]) - mu) * rs;
+          const float d = to_float(pd.v[k]);
+          xhat[j][k] = xh;
+          dgv[j][k] = d * g_reg[j][k];
+          s1 += dgv[j][k] * xh;
+          s2 += dgv[j][k];
+          dg_acc[j][k] += d * xh;
+          db_acc[j][k] += d;
+        }
+      }
+    }
+    s1 = warp_sum(s1) / cols;
+    s2 = warp_sum(s2) / cols;
+    T* dxr = dx + r * cols;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) {
+        Pack<T, VEC> po;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) po.v[k] = from_float<T>(rs * (dgv[j][k] - s2 - xhat[j][k] * s1));
+        *reinterpret_cast<Pack<T, VEC>*>(dxr + c) = po;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    if (c < cols) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        atomicAdd(&acc[c + k], dg_acc[j][k]);
+        atomicAdd(&acc[cols + c + k], db_acc[j][k]);
+      }
+    }
+  }
+  __syncthreads();
+  float* out = partial + int64_t(blockIdx.x) * 2 * cols;
+  for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) out[c] = acc[c];
+}
+
 // dgamma / dbeta = column sums of the per-CTA partials.
 template <typename T>
 __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int cols,
@@ -249,9 +331,16 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(
-        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
-        static_cast<T*>(dx), partial);
+    constexpr int kVec = 16 / sizeof(T);
+    if (cols <= 32 * 4 * kVec) {
+      layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
+          static_cast<T*>(dx), partial);
+    } else {
+      layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
+          static_cast<T*>(dx), partial);
+    }
     layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
   })

@@ -12,15 +12,16 @@
 // the block-diagonal topology of the dropless MoE, the stk sdd / dsd kernels
 // (call sites: megablocks/layers/mlp.py:212-300, 414-523, glu.py:57-205).
 //
-// Structure per CTA (192 threads, one CTA per SM, tiles taken round-robin):
-//   warp 0      TMA producer: cp.async.bulk.tensor tile loads into a ring of
+// Structure per CTA (320 threads, one CTA per SM, tiles taken round-robin):
+//   warp 8      TMA producer: cp.async.bulk.tensor tile loads into a ring of
 //               128-byte-swizzled shared-memory stages, completion on mbarriers;
-//   warp 1      allocates tensor memory and issues tcgen05.mma (one elected lane);
+//   warp 9      allocates tensor memory and issues tcgen05.mma (one elected lane);
 //               tcgen05.commit releases ring stages and publishes accumulators;
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (two TMEM stages, so the
+//   warps 0-7   epilogue (two warps per TMEM lane quarter, interleaving 32-column chunks): tcgen05.ld the fp32 accumulator (two TMEM stages, so the
 //               next tile's MMAs overlap this tile's epilogue), apply the fused
 //               epilogue (activation, activation backward, GLU, GLU backward, add)
-//               and store bf16/fp16 rows with 16-byte stores, masked to the group.
+//               and move rows through a swizzled shared-memory staging buffer so
+//               global loads / stores are coalesced, masked to the group.
 // Operands may be K-major or MN-major in shared memory; MN-major tiles are loaded
 // as 64-column boxes and described to the MMA with the matching leading/stride
 // offsets, so no transposed copy of a weight or activation is ever made.
@@ -41,7 +42,10 @@ namespace gemm {
 using namespace ptx;
 
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;            // two warps per TMEM lane quarter
+constexpr int kProducerWarp = kEpilogueWarps;       // warp 8: TMA loads
+constexpr int kMmaWarp = kEpilogueWarps + 1;        // warp 9: TMEM allocation and tcgen05.mma
+constexpr int kThreads = (kEpilogueWarps + 2) * 32;
 constexpr int kABytes = kBlockM * kBlockK * 2;
 constexpr int kBoxBytes = 64 * kBlockK * 2;   // one 64-wide MN-major box
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -57,7 +61,8 @@ struct Config {
   static constexpr int kTmemCols = 2 * BLOCK_N;
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
   // ring + barriers + tmem base + abort flag + group tables, plus slack for 1024-byte alignment
-  static constexpr int kSmemBytes = kTileBytes + 256 + 2 * kMaxGroups * 4 + 1024;
+  static constexpr int kStagingBytes = kEpilogueWarps * 2048;   // one 32-row x 64-byte buffer per epilogue warp
+  static constexpr int kSmemBytes = kTileBytes + 256 + 2 * kMaxGroups * 4 + kStagingBytes + 1024;
 };
 
 struct Tile {
@@ -127,93 +132,194 @@ __device__ __forceinline__ float round_to(float v) {
   return to_float(from_float<T>(v));
 }
 
-// Fused epilogue on one row x 32 consecutive accumulator columns, specialised at
-// compile time on the epilogue kind and the activation.  `off` is the element
-// offset of the first column in the output; `cols` (a multiple of 8) is how many of
-// the 32 columns exist.
-template <typename T, int EPI, int ACT>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], int64_t off, int cols,
-                                               const GemmParams& p) {
+// ---- epilogue staging ------------------------------------------------------------
+// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns), so a
+// direct global store would touch 32 different cache lines per instruction.  Each
+// epilogue warp therefore owns a 32-row x 64-byte shared-memory buffer: rows are
+// written (or read) by their owner thread, and moved to / from global memory by the
+// whole warp as 8 rows x 64 contiguous bytes per instruction.  16-byte chunks are
+// XOR-swizzled with bits of the row so both access patterns are bank-conflict free.
+__device__ __forceinline__ uint32_t stage_offset(int row, int chunk) {
+  return uint32_t(row) * 64u + uint32_t((chunk ^ ((row >> 1) & 3)) * 16);
+}
+
+// Global [32 rows x 32 columns] (16-bit) -> staging, coalesced.  Rows >= rows_ok and
+// 8-column groups >= cols are skipped (their staging content is never used).
+template <typename T>
+__device__ __forceinline__ void stage_load(uint8_t* stage, const T* base, int64_t row_stride, int rows_ok,
+                                           int cols, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + (lane >> 2), q = lane & 3;
+    if (r < rows_ok && q * 8 < cols)
+      *reinterpret_cast<uint4*>(stage + stage_offset(r, q)) =
+          __ldg(reinterpret_cast<const uint4*>(base + int64_t(r) * row_stride + q * 8));
+  }
+}
+
+// Requests the cache lines of a chunk's auxiliary operand ahead of time (no registers
+// are held): the later `stage_load` of the same addresses then hits in cache.
+template <typename T>
+__device__ __forceinline__ void aux_prefetch(const T* base, int64_t row_stride, int rows_ok, int cols, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + (lane >> 2), q = lane & 3;
+    if (r < rows_ok && q * 8 < cols)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(base + int64_t(r) * row_stride + q * 8));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void stage_store(const uint8_t* stage, T* base, int64_t row_stride, int rows_ok,
+                                            int cols, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + (lane >> 2), q = lane & 3;
+    if (r < rows_ok && q * 8 < cols)
+      *reinterpret_cast<uint4*>(base + int64_t(r) * row_stride + q * 8) =
+          *reinterpret_cast<const uint4*>(stage + stage_offset(r, q));
+  }
+}
+
+// This thread's row of the staging buffer, kept packed (16 registers for 32 values).
+struct PackedRow {
+  uint4 q[4];
+};
+__device__ __forceinline__ void stage_read_row(const uint8_t* stage, int lane, PackedRow& out) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) out.q[v] = *reinterpret_cast<const uint4*>(stage + stage_offset(lane, v));
+}
+// Two 16-bit values <-> one 32-bit word, without taking the address of a register.
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  uint32_t out;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  uint32_t out;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+template <typename T>
+__device__ __forceinline__ float unpack_half(uint32_t word, int hi);
+template <>
+__device__ __forceinline__ float unpack_half<__nv_bfloat16>(uint32_t word, int hi) {
+  return __uint_as_float(hi ? (word & 0xffff0000u) : (word << 16));
+}
+template <>
+__device__ __forceinline__ float unpack_half<__half>(uint32_t word, int hi) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(hi ? (word >> 16) : (word & 0xffffu))));
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& q, int w) {
+  return w == 0 ? q.x : (w == 1 ? q.y : (w == 2 ? q.z : q.w));
+}
+template <typename T>
+__device__ __forceinline__ float packed_at(const PackedRow& row, int i) {
+  return unpack_half<T>(word_of(row.q[i >> 3], (i & 7) >> 1), i & 1);
+}
+
+// Element `i` of output number WHICH (0 = c, 1 = out2, 2 = out3) of the fused epilogue.
+template <typename T, int EPI, int ACT, int WHICH>
+__device__ __forceinline__ float epilogue_value(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
+                                                int i) {
+  const float acc = __uint_as_float(raw[i]);
+  if constexpr (EPI == kEpiNone) {
+    return acc;
+  } else if constexpr (EPI == kEpiAct) {
+    return WHICH == 0 ? acc : act_fwd<ACT>(round_to<T>(acc));
+  } else if constexpr (EPI == kEpiDAct) {
+    const float z = packed_at<T>(a1, i);
+    return WHICH == 0 ? acc * act_bwd<ACT>(z) : act_fwd<ACT>(z);
+  } else if constexpr (EPI == kEpiGlu) {
+    return WHICH == 0 ? acc : act_fwd<ACT>(packed_at<T>(a1, i)) * round_to<T>(acc);
+  } else if constexpr (EPI == kEpiDGlu) {
+    const float z1 = packed_at<T>(a1, i), z2 = packed_at<T>(a2, i);
+    if constexpr (WHICH == 0) return acc * z2 * act_bwd<ACT>(z1);
+    else if constexpr (WHICH == 1) return acc * act_fwd<ACT>(z1);
+    else return act_fwd<ACT>(z1) * z2;
+  } else {  // kEpiAdd
+    return acc + packed_at<T>(a1, i);
+  }
+}
+
+// Computes one output of the chunk, packs it eight columns at a time into this thread's
+// staging row and stores the chunk coalesced.  Only the accumulator row and the packed
+// auxiliary rows stay in registers.
+template <typename T, int EPI, int ACT, int WHICH>
+__device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
+                                              uint8_t* stage, T* out, int64_t row_stride, int rows_ok, int cols,
+                                              int lane) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
-    if (v * 8 >= cols) break;
-    const int64_t o = off + v * 8;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = __uint_as_float(raw[v * 8 + i]);
-    T* c = static_cast<T*>(p.c) + o;
-    if constexpr (EPI == kEpiNone) {
-      store8<T>(c, acc);
-    } else if constexpr (EPI == kEpiAct) {
-      float o2[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o2[i] = act_fwd<ACT>(round_to<T>(acc[i]));
-      store8<T>(c, acc);
-      if (p.out2) store8<T>(static_cast<T*>(p.out2) + o, o2);
-    } else if constexpr (EPI == kEpiDAct) {
-      float a1[8], o1[8], o2[8];
-      load8<T>(static_cast<const T*>(p.aux1) + o, a1);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        o1[i] = acc[i] * act_bwd<ACT>(a1[i]);
-        o2[i] = act_fwd<ACT>(a1[i]);
-      }
-      store8<T>(c, o1);
-      if (p.out2) store8<T>(static_cast<T*>(p.out2) + o, o2);
-    } else if constexpr (EPI == kEpiGlu) {
-      float a1[8], o2[8];
-      load8<T>(static_cast<const T*>(p.aux1) + o, a1);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o2[i] = act_fwd<ACT>(a1[i]) * round_to<T>(acc[i]);
-      store8<T>(c, acc);
-      if (p.out2) store8<T>(static_cast<T*>(p.out2) + o, o2);
-    } else if constexpr (EPI == kEpiDGlu) {
-      float a1[8], a2[8], o1[8], o2[8], o3[8];
-      load8<T>(static_cast<const T*>(p.aux1) + o, a1);
-      load8<T>(static_cast<const T*>(p.aux2) + o, a2);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float g = act_fwd<ACT>(a1[i]);
-        o1[i] = acc[i] * a2[i] * act_bwd<ACT>(a1[i]);
-        o2[i] = acc[i] * g;
-        o3[i] = g * a2[i];
-      }
-      store8<T>(c, o1);
-      if (p.out2) store8<T>(static_cast<T*>(p.out2) + o, o2);
-      if (p.out3) store8<T>(static_cast<T*>(p.out3) + o, o3);
-    } else {  // kEpiAdd
-      float a1[8], o1[8];
-      load8<T>(static_cast<const T*>(p.aux1) + o, a1);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o1[i] = acc[i] + a1[i];
-      store8<T>(c, o1);
-    }
+    uint4 w;
+    w.x = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 0),
+                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 1));
+    w.y = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 2),
+                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 3));
+    w.z = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 4),
+                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 5));
+    w.w = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 6),
+                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 7));
+    *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
+  }
+  __syncwarp();
+  stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
+  __syncwarp();
+}
+
+// Fused epilogue of one warp on a 32-row x 32-column chunk, specialised at compile time
+// on the epilogue kind and the activation.  `base_off` is the element offset of the
+// chunk's first row / first column in the output, `rows_ok` / `cols` its valid extent.
+template <typename T, int EPI, int ACT>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const PackedRow& a1,
+                                               const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                               int64_t row_stride, int rows_ok, int cols, int lane,
+                                               const GemmParams& p) {
+  epilogue_emit<T, EPI, ACT, 0>(raw, a1, a2, stage, static_cast<T*>(p.c) + base_off, row_stride, rows_ok, cols,
+                                lane);
+  if constexpr (EPI == kEpiAct || EPI == kEpiDAct || EPI == kEpiGlu || EPI == kEpiDGlu) {
+    if (p.out2)
+      epilogue_emit<T, EPI, ACT, 1>(raw, a1, a2, stage, static_cast<T*>(p.out2) + base_off, row_stride, rows_ok,
+                                    cols, lane);
+  }
+  if constexpr (EPI == kEpiDGlu) {
+    if (p.out3)
+      epilogue_emit<T, EPI, ACT, 2>(raw, a1, a2, stage, static_cast<T*>(p.out3) + base_off, row_stride, rows_ok,
+                                    cols, lane);
   }
 }
 
 template <typename T, int EPI>
-__device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], int64_t off, int cols,
+__device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], const PackedRow& a1,
+                                                const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                                int64_t row_stride, int rows_ok, int cols, int lane,
                                                 const GemmParams& p) {
   switch (p.act) {
-    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, off, cols, p); break;
-    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, off, cols, p); break;
-    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, off, cols, p); break;
-    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, off, cols, p); break;
-    default: epilogue_chunk<T, EPI, kActIdentity>(raw, off, cols, p); break;
+    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    default: epilogue_chunk<T, EPI, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
   }
 }
 
-// One dispatch per 32-column chunk; everything inside is straight-line code.
+// One dispatch per 32-column chunk (uniform across the warp); straight-line code inside.
 template <typename T>
-__device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], int64_t off, int cols,
+__device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], const PackedRow& a1,
+                                                  const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                                  int64_t row_stride, int rows_ok, int cols, int lane,
                                                   const GemmParams& p) {
   switch (p.epilogue) {
-    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, off, cols, p); break;
-    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, off, cols, p); break;
-    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, off, cols, p); break;
-    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, off, cols, p); break;
-    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, off, cols, p); break;
-    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, off, cols, p); break;
+    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
     default: break;
   }
 }
@@ -256,13 +362,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[s]), 4);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), kEpilogueWarps);
     }
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_base_slot), Cfg::kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_base_slot), Cfg::kTmemCols);
   __syncthreads();
   if (LAYOUT != kTN && threadIdx.x == 0) {
     int acc = 0, prev = 0;
@@ -314,7 +420,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     return tile;
   };
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     // ======================= TMA producer =======================================
     if (lane == 0) {
       int stage = 0;
@@ -375,7 +481,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ======================= MMA issuer ==========================================
     constexpr uint32_t idesc = instr_desc_f16(kIsBf16, kAMn, kBMn, kBlockM, BLOCK_N);
     int stage = 0;
@@ -439,29 +545,74 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
     }
-  } else {
+  } else if (warp < kEpilogueWarps) {
     // ======================= epilogue warps ======================================
     const int quarter = warp & 3;               // TMEM lane quarter this warp may read
-    const int row_in_tile = quarter * 32 + lane;
+    const int half = warp >> 2;                 // which of the two warps of that quarter
+    uint8_t* stage = smem + Cfg::kTileBytes + 256 + 2 * kMaxGroups * 4 + warp * 2048;
+    constexpr int kChunks = BLOCK_N / 32;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Tile tile = decode(t);
       const bool has_k = tile.k_len > 0;
+      // Rows of this warp's quarter that exist in the tile, and its first row's offset.
+      const int rows_ok = max(0, min(32, tile.rows_valid - quarter * 32));
+      int64_t row_off;
+      if constexpr (LAYOUT == kTN) row_off = (int64_t(tile.group) * p.M + tile.row0 + quarter * 32) * p.N;
+      else row_off = int64_t(tile.row0 + quarter * 32) * p.N;
+      // Auxiliary operands (pre-activations) are fetched one chunk ahead, the first one
+      // before the accumulator is even ready.
+      const bool need1 = p.epilogue == kEpiDAct || p.epilogue == kEpiGlu || p.epilogue == kEpiDGlu ||
+                         p.epilogue == kEpiAdd;
+      const bool need2 = p.epilogue == kEpiDGlu;
+      {
+        const int col = tile.n0 + half * 32;
+        if (rows_ok > 0 && col < p.N) {
+          if (need1) aux_prefetch<T>(static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok,
+                                     min(32, p.N - col), lane);
+          if (need2) aux_prefetch<T>(static_cast<const T*>(p.aux2) + row_off + col, p.N, rows_ok,
+                                     min(32, p.N - col), lane);
+        }
+      }
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc_stage]), acc_phase, abort_flag, p.status, kErrEpilogue,
                      kWaitLimitNs);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const bool row_ok = row_in_tile < tile.rows_valid;
-      int64_t row_off;
-      if constexpr (LAYOUT == kTN) row_off = (int64_t(tile.group) * p.M + tile.row0 + row_in_tile) * p.N;
-      else row_off = int64_t(tile.row0 + row_in_tile) * p.N;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc_stage * BLOCK_N;
+      // The two warps of a quarter interleave 32-column chunks.
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
-        if (tile.n0 + c0 >= p.N) break;          // uniform across the warp
+      for (int ci = half; ci < kChunks; ci += 2) {
+        const int c0 = ci * 32;
+        const int col = tile.n0 + c0;
+        if (col >= p.N) break;                   // uniform across the warp
+        // Ask for the next chunk's auxiliary operands, then bring this chunk's through the
+        // staging buffer (coalesced read, each thread picks up its own row).
+        if (ci + 2 < kChunks && rows_ok > 0 && col + 64 < p.N) {
+          const int ncol = col + 64;
+          if (need1) aux_prefetch<T>(static_cast<const T*>(p.aux1) + row_off + ncol, p.N, rows_ok,
+                                     min(32, p.N - ncol), lane);
+          if (need2) aux_prefetch<T>(static_cast<const T*>(p.aux2) + row_off + ncol, p.N, rows_ok,
+                                     min(32, p.N - ncol), lane);
+        }
+        PackedRow a1, a2;
+        if (rows_ok > 0) {
+          const int cols = min(32, p.N - col);
+          if (need1) {
+            stage_load<T>(stage, static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok, cols, lane);
+            __syncwarp();
+            stage_read_row(stage, lane, a1);
+            __syncwarp();
+          }
+          if (need2) {
+            stage_load<T>(stage, static_cast<const T*>(p.aux2) + row_off + col, p.N, rows_ok, cols, lane);
+            __syncwarp();
+            stage_read_row(stage, lane, a2);
+            __syncwarp();
+          }
+        }
         uint32_t raw[32];
         if (has_k) {
           tmem_ld_32x32(taddr + c0, raw);
@@ -470,10 +621,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i) raw[i] = 0u;
         }
-        if (row_ok) {
-          const int col = tile.n0 + c0;
-          epilogue_dispatch<T>(raw, row_off + col, min(32, p.N - col), p);
-        }
+        if (rows_ok > 0)
+          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -484,8 +633,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (LAYOUT != kTN && p.zero_tail) {
       const int last = G > 0 ? s_row_end[G - 1] : 0;
       const int64_t begin = int64_t(last) * p.N, end = int64_t(p.rows_total) * p.N;
-      const int64_t tid = int64_t(blockIdx.x) * 128 + (threadIdx.x - 64);
-      const int64_t stride = int64_t(gridDim.x) * 128;
+      const int64_t tid = int64_t(blockIdx.x) * (kEpilogueWarps * 32) + threadIdx.x;
+      const int64_t stride = int64_t(gridDim.x) * (kEpilogueWarps * 32);
       for (int64_t i = begin + tid * 8; i < end; i += stride * 8) {
         const uint4 z = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(static_cast<T*>(p.c) + i) = z;
@@ -498,7 +647,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   // ---- teardown -----------------------------------------------------------------
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     if (*abort_flag != 0) {
       // Give loads and MMAs that were already in flight time to land before the
       // tensor memory and the shared memory are released.
