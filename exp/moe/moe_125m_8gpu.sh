@@ -1,0 +1,18 @@
+#!/bin/bash
+# Token-dropping MoE, 125m backbone, 8 GPUs
+# Counterpart of the reference's exp/moe/moe_125m_8gpu.sh: same model, batch (512 x 1024 tokens per
+# step on 8 GPUs), optimizer and schedule, run by this library's own trainer on
+# synthetic tokens (no dataset is needed).
+#
+#   bash exp/moe/moe_125m_8gpu.sh [steps] [experts] [top_k] [loss_weight] [micro_batch]
+set -e
+STEPS=${1:-20000}
+EXPERTS=${2:-64}
+TOP_K=${3:-1}
+LOSS_WEIGHT=${4:-0.1}
+MICRO_BATCH=${5:-32}
+GPUS=${GPUS:-8}
+cd "$(dirname "$0")/../.."
+python -m torch.distributed.run --nnodes=1 --nproc-per-node "$GPUS" --master-addr 127.0.0.1 --master-port 29500 \
+    -m megablocks_b200.train --preset dmoe-125m --steps "$STEPS" --experts "$EXPERTS" --top-k "$TOP_K" \
+    --loss-weight "$LOSS_WEIGHT" --micro-batch "$MICRO_BATCH" --lr 1.5e-4 --min-lr 1e-5 --capacity-factor ${CAPACITY_FACTOR:-1} "${@:6}"

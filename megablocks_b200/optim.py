@@ -48,6 +48,8 @@ class FusedAdam:
         self.norm_weights = list(norm_weights) if norm_weights is not None else [1.0] * len(self.params)
         if not self.params:
             self.device = torch.device('cpu')
+            self.offsets = []
+            self.master = self.exp_avg = self.exp_avg_sq = torch.zeros(0)
             return
         self.device = self.params[0].device
         self.dtype = self.params[0].dtype
@@ -152,6 +154,8 @@ class FusedAdam:
     def load_state_dict(self, state):
         self.step_count = int(state['step'])
         self.lr = state.get('lr', self.lr)
+        if not self.params:
+            return
         for name in ('master', 'exp_avg', 'exp_avg_sq'):
             getattr(self, name).copy_(state[name])
         for p, off in zip(self.params, self.offsets):

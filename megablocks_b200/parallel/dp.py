@@ -120,18 +120,18 @@ class GradReducer:
         else:
             ctx = _NullContext()
         with ctx:
-            if self.shard:
+            if self.shard and grad.is_cuda:
                 lo, hi = self.shard_range(bi)
                 out = self.flat.grad[lo:hi]
-                work = dist.reduce_scatter_tensor(out, grad, op=_avg_op(grad), group=self.group, async_op=True)
+                work = dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG, group=self.group, async_op=True)
+                self._works.append((work, grad))
+            elif grad.is_cuda:
+                work = dist.all_reduce(grad, op=dist.ReduceOp.AVG, group=self.group, async_op=True)
+                self._works.append((work, grad))
             else:
-                work = dist.all_reduce(grad, op=_avg_op(grad), group=self.group, async_op=True)
-            self._works.append((work, grad))
-            if not _has_avg(grad):
-                # gloo has no AVG: divide after the sum completes.
-                work.wait()
-                (self.flat.grad[self.shard_range(bi)[0]:self.shard_range(bi)[1]] if self.shard else grad).div_(
-                    self.world)
+                # CPU ranks (gloo): no AVG and no reduce-scatter; sum everything, then divide.
+                dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group)
+                grad.div_(self.world)
 
     def finish(self) -> None:
         """Launch whatever backward did not trigger, then make the current stream wait for all buckets."""
@@ -150,15 +150,12 @@ class GradReducer:
         assert self.shard
         for bi, (s, e, _, _) in enumerate(self.buckets):
             lo, hi = self.shard_range(bi)
-            dist.all_gather_into_tensor(self.flat.param[s:e], self.flat.param[lo:hi].clone(), group=self.group)
-
-
-def _has_avg(t: torch.Tensor) -> bool:
-    return t.is_cuda
-
-
-def _avg_op(t: torch.Tensor):
-    return dist.ReduceOp.AVG if _has_avg(t) else dist.ReduceOp.SUM
+            mine = self.flat.param[lo:hi].clone()
+            if mine.is_cuda:
+                dist.all_gather_into_tensor(self.flat.param[s:e], mine, group=self.group)
+            else:
+                pieces = list(self.flat.param[s:e].chunk(self.world))
+                dist.all_gather(pieces, mine, group=self.group)
 
 
 class _NullContext:

@@ -141,3 +141,112 @@ def synthetic_batch(micro_batch: int, seq_len: int, vocab_size: int, generator: 
     """Uniform-random token ids ``[micro_batch, seq_len + 1]`` in (pinned) host memory."""
     batch = torch.randint(0, vocab_size, (micro_batch, seq_len + 1), generator=generator, dtype=torch.int64)
     return batch.pin_memory() if pin and torch.cuda.is_available() else batch
+
+
+# ---------------------------------------------------------------------------
+# Command line: python -m megablocks_b200.train --preset dmoe-125m ...
+# ---------------------------------------------------------------------------
+def main(argv=None):
+    import argparse
+    import os
+
+    from megablocks_b200 import checkpoint
+    from megablocks_b200.models.transformer import MoETransformer, PRESETS, preset
+    from megablocks_b200.utils import status
+    from megablocks_b200.utils.health import Heartbeat
+    from megablocks_b200.utils.metrics import JsonlLogger, expert_load_stats, nvtx_range
+
+    ap = argparse.ArgumentParser(description='Train a dMoE / MoE transformer on synthetic tokens.')
+    ap.add_argument('--preset', choices=sorted(PRESETS), default='dmoe-125m')
+    ap.add_argument('--micro-batch', type=int, default=32)
+    ap.add_argument('--steps', type=int, default=100)
+    ap.add_argument('--experts', type=int, default=None)
+    ap.add_argument('--top-k', type=int, default=None)
+    ap.add_argument('--loss-weight', type=float, default=0.1)
+    ap.add_argument('--capacity-factor', type=int, default=None, help='token-dropping MoE with this capacity factor')
+    ap.add_argument('--mlp-impl', choices=['grouped', 'sparse'], default='grouped')
+    ap.add_argument('--lr', type=float, default=6e-4)
+    ap.add_argument('--min-lr', type=float, default=6e-5)
+    ap.add_argument('--zero1', action='store_true', help='shard the optimizer state of the replicated parameters')
+    ap.add_argument('--recompute', action='store_true', help='activation checkpointing of every block')
+    ap.add_argument('--ep-comm', choices=['auto', 'fused', 'nccl'], default='auto')
+    ap.add_argument('--log', type=str, default=None, help='JSONL metrics file')
+    ap.add_argument('--log-interval', type=int, default=10)
+    ap.add_argument('--save', type=str, default=None, help='checkpoint directory')
+    ap.add_argument('--save-interval', type=int, default=0)
+    ap.add_argument('--load', type=str, default=None)
+    ap.add_argument('--seed', type=int, default=1234)
+    args = ap.parse_args(argv)
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    use_cuda = torch.cuda.is_available()
+    device = torch.device('cuda', local) if use_cuda else torch.device('cpu')
+    if use_cuda:
+        torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        os.environ.setdefault('MASTER_PORT', '29500')
+        dist.init_process_group('nccl' if use_cuda else 'gloo', rank=rank, world_size=world)
+        group = dist.group.WORLD
+
+    torch.manual_seed(args.seed)
+    overrides = dict(device=device, expert_parallel_group=group, mlp_impl=args.mlp_impl,
+                     moe_loss_weight=args.loss_weight, activation_checkpointing=args.recompute,
+                     ep_fused_comm={'auto': None, 'fused': True, 'nccl': False}[args.ep_comm],
+                     dtype=torch.bfloat16 if use_cuda else torch.float32)
+    if args.experts is not None:
+        overrides['moe_num_experts'] = args.experts
+    if args.top_k is not None:
+        overrides['moe_top_k'] = args.top_k
+    if args.capacity_factor is not None:
+        overrides.update(dropless=False, moe_capacity_factor=args.capacity_factor)
+    cfg = preset(args.preset, **overrides)
+    model = MoETransformer(cfg)
+    trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1),
+                      dp_group=group)
+    if args.load:
+        state = checkpoint.load(args.load, rank, world, map_location=device)
+        model.load_state_dict(state['model'])
+        if 'dense_opt' in state:
+            trainer.load_state_dict(state)
+    logger = JsonlLogger(args.log, rank)
+    heartbeat = Heartbeat(timeout_s=60.0) if world > 1 else None
+    gen = torch.Generator().manual_seed(args.seed + rank)
+    tokens_per_step = world * args.micro_batch * cfg.max_seq_len
+    t_last, loss = time.time(), None
+    for step in range(trainer.step_count, args.steps):
+        if heartbeat is not None:
+            heartbeat.check()
+        batch = synthetic_batch(args.micro_batch, cfg.max_seq_len, cfg.vocab_size, gen)
+        with nvtx_range('train_step'):
+            dev = batch.to(device, non_blocking=True)
+            loss = trainer.step(dev[:, :-1], dev[:, 1:])
+        if heartbeat is not None:
+            heartbeat.beat()
+        if (step + 1) % args.log_interval == 0 or step + 1 == args.steps:
+            value = float(loss)                      # the only host sync of the interval
+            if use_cuda:
+                status.check()
+            now = time.time()
+            rate = tokens_per_step * args.log_interval / max(now - t_last, 1e-9)
+            t_last = now
+            logger.log(step=step + 1, loss=value, grad_norm=trainer.last_grad_norm, tokens_per_s=rate,
+                       lr=trainer.dense_opt.lr)
+            if rank == 0:
+                print(f'step {step + 1:6d}  loss {value:8.4f}  grad-norm {float(trainer.last_grad_norm):7.3f}  '
+                      f'{rate:12.0f} tokens/s', flush=True)
+        if args.save and args.save_interval and (step + 1) % args.save_interval == 0:
+            checkpoint.save(args.save, trainer.state_dict(), rank, world, cfg.moe_num_experts, step + 1)
+    if args.save:
+        checkpoint.save(args.save, trainer.state_dict(), rank, world, cfg.moe_num_experts, trainer.step_count)
+    logger.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return loss
+
+
+if __name__ == '__main__':
+    main()

@@ -15,6 +15,11 @@ _MESSAGES = {
     2: 'grouped GEMM: MMA warp timed out waiting for a TMA tile',
     3: 'grouped GEMM: MMA warp timed out waiting for a free accumulator',
     4: 'grouped GEMM: epilogue timed out waiting for an accumulator',
+    16: 'expert-parallel count exchange: a peer never published its counts',
+    17: 'expert-parallel receive buffer overflow: more rows were routed to this rank than the buffer holds',
+    18: 'grouped GEMM: rows of an expert never arrived from a peer (dispatch flag not released)',
+    19: 'expert-parallel combine: a peer never returned its rows',
+    20: 'expert-parallel dispatch: a peer never released its receive buffer',
 }
 
 
