@@ -159,14 +159,26 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
     const T* src = x + int64_t(copy / top_k) * cols;
     T* dst = peer_ptr<T>(data_base, owner, off_recv) + int64_t(dst_start[e] + (i - src_start[e])) * cols;
     const float scale = weights != nullptr ? to_float(weights[copy]) : 1.f;
-    for (int c = lane * VEC; c < cols; c += 32 * VEC) {
-      uint4 raw = *reinterpret_cast<const uint4*>(src + c);
-      if (weights != nullptr) {
-        T* v = reinterpret_cast<T*>(&raw);
+    // Four 16-byte loads in flight per lane before the first (remote) store.
+    for (int c0 = lane * VEC; c0 < cols; c0 += 4 * 32 * VEC) {
+      uint4 raw[4];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) v[k] = from_float<T>(to_float(v[k]) * scale);
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32 * VEC;
+        if (c < cols) raw[j] = *reinterpret_cast<const uint4*>(src + c);
       }
-      *reinterpret_cast<uint4*>(dst + c) = raw;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32 * VEC;
+        if (c < cols) {
+          if (weights != nullptr) {
+            T* v = reinterpret_cast<T*>(&raw[j]);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] = from_float<T>(to_float(v[k]) * scale);
+          }
+          *reinterpret_cast<uint4*>(dst + c) = raw[j];
+        }
+      }
     }
     __syncwarp();
     if (lane == 0) {
@@ -230,8 +242,19 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
     const int remote_row = remote_start[lo] + (row - seg_begin);
     const T* src = y + int64_t(row) * cols;
     T* dst = peer_ptr<T>(data_base, s, off_ret) + int64_t(remote_row) * cols;
-    for (int c = lane * VEC; c < cols; c += 32 * VEC)
-      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+    for (int c0 = lane * VEC; c0 < cols; c0 += 4 * 32 * VEC) {
+      uint4 raw[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32 * VEC;
+        if (c < cols) raw[j] = *reinterpret_cast<const uint4*>(src + c);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32 * VEC;
+        if (c < cols) *reinterpret_cast<uint4*>(dst + c) = raw[j];
+      }
+    }
     __syncwarp();
     if (lane == 0) {
       __threadfence_system();

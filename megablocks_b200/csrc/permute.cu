@@ -77,7 +77,16 @@ gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, con
   }
   const T* src = x + int64_t(src_token) * cols;
   if (weights == nullptr) {
-    for (int c = lane * VEC; c < cols; c += 32 * VEC) store_pack<T, VEC>(dst + c, load_pack<T, VEC>(src + c));
+    // Four vector loads in flight per lane before the first store.
+    for (int c0 = lane * VEC; c0 < cols; c0 += 4 * 32 * VEC) {
+      Pack<T, VEC> p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c0 + j * 32 * VEC < cols) p[j] = load_pack<T, VEC>(src + c0 + j * 32 * VEC);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c0 + j * 32 * VEC < cols) store_pack<T, VEC>(dst + c0 + j * 32 * VEC, p[j]);
+    }
   } else {
     for (int c = lane * VEC; c < cols; c += 32 * VEC) {
       Pack<T, VEC> p = load_pack<T, VEC>(src + c);
