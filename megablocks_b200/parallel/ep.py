@@ -119,6 +119,7 @@ class EpWorkspace:
         self.recv_dy = self.bwd_heap.view(self.off_recv_dy, (self.capacity, hidden), dtype)
         self.ret_dx = self.bwd_heap.view(self.off_ret_dx, (copies, hidden), dtype)
         self.seq = 0
+        self.released_seq = 0
 
     # -- geometry passed to the kernels -------------------------------------------------
     def _layout(self):
@@ -174,7 +175,21 @@ class EpWorkspace:
 
     def release_receive_buffer(self, seq: int) -> None:
         """Publish that every read of the forward receive buffer of use ``seq`` has been issued."""
-        ext().ep_set_flag(self.flags(self.off_free, 1), seq)
+        if seq > self.released_seq:
+            ext().ep_set_flag(self.flags(self.off_free, 1), seq)
+            self.released_seq = seq
+
+    def begin_use(self, seq: int) -> None:
+        """Called at the start of use ``seq`` of the forward receive buffer.
+
+        Normally the backward pass of use ``seq - 1`` has already released the buffer.  When
+        that backward never runs - the forward was the first pass of an activation-checkpointed
+        block, whose graph is dropped and recomputed - the release happens here: everything of
+        this rank that read the old contents was enqueued on this stream before.  (A backward
+        pass of an older use that arrives after a newer forward, as in interleaved pipeline
+        schedules, is not supported with one workspace per layer.)
+        """
+        self.release_receive_buffer(seq - 1)
 
 
 class _FusedExpertParallel(torch.autograd.Function):
@@ -184,6 +199,7 @@ class _FusedExpertParallel(torch.autograd.Function):
     def forward(ctx: Any, x, expert_weights, w1, w2, v1, ws: EpWorkspace, indices, bin_ids, bins, tpe, top_k: int,
                 act: int, keep_h: bool):
         seq = ws.next_seq()
+        ws.begin_use(seq)
         x = x.contiguous()
         tokens = x.shape[0]
         counts, recv_bins, done = ws.exchange_counts(tpe, seq)

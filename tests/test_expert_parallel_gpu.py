@@ -47,7 +47,11 @@ def _worker(rank, world, port, kw, out_dir):
             for _ in range(2):   # two steps: sequence numbers and buffer reuse
                 layer.zero_grad(set_to_none=True)
                 x.grad = None
-                out = layer(x)
+                if kw.get('checkpoint'):
+                    from torch.utils.checkpoint import checkpoint
+                    out = checkpoint(layer, x, use_reentrant=False)
+                else:
+                    out = layer(x)
                 (out.float() * probe.float()).sum().backward()
                 outs.append(out.detach().float().cpu())
             torch.cuda.synchronize()
@@ -64,6 +68,7 @@ def _worker(rank, world, port, kw, out_dir):
     dict(top_k=1, mlp_type='mlp', mem_opt=True, tokens=512),
     dict(top_k=2, mlp_type='mlp', mem_opt=False, tokens=300),
     dict(top_k=2, mlp_type='glu', mem_opt=True, tokens=1024),
+    dict(top_k=2, mlp_type='mlp', mem_opt=True, tokens=256, checkpoint=True),   # recomputed forward
 ])
 def test_fused_matches_all_to_all(kw, tmp_path):
     world = min(torch.cuda.device_count(), 4)
