@@ -150,9 +150,13 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
   __syncthreads();
   if (!free_ok) return;
   const int lane = threadIdx.x & 31;
-  const int warps_total = gridDim.x * kPushWarps;
   constexpr int VEC = 16 / sizeof(T);
-  for (int i = blockIdx.x * kPushWarps + (threadIdx.x >> 5); i < n; i += warps_total) {
+  // Every CTA owns one contiguous range of sorted positions: it touches few experts, and
+  // one system-scope fence per CTA (instead of one per row) orders all its stores before
+  // the completion counters and flags.
+  const int per_cta = (n + gridDim.x - 1) / gridDim.x;
+  const int begin = min(n, blockIdx.x * per_cta), end = min(n, begin + per_cta);
+  for (int i = begin + (threadIdx.x >> 5); i < end; i += kPushWarps) {
     const int e = upper_bound_i32(bins, E, i);
     const int owner = e / epr;
     const int copy = __ldg(indices + i);
@@ -180,12 +184,20 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
+  }
+  __syncthreads();
+  if (end > begin && threadIdx.x == 0) {
+    __threadfence_system();
+    const int e_first = upper_bound_i32(bins, E, begin), e_last = upper_bound_i32(bins, E, end - 1);
+    for (int e = e_first; e <= e_last; ++e) {
+      const int lo = max(begin, src_start[e]), hi = min(end, bins[e]);
+      if (hi <= lo) continue;
       const int total = bins[e] - src_start[e];
-      if (atomicAdd(done + e, 1) + 1 == total)
+      if (atomicAdd(done + e, hi - lo) + (hi - lo) == total) {
+        __threadfence_system();   // other CTAs' rows of this expert were fenced before their adds
+        const int owner = e / epr;
         st_release_sys(peer_ptr<int>(L.peer_base, owner, off_flags) + L.rank * epr + (e - owner * epr), seq);
+      }
     }
   }
 }
@@ -228,9 +240,11 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
   __syncthreads();
   const int total = seg_end[epr * W - 1];
   const int lane = threadIdx.x & 31;
-  const int warps_total = gridDim.x * kPushWarps;
   constexpr int VEC = 16 / sizeof(T);
-  for (int row = blockIdx.x * kPushWarps + (threadIdx.x >> 5); row < total; row += warps_total) {
+  // Contiguous row range per CTA; one system-scope fence per CTA (see push_rows_kernel).
+  const int per_cta = (total + gridDim.x - 1) / gridDim.x;
+  const int begin = min(total, blockIdx.x * per_cta), end = min(total, begin + per_cta);
+  for (int row = begin + (threadIdx.x >> 5); row < end; row += kPushWarps) {
     // Segment of this row: first (j, s) whose end exceeds it.
     int lo = 0, hi = epr * W;
     while (lo < hi) {
@@ -255,11 +269,29 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
         if (c < cols) *reinterpret_cast<uint4*>(dst + c) = raw[j];
       }
     }
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      if (atomicAdd(done + s, 1) + 1 == per_source[s])
+  }
+  __syncthreads();
+  if (end > begin && threadIdx.x == 0) {
+    __threadfence_system();
+    int seg = 0;
+    {
+      int lo = 0, hi = epr * W;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_end[mid] <= begin) lo = mid + 1; else hi = mid;
+      }
+      seg = lo;
+    }
+    for (; seg < epr * W; ++seg) {
+      const int seg_begin = seg ? seg_end[seg - 1] : 0;
+      if (seg_begin >= end) break;
+      const int lo = max(begin, seg_begin), hi = min(end, seg_end[seg]);
+      if (hi <= lo) continue;
+      const int s = seg % W;
+      if (atomicAdd(done + s, hi - lo) + (hi - lo) == per_source[s]) {
+        __threadfence_system();
         st_release_sys(peer_ptr<int>(L.peer_base, s, off_flags) + L.rank, seq);
+      }
     }
   }
 }
