@@ -161,8 +161,10 @@ struct GemmParams {
 
 // block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit
 // matrices with 64-column boxes and 128-byte swizzle.
+// `pair`: run the CTA-pair kernel (cta_group::2, 256-row tiles; NT / NN with block_n 256, even
+// grid; the B tensor map must then have 128-row boxes for NT).
 cudaError_t launch(bool bf16, int layout, int block_n, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
-                   const GemmParams& params, int grid, cudaStream_t stream);
+                   const GemmParams& params, int grid, cudaStream_t stream, bool pair = false);
 
 }  // namespace gemm
 }  // namespace mb

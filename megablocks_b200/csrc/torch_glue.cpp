@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -454,7 +455,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool want_out2, bool want_out3, int64_t num_groups,
                                      const c10::optional<at::Tensor>& c_in, bool zero_tail,
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
-                                     int64_t wait_stride, int64_t wait_seq) {
+                                     int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -521,9 +522,26 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   if (out_numel == 0) return {c, out2, out3};
 
   const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
+  // CTA pairs (256-row tiles, six 32 KB stages per CTA) hide more load latency but waste up to
+  // 255 rows per group; measured, they win once groups are a few thousand rows long.
+  // pair_mode: -1 = decide here, 0 = never, 1 = whenever the kernel supports the problem.
+  const int64_t rows_expected = rows_hint > 0 ? rows_hint : a.size(0);
+  bool pair = layout != kTN && block_n == 256 && sm_count() >= 2;
+  if (pair_mode == 0) pair = false;
+  else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048;
   CUtensorMap ta, tb;
   int64_t tiles_bound;
   const int64_t num_nb = ceil_div(p.N, block_n);
+  if (pair) {
+    ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
+    tb = layout == kNT ? make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n / 2)
+                       : make_tensor_map(b.data_ptr(), bf16, num_groups * p.K, p.N, 64);
+    tiles_bound = (ceil_div(a.size(0), 2 * kBlockM) + num_groups) * num_nb;
+    const int pairs = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count() / 2)));
+    MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, 2 * pairs, stream(), true));
+    MB_LAUNCHED(1);
+    return {c, out2, out3};
+  }
   if (layout == kNT) {
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
     tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n);

@@ -27,9 +27,10 @@ import torch
 from megablocks_b200.ops import gg as G
 
 
-def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tail: bool = True):
+def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tail: bool = True,
+                rows_hint: int = 0):
     """Forward GEMMs.  Returns ``(y, saved)`` where ``saved = (z1, z2, h or None)``."""
-    kw = dict(zero_tail=zero_tail)
+    kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
     if v1 is not None:
         z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=True, wait=wait, **kw)
         z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=z1, **kw)
@@ -40,11 +41,12 @@ def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tai
     return y, (z1, z2, h if keep_h else None)
 
 
-def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True):
+def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True,
+                 rows_hint: int = 0):
     """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded)."""
     z1, z2, h = saved
     num_experts = w1.shape[0]
-    kw = dict(zero_tail=zero_tail)
+    kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
     if v1 is not None:
         dz1, dz2, h_new = G.grouped_gemm(dy, w2, bins, trans_b=True, epilogue=G.EPI_DGLU, act=act, aux1=z1,
                                          aux2=z2, want_out3=h is None, wait=wait, **kw)

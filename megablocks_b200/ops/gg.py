@@ -22,6 +22,7 @@ epilogue (activation, activation backward, GLU product, GLU backward).  On
 CPU they run per-group ``torch.matmul`` in fp32, which is also the oracle.
 """
 
+import os
 from functools import partial
 from typing import Any, Callable, Optional, Tuple
 
@@ -51,6 +52,11 @@ _ACT_NAMES = {
     'relu': ACT_RELU,
     'gelu': ACT_GELU_ERF,
 }
+
+
+# CTA-pair (cta_group::2) kernel selection: -1 = automatic (groups of >= 2048 rows on average),
+# 0 = never, 1 = whenever supported.  Overridable for experiments with MB200_GEMM_PAIR.
+_PAIR_MODE = int(os.environ.get('MB200_GEMM_PAIR', '-1'))
 
 
 def activation_id(fn: Optional[Callable]) -> Optional[int]:
@@ -173,7 +179,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  trans_b: bool = False, epilogue: int = EPI_NONE, act: int = ACT_IDENTITY,
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
-                 c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None):
+                 c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
+                 rows_hint: int = 0):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -183,6 +190,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     ``wait = (flags, count, stride, seq)`` makes the kernel's load warp wait, per
     group ``g``, until ``flags[s * stride + g] >= seq`` for every ``s < count``: the
     rows of ``a`` are then being delivered by peer GPUs (expert-parallel dispatch).
+    ``rows_hint`` is the expected number of occupied rows when ``a`` is a worst-case sized
+    buffer (it only steers the choice between the single-CTA and the CTA-pair kernel).
     """
     if num_groups is None:
         num_groups = bins.numel()
@@ -190,7 +199,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
         flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
-                                  int(count), int(stride), int(seq))
+                                  int(count), int(stride), int(seq), int(rows_hint), _PAIR_MODE)
     if wait is not None:
         raise RuntimeError('grouped_gemm: peer-arrival waits need the CUDA kernel (unsupported shape or dtype)')
     # Shapes or dtypes the tensor-core kernel does not take (fp32 inputs, rows that

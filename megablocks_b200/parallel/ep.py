@@ -205,7 +205,7 @@ class _FusedExpertParallel(torch.autograd.Function):
         counts, recv_bins, done = ws.exchange_counts(tpe, seq)
         ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0])
         y, saved = mlp_forward(ws.recv_x, w1, w2, v1, recv_bins, act, keep_h, wait=ws.arrival(0, seq),
-                               zero_tail=False)
+                               zero_tail=False, rows_hint=ws.copies)
         ws.return_rows(y, counts, 0, seq, done[1])
         ws.wait_return(0, seq)
         out = ext().scatter_rows(ws.ret_y, indices, bin_ids, expert_weights, bins, bins, top_k, tokens)
@@ -244,7 +244,8 @@ class _FusedExpertParallel(torch.autograd.Function):
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3],
                  ctx.glu and ctx.needs_input_grad[4])
         dxr, dw1, dw2, dv1 = mlp_backward(ws.recv_dy, ws.recv_x, w1, w2, v1, recv_bins, ctx.act, (z1, z2, h),
-                                          (True,) + needs[1:], wait=ws.arrival(1, seq), zero_tail=False)
+                                          (True,) + needs[1:], wait=ws.arrival(1, seq), zero_tail=False,
+                                          rows_hint=ws.copies)
         # Every read of both receive buffers is enqueued above; only now may peers learn
         # (through the return flags / the free flag) that they can be overwritten.
         ws.return_rows(dxr, counts, 1, seq, done_ret)

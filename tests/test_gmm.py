@@ -144,3 +144,44 @@ def test_activation_id():
         zz = torch.randn(1000, dtype=torch.float64, requires_grad=True)
         G.act_forward(zz, act).sum().backward()
         torch.testing.assert_close(G.act_derivative(zz.detach(), act), zz.grad, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_cta_pair_kernel_matches_reference():
+    """The cta_group::2 kernel (256-row tiles on CTA pairs), forced on through its environment switch."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from megablocks_b200.ops import gg as G
+from megablocks_b200.utils import status
+torch.manual_seed(0)
+dev = 'cuda'
+for z, m, k, n in [(1, 128, 128, 256), (3, 1000, 192, 320), (5, 3000, 256, 512), (8, 8192, 768, 3072)]:
+    counts = torch.bincount(torch.randint(0, z, (m,)), minlength=z)
+    bins = torch.cumsum(counts, 0).int().to(dev)
+    a = (torch.randn(m, k) * 0.5).bfloat16().to(dev)
+    for trans_b in (True, False):
+        b = (torch.randn(z, n, k) if trans_b else torch.randn(z, k, n)).mul(0.1).bfloat16().to(dev)
+        aux = torch.randn(m, n).bfloat16().to(dev)
+        out, h, _ = G.grouped_gemm(a, b, bins, trans_b=trans_b, epilogue=G.EPI_DACT, act=G.ACT_GELU_TANH, aux1=aux)
+        ref, start = [], 0
+        for e, c in enumerate(counts.tolist()):
+            w = b[e].float()
+            ref.append(a[start:start + c].float() @ (w.t() if trans_b else w))
+            start += c
+        ref = torch.cat(ref).cpu()
+        zz = aux.float().cpu().requires_grad_(True)
+        G.act_forward(zz, G.ACT_GELU_TANH).sum().backward()
+        want = ref * zz.grad
+        torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=1e-2 * float(want.abs().max()) + 1e-3)
+        torch.testing.assert_close(h.float().cpu(), G.act_forward(aux.float().cpu(), G.ACT_GELU_TANH), rtol=2e-2, atol=2e-2)
+status.check()
+print('PAIR-OK')
+'''
+    env = dict(os.environ, MB200_GEMM_PAIR='1')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env['PYTHONPATH'] = root + os.pathsep + env.get('PYTHONPATH', '')
+    res = subprocess.run([sys.executable, '-c', code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and 'PAIR-OK' in res.stdout, res.stderr[-2000:]
