@@ -47,7 +47,9 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool want_out2, bool want_out3, int64_t num_groups,
                                      const c10::optional<at::Tensor>& c_in, bool zero_tail,
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
-                                     int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode);
+                                     int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
+                                     const c10::optional<std::vector<at::Tensor>>& scatter,
+                                     const std::vector<int64_t>& scatter_args);
 int64_t read_status(bool clear);
 int64_t launch_count();
 

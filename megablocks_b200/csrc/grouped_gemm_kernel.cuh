@@ -42,6 +42,7 @@ namespace gemm {
 using namespace ptx;
 
 constexpr int kUmmaK = 16;
+constexpr int kMaxScatterSegments = 512;     // experts per rank x world of the fused combine
 constexpr int kEpilogueWarps = 8;            // two warps per TMEM lane quarter
 constexpr int kProducerWarp = kEpilogueWarps;       // warp 8: TMA loads
 constexpr int kMmaWarp = kEpilogueWarps + 1;        // warp 9: TMEM allocation and tcgen05.mma
@@ -62,7 +63,8 @@ struct Config {
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
   // ring + barriers + tmem base + abort flag + group tables, plus slack for 1024-byte alignment
   static constexpr int kStagingBytes = kEpilogueWarps * 2048;   // one 32-row x 64-byte buffer per epilogue warp
-  static constexpr int kSmemBytes = kTileBytes + 256 + 2 * kMaxGroups * 4 + kStagingBytes + 1024;
+  static constexpr int kScatterBytes = (2 * kMaxScatterSegments + 128) * 4;   // segment tables of the fused combine
+  static constexpr int kSmemBytes = kTileBytes + 256 + 2 * kMaxGroups * 4 + kStagingBytes + kScatterBytes + 1024;
 };
 
 struct Tile {
@@ -191,6 +193,24 @@ __device__ __forceinline__ void stage_store(const uint8_t* stage, T* base, int64
   }
 }
 
+// Row targets of the fused combine: where the four rows this lane stores (rows i * 8 + lane / 4
+// of the warp's 32-row quarter) live in the peers' return buffers; null = row does not exist.
+template <typename T>
+struct ScatterRows {
+  T* row[4];
+};
+
+template <typename T>
+__device__ __forceinline__ void stage_store_rows(const uint8_t* stage, const ScatterRows<T>& rows, int col, int cols,
+                                                 int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + (lane >> 2), q = lane & 3;
+    if (rows.row[i] != nullptr && q * 8 < cols)
+      *reinterpret_cast<uint4*>(rows.row[i] + col + q * 8) = *reinterpret_cast<const uint4*>(stage + stage_offset(r, q));
+  }
+}
+
 // This thread's row of the staging buffer, kept packed (16 registers for 32 values).
 struct PackedRow {
   uint4 q[4];
@@ -262,7 +282,7 @@ __device__ __forceinline__ float epilogue_value(const uint32_t (&raw)[32], const
 template <typename T, int EPI, int ACT, int WHICH>
 __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
                                               uint8_t* stage, T* out, int64_t row_stride, int rows_ok, int cols,
-                                              int lane) {
+                                              int lane, const ScatterRows<T>* scatter = nullptr, int col = 0) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     uint4 w;
@@ -277,7 +297,8 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
     *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
   }
   __syncwarp();
-  stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
+  if (scatter != nullptr) stage_store_rows<T>(stage, *scatter, col, cols, lane);
+  else stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
   __syncwarp();
 }
 
@@ -288,9 +309,9 @@ template <typename T, int EPI, int ACT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const PackedRow& a1,
                                                const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                int64_t row_stride, int rows_ok, int cols, int lane,
-                                               const GemmParams& p) {
+                                               const GemmParams& p, const ScatterRows<T>* scatter, int col) {
   epilogue_emit<T, EPI, ACT, 0>(raw, a1, a2, stage, static_cast<T*>(p.c) + base_off, row_stride, rows_ok, cols,
-                                lane);
+                                lane, scatter, col);
   if constexpr (EPI == kEpiAct || EPI == kEpiDAct || EPI == kEpiGlu || EPI == kEpiDGlu) {
     if (p.out2)
       epilogue_emit<T, EPI, ACT, 1>(raw, a1, a2, stage, static_cast<T*>(p.out2) + base_off, row_stride, rows_ok,
@@ -307,13 +328,13 @@ template <typename T, int EPI>
 __device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], const PackedRow& a1,
                                                 const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                 int64_t row_stride, int rows_ok, int cols, int lane,
-                                                const GemmParams& p) {
+                                                const GemmParams& p, const ScatterRows<T>* scatter, int col) {
   switch (p.act) {
-    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    default: epilogue_chunk<T, EPI, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    default: epilogue_chunk<T, EPI, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
   }
 }
 
@@ -322,14 +343,15 @@ template <typename T>
 __device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], const PackedRow& a1,
                                                   const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                   int64_t row_stride, int rows_ok, int cols, int lane,
-                                                  const GemmParams& p) {
+                                                  const GemmParams& p, const ScatterRows<T>* scatter = nullptr,
+                                                  int col = 0) {
   switch (p.epilogue) {
-    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
-    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p); break;
+    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
     default: break;
   }
 }
@@ -354,9 +376,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2]
   uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;  // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* scatter_bar = bars + 2 * kStages + 6;  // [2] fused combine: "all warps stored this tile"
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* s_row_end = reinterpret_cast<int*>(smem + Cfg::kTileBytes + 256);   // [kMaxGroups]
   int* s_mblk_end = s_row_end + kMaxGroups;                                 // [kMaxGroups]
+  // Fused combine (NN layout only): per (local expert, source rank) segment tables.
+  int* s_seg_end = reinterpret_cast<int*>(smem + Cfg::kTileBytes + 256 + 2 * kMaxGroups * 4 + Cfg::kStagingBytes);
+  int* s_remote_start = s_seg_end + kMaxScatterSegments;
+  int* s_per_source = s_remote_start + kMaxScatterSegments;                 // [world] rows returned to each source
+  const bool scatter_on = LAYOUT == kNN && p.scatter_base != nullptr;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -373,6 +401,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[s]), kEpilogueWarps);
+      mbar_init(smem_u32(&scatter_bar[s]), kEpilogueWarps);
     }
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
@@ -387,6 +416,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       acc += (end - prev + kBlockM - 1) / kBlockM;
       s_mblk_end[g] = acc;
       prev = end;
+    }
+  }
+  if (scatter_on) {
+    const int W = p.scatter_world, E = p.scatter_experts, epr = G;
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int j = 0; j < epr; ++j)
+        for (int s2 = 0; s2 < W; ++s2) {
+          acc += __ldg(p.scatter_counts + s2 * E + p.scatter_rank * epr + j);
+          s_seg_end[j * W + s2] = acc;
+        }
+    }
+    for (int idx = threadIdx.x; idx < epr * W; idx += kThreads) {
+      const int j = idx / W, s2 = idx - j * W;
+      const int e = p.scatter_rank * epr + j;
+      int acc = 0;
+      for (int e2 = 0; e2 < e; ++e2) acc += __ldg(p.scatter_counts + s2 * E + e2);
+      s_remote_start[idx] = acc;       // first sorted position of (source s2, expert e) at the source
+    }
+    for (int s2 = threadIdx.x; s2 < W; s2 += kThreads) {
+      int acc = 0;
+      for (int j = 0; j < epr; ++j) acc += __ldg(p.scatter_counts + s2 * E + p.scatter_rank * epr + j);
+      s_per_source[s2] = acc;
+      // A source that gets nothing back still needs its flag.
+      if (blockIdx.x == 0 && acc == 0)
+        st_release_sys_s32(reinterpret_cast<int*>(p.scatter_flag_base[s2] + p.scatter_flag_off) + p.scatter_rank,
+                           p.scatter_seq);
     }
   }
   tcgen05_fence_before();
@@ -572,6 +628,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int64_t row_off;
       if constexpr (LAYOUT == kTN) row_off = (int64_t(tile.group) * p.M + tile.row0 + quarter * 32) * p.N;
       else row_off = int64_t(tile.row0 + quarter * 32) * p.N;
+      ScatterRows<T> targets;
+      if (scatter_on) {
+        const int W = p.scatter_world;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = quarter * 32 + i * 8 + (lane >> 2);
+          targets.row[i] = nullptr;
+          if (r < tile.rows_valid) {
+            const int grow = tile.row0 + r;
+            int s2 = 0;
+            while (s2 < W - 1 && s_seg_end[tile.group * W + s2] <= grow) ++s2;
+            const int seg = tile.group * W + s2;
+            const int seg_begin = seg ? s_seg_end[seg - 1] : 0;
+            const int64_t remote_row = s_remote_start[seg] + (grow - seg_begin);
+            targets.row[i] = reinterpret_cast<T*>(p.scatter_base[s2] + p.scatter_off) + remote_row * p.N;
+          }
+        }
+      }
       // Auxiliary operands (pre-activations) are fetched one chunk ahead, the first one
       // before the accumulator is even ready.
       const bool need1 = p.epilogue == kEpiDAct || p.epilogue == kEpiGlu || p.epilogue == kEpiDGlu ||
@@ -632,12 +706,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int i = 0; i < 32; ++i) raw[i] = 0u;
         }
         if (rows_ok > 0)
-          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p);
+          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p,
+                               scatter_on ? &targets : nullptr, col);
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc_stage]));
+      const int tile_stage = acc_stage;
+      const uint32_t tile_phase = acc_phase;
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
+      if (scatter_on) {
+        // Once every epilogue warp has issued its stores of this tile, one thread orders them
+        // system-wide and credits the sources whose rows the tile covered.  (Two barriers,
+        // alternating with the accumulator stage: a warp is never more than one tile ahead.)
+        if (lane == 0) mbar_arrive(smem_u32(&scatter_bar[tile_stage]));
+        if (warp == 0) {
+          bool stored = true;
+          if (lane == 0)
+            stored = mbar_wait(smem_u32(&scatter_bar[tile_stage]), tile_phase, abort_flag, p.status, kErrEpilogue,
+                               kWaitLimitNs);
+          stored = __shfl_sync(0xffffffffu, stored ? 1 : 0, 0) != 0;   // the warp leaves together
+          if (!stored) ok = false;
+        }
+        if (threadIdx.x == 0 && ok && tile.rows_valid > 0) {
+          __threadfence_system();
+          const int W = p.scatter_world;
+          const int lo_row = tile.row0, hi_row = tile.row0 + tile.rows_valid;
+          for (int s2 = 0; s2 < W; ++s2) {
+            const int seg = tile.group * W + s2;
+            const int seg_begin = seg ? s_seg_end[seg - 1] : 0;
+            const int cnt = min(hi_row, s_seg_end[seg]) - max(lo_row, seg_begin);
+            if (cnt <= 0) continue;
+            // A row is complete once all column blocks of its tile row have been stored.
+            if (atomicAdd(p.scatter_done + s2, cnt) + cnt == s_per_source[s2] * num_nb) {
+              __threadfence_system();
+              st_release_sys_s32(reinterpret_cast<int*>(p.scatter_flag_base[s2] + p.scatter_flag_off) +
+                                     p.scatter_rank, p.scatter_seq);
+            }
+          }
+        }
+      }
     }
     // Rows past the last group belong to nobody: defined as zero (NT / NN only).
     if (LAYOUT != kTN && p.zero_tail) {

@@ -157,6 +157,21 @@ struct GemmParams {
   int wait_count;
   int wait_stride;
   int wait_seq;
+  // Optional scatter of the main output (NN layout): instead of c[row], every output row is
+  // stored into the return buffer of the rank it came from (expert-parallel combine fused into
+  // the GEMM epilogue).  Rows of local expert j arrive grouped by source rank; the counts matrix
+  // [world][experts] gives the segment sizes and the row offsets on the source side.  After the
+  // last row for a source has been stored its flag is released.  Null scatter_base = off.
+  const uint64_t* scatter_base;       // mapping of every rank's heap that holds the return buffer
+  const uint64_t* scatter_flag_base;  // mapping of every rank's heap that holds the flags
+  const int* scatter_counts;
+  int* scatter_done;                  // [world] zeroed completion counters
+  int64_t scatter_off;                // byte offset of the return buffer in its heap
+  int64_t scatter_flag_off;           // byte offset of the int32 flag array [world] in its heap
+  int scatter_world;
+  int scatter_rank;
+  int scatter_experts;                // global number of experts
+  int scatter_seq;
 };
 
 // block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit

@@ -387,6 +387,8 @@ at::Tensor router_topk_backward(const at::Tensor& scores, const at::Tensor& weig
 // ---------------------------------------------------------------------------
 namespace {
 
+constexpr int64_t kMaxScatterSegmentsHost = 512;   // = kMaxScatterSegments of the kernel
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -455,7 +457,9 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      bool want_out2, bool want_out3, int64_t num_groups,
                                      const c10::optional<at::Tensor>& c_in, bool zero_tail,
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
-                                     int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode) {
+                                     int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
+                                     const c10::optional<std::vector<at::Tensor>>& scatter,
+                                     const std::vector<int64_t>& scatter_args) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -480,10 +484,12 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     p.K = int(a.size(1));
     p.N = int(trans_b ? b.size(1) : b.size(2));
     p.M = 0;
-    c = c_in.has_value() ? *c_in : at::empty({a.size(0), p.N}, a.options());
+    // With the fused combine the rows go to the peers' return buffers: no local output exists.
+    if (scatter.has_value()) c = at::empty({0, p.N}, a.options());
+    else c = c_in.has_value() ? *c_in : at::empty({a.size(0), p.N}, a.options());
   }
   TORCH_CHECK(c.is_contiguous() && c.scalar_type() == a.scalar_type(), "bad output buffer");
-  const int64_t out_numel = c.numel();
+  const int64_t out_numel = scatter.has_value() ? a.size(0) * int64_t(p.N) : c.numel();
   auto check_aux = [&](const c10::optional<at::Tensor>& t, const char* name) {
     TORCH_CHECK(t.has_value() && t->is_cuda() && t->is_contiguous() && t->numel() == out_numel &&
                     t->scalar_type() == a.scalar_type(),
@@ -519,6 +525,34 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     p.wait_stride = int(wait_stride);
     p.wait_seq = int(wait_seq);
   }
+  if (scatter.has_value()) {
+    // scatter = {data heap bases, flag heap bases, counts, done}; scatter_args = {data offset, flag
+    // offset, world, rank, experts, seq}.
+    TORCH_CHECK(layout == kNN && scatter->size() == 4 && scatter_args.size() == 6,
+                "the fused combine needs the NN layout, four tensors and six integers");
+    const auto& bases = (*scatter)[0];
+    const auto& flag_bases = (*scatter)[1];
+    const auto& counts = (*scatter)[2];
+    const auto& done = (*scatter)[3];
+    const int64_t world = scatter_args[2];
+    TORCH_CHECK(bases.is_cuda() && bases.scalar_type() == at::kLong && bases.numel() == world &&
+                    flag_bases.is_cuda() && flag_bases.scalar_type() == at::kLong && flag_bases.numel() == world &&
+                    counts.scalar_type() == at::kInt && counts.numel() == world * scatter_args[4] &&
+                    done.scalar_type() == at::kInt && done.numel() >= world,
+                "bad fused-combine arguments");
+    TORCH_CHECK(num_groups * world <= kMaxScatterSegmentsHost, "fused combine: too many (expert, rank) segments");
+    p.scatter_base = reinterpret_cast<const uint64_t*>(bases.data_ptr<int64_t>());
+    p.scatter_flag_base = reinterpret_cast<const uint64_t*>(flag_bases.data_ptr<int64_t>());
+    p.scatter_counts = counts.data_ptr<int>();
+    p.scatter_done = done.data_ptr<int>();
+    p.scatter_off = scatter_args[0];
+    p.scatter_flag_off = scatter_args[1];
+    p.scatter_world = int(world);
+    p.scatter_rank = int(scatter_args[3]);
+    p.scatter_experts = int(scatter_args[4]);
+    p.scatter_seq = int(scatter_args[5]);
+    p.zero_tail = 0;   // there is no local output to clear
+  }
   if (out_numel == 0) return {c, out2, out3};
 
   const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
@@ -526,7 +560,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   // 255 rows per group; measured, they win once groups are a few thousand rows long.
   // pair_mode: -1 = decide here, 0 = never, 1 = whenever the kernel supports the problem.
   const int64_t rows_expected = rows_hint > 0 ? rows_hint : a.size(0);
-  bool pair = layout != kTN && block_n == 256 && sm_count() >= 2;
+  bool pair = layout != kTN && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
   if (pair_mode == 0) pair = false;
   else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048;
   CUtensorMap ta, tb;

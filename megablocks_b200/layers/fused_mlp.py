@@ -28,7 +28,7 @@ from megablocks_b200.ops import gg as G
 
 
 def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tail: bool = True,
-                rows_hint: int = 0):
+                rows_hint: int = 0, scatter=None):
     """Forward GEMMs.  Returns ``(y, saved)`` where ``saved = (z1, z2, h or None)``."""
     kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
     if v1 is not None:
@@ -37,12 +37,13 @@ def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tai
     else:
         z1, h, _ = G.grouped_gemm(x, w1, bins, trans_b=True, epilogue=G.EPI_ACT, act=act, wait=wait, **kw)
         z2 = None
-    y, _, _ = G.grouped_gemm(h, w2, bins, **kw)
+    # `scatter`: the last GEMM stores its rows straight into the peers' return buffers.
+    y, _, _ = G.grouped_gemm(h, w2, bins, scatter=scatter, **kw)
     return y, (z1, z2, h if keep_h else None)
 
 
 def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True,
-                 rows_hint: int = 0):
+                 rows_hint: int = 0, scatter=None):
     """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded)."""
     z1, z2, h = saved
     num_experts = w1.shape[0]
@@ -64,9 +65,13 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
     if v1 is not None and needs[3]:
         dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts)
     if needs[0]:
-        dx, _, _ = G.grouped_gemm(dz1, w1, bins, **kw)
-        if v1 is not None:
-            dx, _, _ = G.grouped_gemm(dz2, v1, bins, epilogue=G.EPI_ADD, aux1=dx, **kw)
+        # The GEMM that produces the final dx is the last reader of the receive buffers and, with
+        # `scatter`, also the one that returns the rows to their sources.
+        if v1 is None:
+            dx, _, _ = G.grouped_gemm(dz1, w1, bins, scatter=scatter, **kw)
+        else:
+            dx, _, _ = G.grouped_gemm(dz1, w1, bins, **kw)
+            dx, _, _ = G.grouped_gemm(dz2, v1, bins, epilogue=G.EPI_ADD, aux1=dx, scatter=scatter, **kw)
     return dx, dw1, dw2, dv1
 
 

@@ -180,7 +180,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
                  c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
-                 rows_hint: int = 0):
+                 rows_hint: int = 0, scatter=None):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -192,6 +192,10 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     rows of ``a`` are then being delivered by peer GPUs (expert-parallel dispatch).
     ``rows_hint`` is the expected number of occupied rows when ``a`` is a worst-case sized
     buffer (it only steers the choice between the single-CTA and the CTA-pair kernel).
+    ``scatter = ([data_bases, flag_bases, counts, done], [data_off, flag_off, world, rank, experts,
+    seq])`` (NN layout) stores every output row into the return buffer of the rank it came from
+    instead of ``c`` and releases that rank's flag after its last row: the expert-parallel combine
+    fused into the GEMM epilogue.  The returned ``c`` is then empty.
     """
     if num_groups is None:
         num_groups = bins.numel()
@@ -199,7 +203,11 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
         flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
-                                  int(count), int(stride), int(seq), int(rows_hint), _PAIR_MODE)
+                                  int(count), int(stride), int(seq), int(rows_hint), _PAIR_MODE,
+                                  scatter[0] if scatter is not None else None,
+                                  scatter[1] if scatter is not None else [])
+    if scatter is not None:
+        raise RuntimeError('grouped_gemm: the fused combine needs the CUDA kernel (unsupported shape or dtype)')
     if wait is not None:
         raise RuntimeError('grouped_gemm: peer-arrival waits need the CUDA kernel (unsupported shape or dtype)')
     # Shapes or dtypes the tensor-core kernel does not take (fp32 inputs, rows that

@@ -28,6 +28,8 @@ that :func:`megablocks_b200.utils.status.check` turns into an exception.
 
 from typing import Any, Dict, Optional, Tuple
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -166,6 +168,17 @@ class EpWorkspace:
             ext().ep_return_rows(y, counts, *self._layout(), self.bwd_heap.peer_base, self.off_ret_dx,
                                  self.off_ret_flags[1], seq, done)
 
+    def scatter_args(self, counts, direction: int, seq: int, done):
+        """``scatter`` argument of the grouped GEMM: return the output rows to their sources from the epilogue."""
+        heap = self.heap if direction == 0 else self.bwd_heap
+        off = self.off_ret_y if direction == 0 else self.off_ret_dx
+        return ([heap.peer_base, self.heap.peer_base, counts, done],
+                [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq])
+
+    def fuse_combine(self) -> bool:
+        """Whether the kernel's segment tables can hold this workspace's (expert, rank) pairs."""
+        return self.epr * self.world <= 512 and os.environ.get('MB200_EP_FUSED_COMBINE', '1') != '0'
+
     def wait_return(self, direction: int, seq: int) -> None:
         ext().ep_wait_flags(self.flags(self.off_ret_flags[direction], self.world), self.world, seq, ERR_RETURN_WAIT)
 
@@ -204,9 +217,12 @@ class _FusedExpertParallel(torch.autograd.Function):
         tokens = x.shape[0]
         counts, recv_bins, done = ws.exchange_counts(tpe, seq)
         ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0])
+        fuse = ws.fuse_combine()
         y, saved = mlp_forward(ws.recv_x, w1, w2, v1, recv_bins, act, keep_h, wait=ws.arrival(0, seq),
-                               zero_tail=False, rows_hint=ws.copies)
-        ws.return_rows(y, counts, 0, seq, done[1])
+                               zero_tail=False, rows_hint=ws.copies,
+                               scatter=ws.scatter_args(counts, 0, seq, done[1]) if fuse else None)
+        if not fuse:
+            ws.return_rows(y, counts, 0, seq, done[1])
         ws.wait_return(0, seq)
         out = ext().scatter_rows(ws.ret_y, indices, bin_ids, expert_weights, bins, bins, top_k, tokens)
         will_backward = torch.is_grad_enabled() and any(
@@ -236,6 +252,7 @@ class _FusedExpertParallel(torch.autograd.Function):
             v1, z2 = saved[11:13]
         h = saved[-1] if ctx.keep_h else None
         dout = dout.contiguous()
+        fuse = ws.fuse_combine()
         # d(out)/d(expert rows): each copy's gradient is its token's gradient times its router weight.
         ws.push(dout, indices, expert_weights, bins, counts, 1, seq, top_k, done_push)
         dweights = None
@@ -245,10 +262,12 @@ class _FusedExpertParallel(torch.autograd.Function):
                  ctx.glu and ctx.needs_input_grad[4])
         dxr, dw1, dw2, dv1 = mlp_backward(ws.recv_dy, ws.recv_x, w1, w2, v1, recv_bins, ctx.act, (z1, z2, h),
                                           (True,) + needs[1:], wait=ws.arrival(1, seq), zero_tail=False,
-                                          rows_hint=ws.copies)
+                                          rows_hint=ws.copies,
+                                          scatter=ws.scatter_args(counts, 1, seq, done_ret) if fuse else None)
         # Every read of both receive buffers is enqueued above; only now may peers learn
         # (through the return flags / the free flag) that they can be overwritten.
-        ws.return_rows(dxr, counts, 1, seq, done_ret)
+        if not fuse:
+            ws.return_rows(dxr, counts, 1, seq, done_ret)
         ws.release_receive_buffer(seq)
         ws.wait_return(1, seq)
         dx = None

@@ -24,6 +24,8 @@ def _free_port():
 
 def _worker(rank, world, port, kw, out_dir):
     os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    # Combine either inside the last expert GEMM's epilogue (default) or by the separate return kernel.
+    os.environ['MB200_EP_FUSED_COMBINE'] = '0' if kw.get('combine') == 'kernel' else '1'
     torch.cuda.set_device(rank)
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
     import megablocks_b200 as mb
@@ -69,6 +71,7 @@ def _worker(rank, world, port, kw, out_dir):
     dict(top_k=2, mlp_type='mlp', mem_opt=False, tokens=300),
     dict(top_k=2, mlp_type='glu', mem_opt=True, tokens=1024),
     dict(top_k=2, mlp_type='mlp', mem_opt=True, tokens=256, checkpoint=True),   # recomputed forward
+    dict(top_k=2, mlp_type='glu', mem_opt=False, tokens=640, combine='kernel'),
 ])
 def test_fused_matches_all_to_all(kw, tmp_path):
     world = min(torch.cuda.device_count(), 4)
