@@ -52,6 +52,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const std::vector<int64_t>& scatter_args);
 int64_t read_status(bool clear);
 int64_t launch_count();
+at::Tensor gemm_role_timers(const at::Tensor& like);
 
 // torch_glue.cpp: symmetric heap and expert-parallel exchange
 std::vector<at::Tensor> symm_alloc(int64_t nbytes);
@@ -114,6 +115,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &mb::grouped_gemm);
   m.def("read_status", &mb::read_status);
   m.def("launch_count", &mb::launch_count);
+  m.def("gemm_role_timers", &mb::gemm_role_timers,
+        "Per-CTA cycle counters of the grouped GEMM roles (builds with -DMB_GEMM_TIMING)");
   m.def("cross_entropy_forward", &mb::cross_entropy_forward);
   m.def("cross_entropy_backward_", &mb::cross_entropy_backward_);
   m.def("layernorm_forward", &mb::layernorm_forward);

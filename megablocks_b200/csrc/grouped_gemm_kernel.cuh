@@ -184,6 +184,9 @@ __device__ __forceinline__ void aux_prefetch(const T* base, int64_t row_stride, 
 template <typename T>
 __device__ __forceinline__ void stage_store(const uint8_t* stage, T* base, int64_t row_stride, int rows_ok,
                                             int cols, int lane) {
+#ifdef MB_GEMM_NO_STORE
+  if (rows_ok >= 0) return;
+#endif
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = i * 8 + (lane >> 2), q = lane & 3;
@@ -209,6 +212,19 @@ __device__ __forceinline__ void stage_store_rows(const uint8_t* stage, const Sca
     if (rows.row[i] != nullptr && q * 8 < cols)
       *reinterpret_cast<uint4*>(rows.row[i] + col + q * 8) = *reinterpret_cast<const uint4*>(stage + stage_offset(r, q));
   }
+}
+
+// TMA store target of one warp for the current tile: `on` when the tensor maps exist and all 32
+// rows of the warp's quarter are real rows of the group; `row` = first of them in the [rows, N] view.
+struct TmaOut {
+  bool on;
+  int row;
+};
+
+// Before a staging buffer is rewritten the bulk store that last read it must be done reading.
+__device__ __forceinline__ void stage_acquire(int lane) {
+  if (lane == 0) bulk_wait_read_all();
+  __syncwarp();
 }
 
 // This thread's row of the staging buffer, kept packed (16 registers for 32 values).
@@ -282,7 +298,9 @@ __device__ __forceinline__ float epilogue_value(const uint32_t (&raw)[32], const
 template <typename T, int EPI, int ACT, int WHICH>
 __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
                                               uint8_t* stage, T* out, int64_t row_stride, int rows_ok, int cols,
-                                              int lane, const ScatterRows<T>* scatter = nullptr, int col = 0) {
+                                              int lane, const ScatterRows<T>* scatter = nullptr, int col = 0,
+                                              const CUtensorMap* tmap = nullptr, TmaOut tma = TmaOut{false, 0}) {
+  if (tmap != nullptr) stage_acquire(lane);
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     uint4 w;
@@ -295,6 +313,17 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
     w.w = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 6),
                    epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 7));
     *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
+  }
+  if (tma.on) {
+    // The staging layout is the 64-byte swizzle of a 32 x 32 box: one thread hands the chunk to
+    // the TMA unit, which clips columns past N.
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmap, smem_u32(stage), col, tma.row);
+      bulk_commit_group();
+    }
+    return;
   }
   __syncwarp();
   if (scatter != nullptr) stage_store_rows<T>(stage, *scatter, col, cols, lane);
@@ -309,18 +338,20 @@ template <typename T, int EPI, int ACT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const PackedRow& a1,
                                                const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                int64_t row_stride, int rows_ok, int cols, int lane,
-                                               const GemmParams& p, const ScatterRows<T>* scatter, int col) {
+                                               const GemmParams& p, const ScatterRows<T>* scatter, int col,
+                                               TmaOut tma) {
+  const CUtensorMap* maps = p.store_tma ? p.out_map : nullptr;
   epilogue_emit<T, EPI, ACT, 0>(raw, a1, a2, stage, static_cast<T*>(p.c) + base_off, row_stride, rows_ok, cols,
-                                lane, scatter, col);
+                                lane, scatter, col, maps, tma);
   if constexpr (EPI == kEpiAct || EPI == kEpiDAct || EPI == kEpiGlu || EPI == kEpiDGlu) {
     if (p.out2)
       epilogue_emit<T, EPI, ACT, 1>(raw, a1, a2, stage, static_cast<T*>(p.out2) + base_off, row_stride, rows_ok,
-                                    cols, lane);
+                                    cols, lane, nullptr, col, maps ? maps + 1 : nullptr, tma);
   }
   if constexpr (EPI == kEpiDGlu) {
     if (p.out3)
       epilogue_emit<T, EPI, ACT, 2>(raw, a1, a2, stage, static_cast<T*>(p.out3) + base_off, row_stride, rows_ok,
-                                    cols, lane);
+                                    cols, lane, nullptr, col, maps ? maps + 2 : nullptr, tma);
   }
 }
 
@@ -328,13 +359,14 @@ template <typename T, int EPI>
 __device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], const PackedRow& a1,
                                                 const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                 int64_t row_stride, int rows_ok, int cols, int lane,
-                                                const GemmParams& p, const ScatterRows<T>* scatter, int col) {
+                                                const GemmParams& p, const ScatterRows<T>* scatter, int col,
+                                                TmaOut tma) {
   switch (p.act) {
-    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    default: epilogue_chunk<T, EPI, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kActGeluTanh: epilogue_chunk<T, EPI, kActGeluTanh>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kActSilu: epilogue_chunk<T, EPI, kActSilu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kActRelu: epilogue_chunk<T, EPI, kActRelu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kActGeluErf: epilogue_chunk<T, EPI, kActGeluErf>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    default: epilogue_chunk<T, EPI, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
   }
 }
 
@@ -344,22 +376,39 @@ __device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], con
                                                   const PackedRow& a2, uint8_t* stage, int64_t base_off,
                                                   int64_t row_stride, int rows_ok, int cols, int lane,
                                                   const GemmParams& p, const ScatterRows<T>* scatter = nullptr,
-                                                  int col = 0) {
+                                                  int col = 0, TmaOut tma = TmaOut{false, 0}) {
   switch (p.epilogue) {
-    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
-    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col); break;
+    case kEpiNone: epilogue_chunk<T, kEpiNone, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kEpiAdd: epilogue_chunk<T, kEpiAdd, kActIdentity>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kEpiAct: epilogue_by_act<T, kEpiAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kEpiDAct: epilogue_by_act<T, kEpiDAct>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kEpiGlu: epilogue_by_act<T, kEpiGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
+    case kEpiDGlu: epilogue_by_act<T, kEpiDGlu>(raw, a1, a2, stage, base_off, row_stride, rows_ok, cols, lane, p, scatter, col, tma); break;
     default: break;
   }
 }
 
+// Role timers: a build with -DMB_GEMM_TIMING accumulates, per CTA, the cycles each role spends
+// waiting on its barriers (slots: 0 MMA waits for operands, 1 MMA waits for a free accumulator,
+// 2 MMA role total, 3 producer waits for a free stage, 4 epilogue warp 0 waits for an accumulator,
+// 5 epilogue warp 0 total, 6 its tcgen05.ld time, 7 its convert / stage / store time, 8 its per-tile
+// preamble, 9 its whole chunk loop, 10 its accumulator release).
+#ifdef MB_GEMM_TIMING
+#define MB_T_DECL(name) long long name = 0
+#define MB_T_BEGIN(var) const long long var = clock64()
+#define MB_T_END(var, acc) acc += clock64() - var
+#define MB_T_WRITE(slot, acc) if (p.timing) p.timing[blockIdx.x * 16 + (slot)] = acc
+#else
+#define MB_T_DECL(name)
+#define MB_T_BEGIN(var)
+#define MB_T_END(var, acc)
+#define MB_T_WRITE(slot, acc)
+#endif
+
 template <typename T, int LAYOUT, int BLOCK_N>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const GemmParams p) {
+                    const __grid_constant__ GemmParams p) {
   using Cfg = Config<BLOCK_N>;
   constexpr bool kAMn = LAYOUT == kTN;
   constexpr bool kBMn = LAYOUT != kNT;
@@ -370,7 +419,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTileBytes);
+  // Staging buffers directly after the operand ring: 1024-byte aligned, as the swizzled TMA stores need.
+  uint8_t* staging = smem + Cfg::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + kStages;            // [kStages]
   uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2]
@@ -378,10 +429,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   uint64_t* scatter_bar = bars + 2 * kStages + 6;  // [2] fused combine: "all warps stored this tile"
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  int* s_row_end = reinterpret_cast<int*>(smem + Cfg::kTileBytes + 256);   // [kMaxGroups]
+  int* s_row_end = reinterpret_cast<int*>(staging + Cfg::kStagingBytes + 256);   // [kMaxGroups]
   int* s_mblk_end = s_row_end + kMaxGroups;                                 // [kMaxGroups]
   // Fused combine (NN layout only): per (local expert, source rank) segment tables.
-  int* s_seg_end = reinterpret_cast<int*>(smem + Cfg::kTileBytes + 256 + 2 * kMaxGroups * 4 + Cfg::kStagingBytes);
+  int* s_seg_end = s_mblk_end + kMaxGroups;
   int* s_remote_start = s_seg_end + kMaxScatterSegments;
   int* s_per_source = s_remote_start + kMaxScatterSegments;                 // [world] rows returned to each source
   const bool scatter_on = LAYOUT == kNN && p.scatter_base != nullptr;
@@ -493,6 +544,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       int arrived_group = -1;
+      MB_T_DECL(t_empty);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const Tile tile = decode(t);
         const int num_kb = (tile.k_len + kBlockK - 1) / kBlockK;
@@ -520,7 +572,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           fence_proxy_async_all();   // the acquire above must precede the TMA (async proxy) reads
         }
         for (int kb = 0; kb < num_kb; ++kb) {
+          MB_T_BEGIN(w0);
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, kErrProducer, kWaitLimitNs);
+          MB_T_END(w0, t_empty);
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[stage]);
           mbar_arrive_expect_tx(bar, kABytes + Cfg::kBBytes);
@@ -546,6 +600,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      MB_T_WRITE(3, t_empty);
     }
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer ==========================================
@@ -555,17 +610,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    MB_T_DECL(t_full);
+    MB_T_DECL(t_tmem);
+    MB_T_DECL(t_total);
+    MB_T_BEGIN(role0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Tile tile = decode(t);
       const int num_kb = (tile.k_len + kBlockK - 1) / kBlockK;
+      MB_T_BEGIN(w1);
       ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_stage]), acc_phase ^ 1u, abort_flag, p.status, kErrMmaTmem,
                      kWaitLimitNs);
+      MB_T_END(w1, t_tmem);
       ok = __all_sync(0xffffffffu, ok);   // the whole warp leaves together
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
       for (int kb = 0; kb < num_kb; ++kb) {
+        MB_T_BEGIN(w0);
         ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, kErrMmaFull, kWaitLimitNs);
+        MB_T_END(w0, t_full);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         uint8_t* a_tile = smem_a + stage * kABytes;
@@ -611,16 +674,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
     }
+    MB_T_END(role0, t_total);
+    if (lane == 0) {
+      MB_T_WRITE(0, t_full);
+      MB_T_WRITE(1, t_tmem);
+      MB_T_WRITE(2, t_total);
+    }
   } else if (warp < kEpilogueWarps) {
     // ======================= epilogue warps ======================================
     const int quarter = warp & 3;               // TMEM lane quarter this warp may read
     const int half = warp >> 2;                 // which of the two warps of that quarter
-    uint8_t* stage = smem + Cfg::kTileBytes + 256 + 2 * kMaxGroups * 4 + warp * 2048;
+    uint8_t* stage = staging + warp * 2048;
     constexpr int kChunks = BLOCK_N / 32;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    MB_T_DECL(t_acc);
+    MB_T_DECL(t_epi);
+    MB_T_DECL(t_ld);
+    MB_T_DECL(t_out);
+    MB_T_DECL(t_pre);
+    MB_T_DECL(t_loop);
+    MB_T_DECL(t_post);
+    MB_T_BEGIN(role0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      MB_T_BEGIN(wpre);
       const Tile tile = decode(t);
       const bool has_k = tile.k_len > 0;
       // Rows of this warp's quarter that exist in the tile, and its first row's offset.
@@ -628,6 +706,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int64_t row_off;
       if constexpr (LAYOUT == kTN) row_off = (int64_t(tile.group) * p.M + tile.row0 + quarter * 32) * p.N;
       else row_off = int64_t(tile.row0 + quarter * 32) * p.N;
+      TmaOut tma;
+      tma.on = p.store_tma != 0 && rows_ok == 32;
+      if constexpr (LAYOUT == kTN) tma.row = tile.group * p.M + tile.row0 + quarter * 32;
+      else tma.row = tile.row0 + quarter * 32;
       ScatterRows<T> targets;
       if (scatter_on) {
         const int W = p.scatter_world;
@@ -660,13 +742,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      min(32, p.N - col), lane);
         }
       }
+      MB_T_END(wpre, t_pre);
+      MB_T_BEGIN(w0);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc_stage]), acc_phase, abort_flag, p.status, kErrEpilogue,
                      kWaitLimitNs);
+      MB_T_END(w0, t_acc);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc_stage * BLOCK_N;
       // The two warps of a quarter interleave 32-column chunks.
+      MB_T_BEGIN(wloop);
 #pragma unroll 1
       for (int ci = half; ci < kChunks; ci += 2) {
         const int c0 = ci * 32;
@@ -685,6 +771,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (rows_ok > 0) {
           const int cols = min(32, p.N - col);
           if (need1) {
+            if (p.store_tma) stage_acquire(lane);
             stage_load<T>(stage, static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok, cols, lane);
             __syncwarp();
             stage_read_row(stage, lane, a1);
@@ -698,6 +785,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
         uint32_t raw[32];
+        MB_T_BEGIN(w1);
         if (has_k) {
           tmem_ld_32x32(taddr + c0, raw);
           tmem_ld_wait();
@@ -705,13 +793,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i) raw[i] = 0u;
         }
+        MB_T_END(w1, t_ld);
+        MB_T_BEGIN(w2);
         if (rows_ok > 0)
           epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p,
-                               scatter_on ? &targets : nullptr, col);
+                               scatter_on ? &targets : nullptr, col, tma);
+        MB_T_END(w2, t_out);
       }
+      MB_T_END(wloop, t_loop);
+      MB_T_BEGIN(wpost);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc_stage]));
+      MB_T_END(wpost, t_post);
       const int tile_stage = acc_stage;
       const uint32_t tile_phase = acc_phase;
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
@@ -746,6 +840,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
+    }
+    if (p.store_tma && lane == 0) bulk_wait_all();   // bulk stores complete before the CTA retires
+    MB_T_END(role0, t_epi);
+    if (threadIdx.x == 0) {
+      MB_T_WRITE(4, t_acc);
+      MB_T_WRITE(5, t_epi);
+      MB_T_WRITE(6, t_ld);
+      MB_T_WRITE(7, t_out);
+      MB_T_WRITE(8, t_pre);
+      MB_T_WRITE(9, t_loop);
+      MB_T_WRITE(10, t_post);
     }
     // Rows past the last group belong to nobody: defined as zero (NT / NN only).
     if (LAYOUT != kTN && p.zero_tail) {

@@ -32,7 +32,7 @@ constexpr int kPairSmemBytes = kPairTileBytes + 256 + 2 * kMaxGroups * 4 + kEpil
 template <typename T, int LAYOUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const GemmParams p) {
+                         const __grid_constant__ GemmParams p) {
   static_assert(LAYOUT == kNT || LAYOUT == kNN, "CTA pairs serve the NT and NN layouts");
   constexpr bool kBMn = LAYOUT == kNN;
   constexpr int kStages = kPairStages;

@@ -172,6 +172,13 @@ struct GemmParams {
   int scatter_rank;
   int scatter_experts;                // global number of experts
   int scatter_seq;
+  // Optional TMA stores of the outputs (single-CTA kernel): tensor maps of c / out2 / out3 viewed as
+  // [rows, N] with 32 x 32 boxes and 64-byte swizzle.  Warps whose 32 rows of a tile all exist hand
+  // their staged chunk to the TMA unit instead of storing it with the LSU.  0 = off.
+  int store_tma;
+  CUtensorMap out_map[3];
+  // Role timers (builds with -DMB_GEMM_TIMING only): [grid][16] cycle counters, see the kernel.
+  long long* timing;
 };
 
 // block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit

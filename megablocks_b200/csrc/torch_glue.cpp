@@ -421,6 +421,20 @@ CUtensorMap make_tensor_map(const void* base, bool bf16, int64_t rows, int64_t c
   return map;
 }
 
+// Row-major [rows, cols] 16-bit output, box = 32 x 32, 64-byte swizzle (the epilogue's staging layout).
+bool make_output_map(CUtensorMap* map, const void* base, bool bf16, int64_t rows, int64_t cols) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || cols % 8 != 0 || rows < 1) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {32u, 32u};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult rc = encode_tiled_fn()(
+      map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
+      strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
 at::Tensor& status_word(const at::Device& device) {
   // Leaked on purpose: freeing CUDA tensors during static destruction races with
   // the teardown of the CUDA context.
@@ -430,7 +444,27 @@ at::Tensor& status_word(const at::Device& device) {
   return (*words)[idx];
 }
 
+// MB200_GEMM_TMA_STORE=0 keeps every output store on the LSU path.
+bool store_tma_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("MB200_GEMM_TMA_STORE");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return on;
+}
+
+// [CTA][16] cycle counters written by builds with -DMB_GEMM_TIMING (zero otherwise).
+at::Tensor& timing_words(const at::Device& device) {
+  static auto* words = new std::vector<at::Tensor>(64);
+  const int idx = device.index();
+  if (!(*words)[idx].defined())
+    (*words)[idx] = at::zeros({1024, 16}, at::TensorOptions().device(device).dtype(at::kLong));
+  return (*words)[idx];
+}
+
 }  // namespace
+
+at::Tensor gemm_role_timers(const at::Tensor& like) { return timing_words(like.device()); }
 
 // True when the tcgen05 kernel can run this problem; the Python caller falls back
 // to per-group library matmuls otherwise (odd sizes, fp32 inputs).
@@ -516,6 +550,9 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   p.c = c.data_ptr();
   p.status = status_word(a.device()).data_ptr<int>();
+#ifdef MB_GEMM_TIMING
+  p.timing = reinterpret_cast<long long*>(timing_words(a.device()).data_ptr<int64_t>());
+#endif
   p.zero_tail = zero_tail ? 1 : 0;
   if (wait_flags.has_value()) {
     TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == at::kInt && layout != kTN,
@@ -588,6 +625,14 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.M, 64);
     tb = make_tensor_map(b.data_ptr(), bf16, b.size(0), p.N, 64);
     tiles_bound = num_groups * ceil_div(p.M, kBlockM) * num_nb;
+  }
+  if (!scatter.has_value() && store_tma_enabled()) {
+    // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
+    const int64_t out_rows = out_numel / p.N;
+    bool ok = make_output_map(&p.out_map[0], p.c, bf16, out_rows, p.N);
+    if (ok && p.out2) ok = make_output_map(&p.out_map[1], p.out2, bf16, out_rows, p.N);
+    if (ok && p.out3) ok = make_output_map(&p.out_map[2], p.out3, bf16, out_rows, p.N);
+    p.store_tma = ok ? 1 : 0;
   }
   const int grid = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count())));
   MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, grid, stream()));

@@ -29,6 +29,13 @@ NVCC_FLAGS = [
     '-U__CUDA_NO_BFLOAT16_CONVERSIONS__',
 ]
 
+# MB200_GEMM_TIMING=1: diagnostic build whose grouped GEMM records per-role wait cycles
+# (read back with `_C.gemm_role_timers`).
+DEFINES = ['-DMB_GEMM_TIMING'] if os.environ.get('MB200_GEMM_TIMING') == '1' else []
+if os.environ.get('MB200_GEMM_NO_STORE') == '1':
+    DEFINES.append('-DMB_GEMM_NO_STORE')
+NVCC_FLAGS += DEFINES
+
 sources = sorted(glob.glob(os.path.join(CSRC, '*.cu'))) + sorted(glob.glob(os.path.join(CSRC, '*.cpp')))
 
 setup(
@@ -40,7 +47,7 @@ setup(
             name='megablocks_b200._C',
             sources=sources,
             include_dirs=[os.path.join(ROOT, CSRC)],
-            extra_compile_args={'cxx': ['-O3', '-std=c++17'], 'nvcc': NVCC_FLAGS},
+            extra_compile_args={'cxx': ['-O3', '-std=c++17'] + DEFINES, 'nvcc': NVCC_FLAGS},
         )
     ],
     cmdclass={'build_ext': BuildExtension.with_options(use_ninja=True)},
