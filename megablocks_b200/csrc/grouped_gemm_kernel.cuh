@@ -292,6 +292,78 @@ __device__ __forceinline__ float epilogue_value(const uint32_t (&raw)[32], const
   }
 }
 
+// Activation backward: both outputs of element `i` from one evaluation of the activation's
+// transcendental (dz = acc * act'(z), h = act(z)).
+template <typename T, int ACT>
+__device__ __forceinline__ void dact_values(float acc, float z, float& dz, float& h) {
+  if constexpr (ACT == kActGeluTanh) {
+    const float u = z * z;
+    const float t = tanh_fast(z * (0.7978845608f + 0.0356774081f * u));
+    const float hz = 0.5f * z;
+    h = fmaf(hz, t, hz);
+    const float g = fmaf(u, 0.1070322243f, 0.7978845608f);          // d(inner)/dz
+    const float d = fmaf(hz * fmaf(-t, t, 1.f), g, fmaf(t, 0.5f, 0.5f));
+    dz = acc * d;
+  } else if constexpr (ACT == kActSilu) {
+    const float sg = 1.f / (1.f + __expf(-z));
+    h = z * sg;
+    dz = acc * (sg * (1.f + z * (1.f - sg)));
+  } else {
+    h = act_fwd<ACT>(z);
+    dz = acc * act_bwd<ACT>(z);
+  }
+}
+
+// One pass over the chunk for the activation-backward epilogue: dz goes to the staging buffer as
+// it is produced, h waits packed in registers until the buffer is free again.
+template <typename T, int ACT>
+__device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], const PackedRow& a1, uint8_t* stage,
+                                                   T* out, T* out2, int64_t row_stride, int rows_ok, int cols,
+                                                   int lane, int col, const CUtensorMap* maps, TmaOut tma) {
+  uint4 hw[4];
+  if (maps != nullptr) stage_acquire(lane);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    float dz[8], h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      dact_values<T, ACT>(__uint_as_float(raw[v * 8 + j]), packed_at<T>(a1, v * 8 + j), dz[j], h[j]);
+    uint4 w;
+    w.x = pack2<T>(dz[0], dz[1]); w.y = pack2<T>(dz[2], dz[3]); w.z = pack2<T>(dz[4], dz[5]); w.w = pack2<T>(dz[6], dz[7]);
+    hw[v].x = pack2<T>(h[0], h[1]); hw[v].y = pack2<T>(h[2], h[3]);
+    hw[v].z = pack2<T>(h[4], h[5]); hw[v].w = pack2<T>(h[6], h[7]);
+    *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
+  }
+  if (tma.on) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(maps, smem_u32(stage), col, tma.row);
+      bulk_commit_group();
+    }
+  } else {
+    __syncwarp();
+    stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
+    __syncwarp();
+  }
+  if (out2 == nullptr) return;
+  if (maps != nullptr) stage_acquire(lane);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = hw[v];
+  if (tma.on) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(maps + 1, smem_u32(stage), col, tma.row);
+      bulk_commit_group();
+    }
+  } else {
+    __syncwarp();
+    stage_store<T>(stage, out2, row_stride, rows_ok, cols, lane);
+    __syncwarp();
+  }
+}
+
 // Computes one output of the chunk, packs it eight columns at a time into this thread's
 // staging row and stores the chunk coalesced.  Only the accumulator row and the packed
 // auxiliary rows stay in registers.
@@ -341,6 +413,12 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const 
                                                const GemmParams& p, const ScatterRows<T>* scatter, int col,
                                                TmaOut tma) {
   const CUtensorMap* maps = p.store_tma ? p.out_map : nullptr;
+  if constexpr (EPI == kEpiDAct) {
+    epilogue_emit_dact<T, ACT>(raw, a1, stage, static_cast<T*>(p.c) + base_off,
+                               p.out2 ? static_cast<T*>(p.out2) + base_off : nullptr, row_stride, rows_ok, cols,
+                               lane, col, maps, tma);
+    return;
+  }
   epilogue_emit<T, EPI, ACT, 0>(raw, a1, a2, stage, static_cast<T*>(p.c) + base_off, row_stride, rows_ok, cols,
                                 lane, scatter, col, maps, tma);
   if constexpr (EPI == kEpiAct || EPI == kEpiDAct || EPI == kEpiGlu || EPI == kEpiDGlu) {

@@ -565,6 +565,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   if (scatter.has_value()) {
     // scatter = {data heap bases, flag heap bases, counts, done}; scatter_args = {data offset, flag
     // offset, world, rank, experts, seq}.
+    TORCH_CHECK(epilogue == kEpiNone || epilogue == kEpiAdd, "the fused combine supports the plain and the add epilogue");
     TORCH_CHECK(layout == kNN && scatter->size() == 4 && scatter_args.size() == 6,
                 "the fused combine needs the NN layout, four tensors and six integers");
     const auto& bases = (*scatter)[0];
