@@ -118,6 +118,32 @@ __device__ __forceinline__ float act_bwd(float x) {
   }
 }
 
+// ---- packed fp32 pairs (sm_100 f32x2 arithmetic: two elements per instruction) ------------
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+
+// tanh-GELU of a pair: 0.5 z (1 + tanh(z (k + k c z^2))).
+__device__ __forceinline__ float2 gelu_tanh_fwd2(float2 z) {
+  const float2 u = __fmul2_rn(z, z);
+  const float2 inner = __fmul2_rn(z, __ffma2_rn(u, splat2(0.0356774081f), splat2(0.7978845608f)));
+  const float2 t = make_float2(tanh_fast(inner.x), tanh_fast(inner.y));
+  const float2 hz = __fmul2_rn(z, splat2(0.5f));
+  return __ffma2_rn(hz, t, hz);
+}
+
+// tanh-GELU and its derivative times `acc` for a pair, from one tanh per element.
+__device__ __forceinline__ void gelu_tanh_dact2(float2 acc, float2 z, float2& dz, float2& h) {
+  const float2 u = __fmul2_rn(z, z);
+  const float2 inner = __fmul2_rn(z, __ffma2_rn(u, splat2(0.0356774081f), splat2(0.7978845608f)));
+  const float2 t = make_float2(tanh_fast(inner.x), tanh_fast(inner.y));
+  const float2 hz = __fmul2_rn(z, splat2(0.5f));
+  h = __ffma2_rn(hz, t, hz);
+  const float2 neg_g = __ffma2_rn(u, splat2(-0.1070322243f), splat2(-0.7978845608f));   // -d(inner)/dz
+  const float2 s = __ffma2_rn(t, t, splat2(-1.f));                                         // t^2 - 1
+  const float2 q = __ffma2_rn(t, splat2(0.5f), splat2(0.5f));
+  const float2 d = __ffma2_rn(__fmul2_rn(hz, s), neg_g, q);
+  dz = __fmul2_rn(acc, d);
+}
+
 template <typename T>
 struct Vec8 {
   T v[8];
@@ -268,6 +294,13 @@ __device__ __forceinline__ float packed_at(const PackedRow& row, int i) {
   return unpack_half<T>(word_of(row.q[i >> 3], (i & 7) >> 1), i & 1);
 }
 
+// Elements (2w, 2w + 1) of a packed row as a pair.
+template <typename T>
+__device__ __forceinline__ float2 packed_pair(const PackedRow& row, int w) {
+  const uint32_t word = word_of(row.q[w >> 2], w & 3);
+  return make_float2(unpack_half<T>(word, 0), unpack_half<T>(word, 1));
+}
+
 // Element `i` of output number WHICH (0 = c, 1 = out2, 2 = out3) of the fused epilogue.
 template <typename T, int EPI, int ACT, int WHICH>
 __device__ __forceinline__ float epilogue_value(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
@@ -325,9 +358,20 @@ __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], co
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     float dz[8], h[8];
+    if constexpr (ACT == kActGeluTanh) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      dact_values<T, ACT>(__uint_as_float(raw[v * 8 + j]), packed_at<T>(a1, v * 8 + j), dz[j], h[j]);
+      for (int j = 0; j < 4; ++j) {
+        float2 dz2, h2;
+        gelu_tanh_dact2(make_float2(__uint_as_float(raw[v * 8 + 2 * j]), __uint_as_float(raw[v * 8 + 2 * j + 1])),
+                        packed_pair<T>(a1, v * 4 + j), dz2, h2);
+        dz[2 * j] = dz2.x; dz[2 * j + 1] = dz2.y;
+        h[2 * j] = h2.x; h[2 * j + 1] = h2.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        dact_values<T, ACT>(__uint_as_float(raw[v * 8 + j]), packed_at<T>(a1, v * 8 + j), dz[j], h[j]);
+    }
     uint4 w;
     w.x = pack2<T>(dz[0], dz[1]); w.y = pack2<T>(dz[2], dz[3]); w.z = pack2<T>(dz[4], dz[5]); w.w = pack2<T>(dz[6], dz[7]);
     hw[v].x = pack2<T>(h[0], h[1]); hw[v].y = pack2<T>(h[2], h[3]);
@@ -364,6 +408,21 @@ __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], co
   }
 }
 
+// Elements (i, i + 1) of output WHICH, packed to 16 bits.
+template <typename T, int EPI, int ACT, int WHICH>
+__device__ __forceinline__ uint32_t epilogue_pair(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
+                                                  int i) {
+  if constexpr (EPI == kEpiAct && ACT == kActGeluTanh && WHICH == 1) {
+    // act(round(acc)): round through the 16-bit type first, as the unfused sequence does.
+    const uint32_t rounded = pack2<T>(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+    const float2 h = gelu_tanh_fwd2(make_float2(unpack_half<T>(rounded, 0), unpack_half<T>(rounded, 1)));
+    return pack2<T>(h.x, h.y);
+  } else {
+    return pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, i),
+                    epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, i + 1));
+  }
+}
+
 // Computes one output of the chunk, packs it eight columns at a time into this thread's
 // staging row and stores the chunk coalesced.  Only the accumulator row and the packed
 // auxiliary rows stay in registers.
@@ -376,14 +435,10 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     uint4 w;
-    w.x = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 0),
-                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 1));
-    w.y = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 2),
-                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 3));
-    w.z = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 4),
-                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 5));
-    w.w = pack2<T>(epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 6),
-                   epilogue_value<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 7));
+    w.x = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 0);
+    w.y = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 2);
+    w.z = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 4);
+    w.w = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 6);
     *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
   }
   if (tma.on) {
