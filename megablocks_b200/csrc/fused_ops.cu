@@ -194,9 +194,11 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
 
 // Same, for rows of at most 32 * MAXV * VEC elements: every lane owns fixed columns, so
 // the weight / bias gradients accumulate in registers across the rows a warp visits and
-// meet in shared memory once at the end (no per-element atomics).
+// meet in shared memory once at the end (no per-element atomics).  The row's operands stay
+// packed (16-bit) in registers between the two passes, which keeps the kernel at two CTAs
+// per SM; all loads of a row are issued before the first use.
 template <typename T, int MAXV>
-__global__ void __launch_bounds__(kLnWarps * 32)
+__global__ void __launch_bounds__(kLnWarps * 32, 2)
 layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                          const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
                          T* __restrict__ dx, float* __restrict__ partial) {
@@ -205,40 +207,45 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  float dg_acc[MAXV][VEC], db_acc[MAXV][VEC], g_reg[MAXV][VEC];
+  float dg_acc[MAXV][VEC], db_acc[MAXV][VEC];
+  Pack<T, VEC> pg[MAXV];
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
     const int c = (j * 32 + lane) * VEC;
-    Pack<T, VEC> pg;
-    if (c < cols) pg = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+    if (c < cols) pg[j] = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       dg_acc[j][k] = 0.f;
       db_acc[j][k] = 0.f;
-      g_reg[j][k] = c < cols ? to_float(pg.v[k]) : 0.f;
+      if (c >= cols) pg[j].v[k] = from_float<T>(0.f);
     }
   }
   const int64_t stride = int64_t(gridDim.x) * kLnWarps;
   for (int64_t r = int64_t(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); r < rows; r += stride) {
     const T* xr = x + r * cols;
     const T* dr = dy + r * cols;
+    Pack<T, VEC> px[MAXV], pd[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) {
+        px[j] = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+        pd[j] = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
+      }
+    }
     const float mu = mean[r], rs = rstd[r];
-    float xhat[MAXV][VEC], dgv[MAXV][VEC];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) {
-        Pack<T, VEC> px = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
-        Pack<T, VEC> pd = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
-          const float xh = (to_float(px.v[k]) - mu) * rs;
-          const float d = to_float(pd.v[k]);
-          xhat[j][k] = xh;
-          dgv[j][k] = d * g_reg[j][k];
-          s1 += dgv[j][k] * xh;
-          s2 += dgv[j][k];
+          const float xh = (to_float(px[j].v[k]) - mu) * rs;
+          const float d = to_float(pd[j].v[k]);
+          const float dg = d * to_float(pg[j].v[k]);
+          s1 += dg * xh;
+          s2 += dg;
           dg_acc[j][k] += d * xh;
           db_acc[j][k] += d;
         }
@@ -253,7 +260,11 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
       if (c < cols) {
         Pack<T, VEC> po;
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) po.v[k] = from_float<T>(rs * (dgv[j][k] - s2 - xhat[j][k] * s1));
+        for (int k = 0; k < VEC; ++k) {
+          const float xh = (to_float(px[j].v[k]) - mu) * rs;
+          const float dg = to_float(pd[j].v[k]) * to_float(pg[j].v[k]);
+          po.v[k] = from_float<T>(rs * (dg - s2 - xh * s1));
+        }
         *reinterpret_cast<Pack<T, VEC>*>(dxr + c) = po;
       }
     }
@@ -274,6 +285,63 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) out[c] = acc[c];
 }
 
+// Forward for rows of at most 32 * MAXV * VEC elements: the row is read once and stays in
+// registers between the statistics and the normalisation; weight and bias are loaded once per warp.
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                         int64_t rows, int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
+                         float* __restrict__ rstd_out) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  Pack<T, VEC> pg[MAXV], pb[MAXV];
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    if (c < cols) {
+      pg[j] = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+      pb[j] = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
+    }
+  }
+  const float inv_cols = 1.f / cols;
+  const int64_t stride = int64_t(gridDim.x) * kLnWarps;
+  for (int64_t r = int64_t(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); r < rows; r += stride) {
+    const T* xr = x + r * cols;
+    Pack<T, VEC> px[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) px[j] = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+    }
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { const float v = to_float(px[j].v[k]); s += v; ss += v * v; }
+      }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mean = s * inv_cols;
+    const float rstd = rsqrtf(fmaxf(ss * inv_cols - mean * mean, 0.f) + eps);
+    if (lane == 0) { mean_out[r] = mean; rstd_out[r] = rstd; }
+    T* yr = y + r * cols;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < cols) {
+        Pack<T, VEC> po;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k)
+          po.v[k] = from_float<T>((to_float(px[j].v[k]) - mean) * rstd * to_float(pg[j].v[k]) + to_float(pb[j].v[k]));
+        *reinterpret_cast<Pack<T, VEC>*>(yr + c) = po;
+      }
+    }
+  }
+}
+
 // dgamma / dbeta = column sums of the per-CTA partials.
 template <typename T>
 __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int cols,
@@ -283,6 +351,37 @@ __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, i
   float s = 0.f;
   for (int p = 0; p < num_partials; ++p) s += partial[int64_t(p) * 2 * cols + c];
   if (c < cols) dgamma[c] = from_float<T>(s); else dbeta[c - cols] = from_float<T>(s);
+}
+
+template <typename T>
+void launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
+                          float* mean, float* rstd, int sms, cudaStream_t stream) {
+  constexpr int kVec = 16 / sizeof(T);
+  const int grid = max(1, min(ceil_div(rows, kLnWarps), sms * 6));
+  const int packs = ceil_div(cols, 32 * kVec);
+  switch (packs) {
+    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
+    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
+    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
+    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
+    default:
+      layernorm_fwd_kernel<T><<<max(1, min(ceil_div(rows, kLnWarps), sms * 2)), kLnWarps * 32, 0, stream>>>(
+          x, gamma, beta, rows, cols, eps, y, mean, rstd);
+  }
+}
+
+template <typename T>
+void launch_layernorm_bwd(const T* dy, const T* x, const T* gamma, const float* mean, const float* rstd, int64_t rows,
+                          int cols, T* dx, float* partial, int grid, size_t smem, cudaStream_t stream) {
+  constexpr int kVec = 16 / sizeof(T);
+  const int packs = ceil_div(cols, 32 * kVec);
+  switch (packs) {
+    case 1: layernorm_bwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
+    case 2: layernorm_bwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
+    case 3: layernorm_bwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
+    case 4: layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
+    default: layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial);
+  }
 }
 
 }  // namespace
@@ -315,9 +414,8 @@ cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const vo
   if (rows == 0) return cudaSuccess;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    layernorm_fwd_kernel<T><<<layernorm_grid(rows, sms), kLnWarps * 32, 0, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), rows, cols, eps,
-        static_cast<T*>(y), mean, rstd);
+    launch_layernorm_fwd<T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), rows,
+                            cols, eps, static_cast<T*>(y), mean, rstd, sms, stream);
   })
   return cudaGetLastError();
 }
@@ -331,16 +429,8 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    constexpr int kVec = 16 / sizeof(T);
-    if (cols <= 32 * 4 * kVec) {
-      layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(
-          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
-          static_cast<T*>(dx), partial);
-    } else {
-      layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(
-          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
-          static_cast<T*>(dx), partial);
-    }
+    launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean,
+                            rstd, rows, cols, static_cast<T*>(dx), partial, grid, smem, stream);
     layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
   })

@@ -42,6 +42,7 @@ namespace gemm {
 using namespace ptx;
 
 constexpr int kUmmaK = 16;
+constexpr int kSmallGroups = 224;            // groups whose tables fit beside two sets of staging buffers
 constexpr int kMaxScatterSegments = 512;     // experts per rank x world of the fused combine
 constexpr int kEpilogueWarps = 8;            // two warps per TMEM lane quarter
 constexpr int kProducerWarp = kEpilogueWarps;       // warp 8: TMA loads
@@ -64,7 +65,9 @@ struct Config {
   // ring + barriers + tmem base + abort flag + group tables, plus slack for 1024-byte alignment
   static constexpr int kStagingBytes = kEpilogueWarps * 2048;   // one 32-row x 64-byte buffer per epilogue warp
   static constexpr int kScatterBytes = (2 * kMaxScatterSegments + 128) * 4;   // segment tables of the fused combine
-  static constexpr int kSmemBytes = kTileBytes + 256 + 2 * kMaxGroups * 4 + kStagingBytes + kScatterBytes + 1024;
+  // ring, two sets of staging buffers (the second doubles as the large-table area), barriers, small tables, alignment slack
+  static constexpr int kSmemBytes = kTileBytes + 2 * kStagingBytes + 256 + 2 * kSmallGroups * 4 + 1024;
+  static_assert(2 * kMaxGroups * 4 + kScatterBytes <= kStagingBytes, "large tables must fit the alternate staging area");
 };
 
 struct Tile {
@@ -247,10 +250,28 @@ struct TmaOut {
   int row;
 };
 
+// A warp's staging buffer(s).  With two buffers (`other` = byte distance to the alternate one,
+// 0 = single buffer) consecutive TMA stores alternate, so the second output of a chunk does not
+// wait for the TMA unit to finish reading the first.
+struct Staging {
+  uint8_t* buf;
+  int other;
+};
+
 // Before a staging buffer is rewritten the bulk store that last read it must be done reading.
-__device__ __forceinline__ void stage_acquire(int lane) {
-  if (lane == 0) bulk_wait_read_all();
+// With alternating buffers that is the store before the latest one.
+__device__ __forceinline__ void stage_acquire(const Staging& st, int lane) {
+  if (lane == 0) {
+    if (st.other != 0) bulk_wait_read_but_one();
+    else bulk_wait_read_all();
+  }
   __syncwarp();
+}
+
+// After a TMA store was issued from the current buffer: continue in the other one.
+__device__ __forceinline__ void stage_flip(Staging& st) {
+  st.buf += st.other;
+  st.other = -st.other;
 }
 
 // This thread's row of the staging buffer, kept packed (16 registers for 32 values).
@@ -350,11 +371,11 @@ __device__ __forceinline__ void dact_values(float acc, float z, float& dz, float
 // One pass over the chunk for the activation-backward epilogue: dz goes to the staging buffer as
 // it is produced, h waits packed in registers until the buffer is free again.
 template <typename T, int ACT>
-__device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], const PackedRow& a1, uint8_t* stage,
+__device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], const PackedRow& a1, Staging& stage,
                                                    T* out, T* out2, int64_t row_stride, int rows_ok, int cols,
                                                    int lane, int col, const CUtensorMap* maps, TmaOut tma) {
   uint4 hw[4];
-  if (maps != nullptr) stage_acquire(lane);
+  if (maps != nullptr) stage_acquire(stage, lane);
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     float dz[8], h[8];
@@ -376,34 +397,36 @@ __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], co
     w.x = pack2<T>(dz[0], dz[1]); w.y = pack2<T>(dz[2], dz[3]); w.z = pack2<T>(dz[4], dz[5]); w.w = pack2<T>(dz[6], dz[7]);
     hw[v].x = pack2<T>(h[0], h[1]); hw[v].y = pack2<T>(h[2], h[3]);
     hw[v].z = pack2<T>(h[4], h[5]); hw[v].w = pack2<T>(h[6], h[7]);
-    *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
+    *reinterpret_cast<uint4*>(stage.buf + stage_offset(lane, v)) = w;
   }
   if (tma.on) {
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(maps, smem_u32(stage), col, tma.row);
+      tma_store_2d(maps, smem_u32(stage.buf), col, tma.row);
       bulk_commit_group();
     }
+    stage_flip(stage);
   } else {
     __syncwarp();
-    stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
+    stage_store<T>(stage.buf, out, row_stride, rows_ok, cols, lane);
     __syncwarp();
   }
   if (out2 == nullptr) return;
-  if (maps != nullptr) stage_acquire(lane);
+  if (maps != nullptr) stage_acquire(stage, lane);
 #pragma unroll
-  for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = hw[v];
+  for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(stage.buf + stage_offset(lane, v)) = hw[v];
   if (tma.on) {
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(maps + 1, smem_u32(stage), col, tma.row);
+      tma_store_2d(maps + 1, smem_u32(stage.buf), col, tma.row);
       bulk_commit_group();
     }
+    stage_flip(stage);
   } else {
     __syncwarp();
-    stage_store<T>(stage, out2, row_stride, rows_ok, cols, lane);
+    stage_store<T>(stage.buf, out2, row_stride, rows_ok, cols, lane);
     __syncwarp();
   }
 }
@@ -428,10 +451,10 @@ __device__ __forceinline__ uint32_t epilogue_pair(const uint32_t (&raw)[32], con
 // auxiliary rows stay in registers.
 template <typename T, int EPI, int ACT, int WHICH>
 __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const PackedRow& a1, const PackedRow& a2,
-                                              uint8_t* stage, T* out, int64_t row_stride, int rows_ok, int cols,
+                                              Staging& stage, T* out, int64_t row_stride, int rows_ok, int cols,
                                               int lane, const ScatterRows<T>* scatter = nullptr, int col = 0,
                                               const CUtensorMap* tmap = nullptr, TmaOut tma = TmaOut{false, 0}) {
-  if (tmap != nullptr) stage_acquire(lane);
+  if (tmap != nullptr) stage_acquire(stage, lane);
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     uint4 w;
@@ -439,7 +462,7 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
     w.y = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 2);
     w.z = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 4);
     w.w = epilogue_pair<T, EPI, ACT, WHICH>(raw, a1, a2, v * 8 + 6);
-    *reinterpret_cast<uint4*>(stage + stage_offset(lane, v)) = w;
+    *reinterpret_cast<uint4*>(stage.buf + stage_offset(lane, v)) = w;
   }
   if (tma.on) {
     // The staging layout is the 64-byte swizzle of a 32 x 32 box: one thread hands the chunk to
@@ -447,14 +470,15 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(tmap, smem_u32(stage), col, tma.row);
+      tma_store_2d(tmap, smem_u32(stage.buf), col, tma.row);
       bulk_commit_group();
     }
+    stage_flip(stage);
     return;
   }
   __syncwarp();
-  if (scatter != nullptr) stage_store_rows<T>(stage, *scatter, col, cols, lane);
-  else stage_store<T>(stage, out, row_stride, rows_ok, cols, lane);
+  if (scatter != nullptr) stage_store_rows<T>(stage.buf, *scatter, col, cols, lane);
+  else stage_store<T>(stage.buf, out, row_stride, rows_ok, cols, lane);
   __syncwarp();
 }
 
@@ -463,7 +487,7 @@ __device__ __forceinline__ void epilogue_emit(const uint32_t (&raw)[32], const P
 // chunk's first row / first column in the output, `rows_ok` / `cols` its valid extent.
 template <typename T, int EPI, int ACT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const PackedRow& a1,
-                                               const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                               const PackedRow& a2, Staging& stage, int64_t base_off,
                                                int64_t row_stride, int rows_ok, int cols, int lane,
                                                const GemmParams& p, const ScatterRows<T>* scatter, int col,
                                                TmaOut tma) {
@@ -490,7 +514,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const 
 
 template <typename T, int EPI>
 __device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], const PackedRow& a1,
-                                                const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                                const PackedRow& a2, Staging& stage, int64_t base_off,
                                                 int64_t row_stride, int rows_ok, int cols, int lane,
                                                 const GemmParams& p, const ScatterRows<T>* scatter, int col,
                                                 TmaOut tma) {
@@ -506,7 +530,7 @@ __device__ __forceinline__ void epilogue_by_act(const uint32_t (&raw)[32], const
 // One dispatch per 32-column chunk (uniform across the warp); straight-line code inside.
 template <typename T>
 __device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], const PackedRow& a1,
-                                                  const PackedRow& a2, uint8_t* stage, int64_t base_off,
+                                                  const PackedRow& a2, Staging& stage, int64_t base_off,
                                                   int64_t row_stride, int rows_ok, int cols, int lane,
                                                   const GemmParams& p, const ScatterRows<T>* scatter = nullptr,
                                                   int col = 0, TmaOut tma = TmaOut{false, 0}) {
@@ -525,7 +549,7 @@ __device__ __forceinline__ void epilogue_dispatch(const uint32_t (&raw)[32], con
 // waiting on its barriers (slots: 0 MMA waits for operands, 1 MMA waits for a free accumulator,
 // 2 MMA role total, 3 producer waits for a free stage, 4 epilogue warp 0 waits for an accumulator,
 // 5 epilogue warp 0 total, 6 its tcgen05.ld time, 7 its convert / stage / store time, 8 its per-tile
-// preamble, 9 its whole chunk loop, 10 its accumulator release).
+// preamble, 9 its whole chunk loop, 10 its accumulator release, 11 its auxiliary-operand loads).
 #ifdef MB_GEMM_TIMING
 #define MB_T_DECL(name) long long name = 0
 #define MB_T_BEGIN(var) const long long var = clock64()
@@ -554,7 +578,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint8_t* smem_b = smem + kStages * kABytes;
   // Staging buffers directly after the operand ring: 1024-byte aligned, as the swizzled TMA stores need.
   uint8_t* staging = smem + Cfg::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint8_t* staging1 = staging + Cfg::kStagingBytes;   // alternate buffers, or the large tables
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging1 + Cfg::kStagingBytes);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + kStages;            // [kStages]
   uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2]
@@ -562,13 +587,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   uint64_t* scatter_bar = bars + 2 * kStages + 6;  // [2] fused combine: "all warps stored this tile"
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  int* s_row_end = reinterpret_cast<int*>(staging + Cfg::kStagingBytes + 256);   // [kMaxGroups]
-  int* s_mblk_end = s_row_end + kMaxGroups;                                 // [kMaxGroups]
+  const bool scatter_on = LAYOUT == kNN && p.scatter_base != nullptr;
+  // Up to kSmallGroups groups the tables fit behind the barriers; more groups, or the segment tables
+  // of the fused combine, take the place of the alternate staging buffers.
+  const bool big_tables = p.num_groups > kSmallGroups || scatter_on;
+  int* tables = big_tables ? reinterpret_cast<int*>(staging1)
+                           : reinterpret_cast<int*>(staging1 + Cfg::kStagingBytes + 256);
+  int* s_row_end = tables;                                                   // [groups]
+  int* s_mblk_end = tables + (big_tables ? kMaxGroups : kSmallGroups);       // [groups]
   // Fused combine (NN layout only): per (local expert, source rank) segment tables.
   int* s_seg_end = s_mblk_end + kMaxGroups;
   int* s_remote_start = s_seg_end + kMaxScatterSegments;
   int* s_per_source = s_remote_start + kMaxScatterSegments;                 // [world] rows returned to each source
-  const bool scatter_on = LAYOUT == kNN && p.scatter_base != nullptr;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -817,7 +847,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ======================= epilogue warps ======================================
     const int quarter = warp & 3;               // TMEM lane quarter this warp may read
     const int half = warp >> 2;                 // which of the two warps of that quarter
-    uint8_t* stage = staging + warp * 2048;
+    Staging stage{staging + warp * 2048, (p.store_tma != 0 && !big_tables) ? Cfg::kStagingBytes : 0};
     constexpr int kChunks = BLOCK_N / 32;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
@@ -829,6 +859,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     MB_T_DECL(t_pre);
     MB_T_DECL(t_loop);
     MB_T_DECL(t_post);
+    MB_T_DECL(t_aux);
     MB_T_BEGIN(role0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       MB_T_BEGIN(wpre);
@@ -901,27 +932,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      min(32, p.N - ncol), lane);
         }
         PackedRow a1, a2;
+        MB_T_BEGIN(waux);
         if (rows_ok > 0) {
           const int cols = min(32, p.N - col);
           if (need1) {
-            if (p.store_tma) stage_acquire(lane);
-            stage_load<T>(stage, static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok, cols, lane);
+            if (p.store_tma) stage_acquire(stage, lane);
+            stage_load<T>(stage.buf, static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok, cols, lane);
             __syncwarp();
-            stage_read_row(stage, lane, a1);
+            stage_read_row(stage.buf, lane, a1);
             __syncwarp();
           }
           if (need2) {
-            stage_load<T>(stage, static_cast<const T*>(p.aux2) + row_off + col, p.N, rows_ok, cols, lane);
+            stage_load<T>(stage.buf, static_cast<const T*>(p.aux2) + row_off + col, p.N, rows_ok, cols, lane);
             __syncwarp();
-            stage_read_row(stage, lane, a2);
+            stage_read_row(stage.buf, lane, a2);
             __syncwarp();
           }
         }
+        MB_T_END(waux, t_aux);
         uint32_t raw[32];
         MB_T_BEGIN(w1);
         if (has_k) {
           tmem_ld_32x32(taddr + c0, raw);
           tmem_ld_wait();
+          if (p.alpha != 1.f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * p.alpha);
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) raw[i] = 0u;
@@ -984,6 +1021,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       MB_T_WRITE(8, t_pre);
       MB_T_WRITE(9, t_loop);
       MB_T_WRITE(10, t_post);
+      MB_T_WRITE(11, t_aux);
     }
     // Rows past the last group belong to nobody: defined as zero (NT / NN only).
     if (LAYOUT != kTN && p.zero_tail) {

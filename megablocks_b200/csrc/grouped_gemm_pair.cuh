@@ -220,6 +220,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int quarter = warp & 3;
     const int half = warp >> 2;
     uint8_t* stage_buf = smem + kPairTileBytes + 256 + 2 * kMaxGroups * 4 + warp * 2048;
+    Staging stage{stage_buf, 0};
     constexpr int kChunks = BLOCK_N / 32;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
@@ -277,8 +278,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t raw[32];
         tmem_ld_32x32(taddr + c0, raw);
         tmem_ld_wait();
+        if (p.alpha != 1.f) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * p.alpha);
+        }
         if (rows_ok > 0)
-          epilogue_dispatch<T>(raw, a1, a2, stage_buf, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p);
+          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p);
       }
       tcgen05_fence_before();
       __syncwarp();

@@ -148,6 +148,7 @@ struct GemmParams {
   const void* aux2;
   int epilogue;
   int act;
+  float alpha;      // every accumulator is multiplied by this before the epilogue (1 = off)
   int* status;      // device word that receives a code when a wait is abandoned
   int zero_tail;    // NT / NN: write zeros to the rows of c past the last group
   // Optional arrival flags (expert-parallel receive buffer): before the first load of

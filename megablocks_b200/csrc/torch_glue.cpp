@@ -493,7 +493,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
                                      int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
-                                     const std::vector<int64_t>& scatter_args) {
+                                     const std::vector<int64_t>& scatter_args, double alpha) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -532,6 +532,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   at::Tensor out2, out3;
   p.epilogue = int(epilogue);
   p.act = int(act);
+  p.alpha = float(alpha);
   if (epilogue == kEpiDAct || epilogue == kEpiGlu || epilogue == kEpiDGlu || epilogue == kEpiAdd) {
     check_aux(aux1, "aux1");
     p.aux1 = aux1->data_ptr();

@@ -163,15 +163,16 @@ class ParallelDroplessMLP(moe.ParallelMLP):
                                                 args.hidden_size, x2d.dtype, x2d.device)
             self._ep_workspace_key = key
         mlp = self.mlp
-        w1, w2 = mlp._weights()
+        # Unscaled weights: the 1 / world factor of their gradients is applied inside the wgrad GEMMs.
+        w1, w2 = mlp._raw_weights()
         v1 = None
         if args.mlp_type == 'glu':
-            w1, v1, w2 = mlp._glu_weights()
+            w1, v1, w2 = mlp._raw_glu_weights()
             v1 = mlp._grouped_view(v1)
         out = ep.fused_expert_parallel(x2d, expert_weights.to(x2d.dtype), mlp._grouped_view(w1),
                                        mlp._grouped_view(w2), v1, self._ep_workspace, indices, bin_ids, bins,
                                        tokens_per_expert, self.top_k, gg.activation_id(args.activation_fn),
-                                       args.memory_optimized_mlp)
+                                       args.memory_optimized_mlp, wgrad_scale=mlp.wgrad_scale())
         return out, tokens_per_expert
 
     # -- dispatch --------------------------------------------------------------

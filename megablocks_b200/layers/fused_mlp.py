@@ -43,8 +43,12 @@ def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tai
 
 
 def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True,
-                 rows_hint: int = 0, scatter=None):
-    """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded)."""
+                 rows_hint: int = 0, scatter=None, wgrad_scale: float = 1.0):
+    """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded).
+
+    ``wgrad_scale`` multiplies the weight gradients inside their GEMMs (the expert-parallel
+    gradient pre-scale of megablocks/layers/mlp.py:18-32 without its extra pass over the weights).
+    """
     z1, z2, h = saved
     num_experts = w1.shape[0]
     kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
@@ -59,11 +63,11 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
         h = h_new
     dx = dw1 = dw2 = dv1 = None
     if needs[2]:
-        dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts)
+        dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
     if needs[1]:
-        dw1, _, _ = G.grouped_gemm(dz1, x, bins, trans_a=True, num_groups=num_experts)
+        dw1, _, _ = G.grouped_gemm(dz1, x, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
     if v1 is not None and needs[3]:
-        dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts)
+        dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
     if needs[0]:
         # The GEMM that produces the final dx is the last reader of the receive buffers and, with
         # `scatter`, also the one that returns the rows to their sources.
@@ -78,7 +82,7 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
 class _ExpertMLP(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx: Any, x, w1, w2, v1, bins, act: int, memory_optimized: bool):
+    def forward(ctx: Any, x, w1, w2, v1, bins, act: int, memory_optimized: bool, wgrad_scale: float = 1.0):
         x = x.contiguous()
         y, (z1, z2, h) = mlp_forward(x, w1, w2, v1, bins, act, keep_h=not memory_optimized)
         saved = [x, w1, w2, bins, z1]
@@ -90,6 +94,7 @@ class _ExpertMLP(torch.autograd.Function):
         ctx.glu = v1 is not None
         ctx.act = act
         ctx.keep_h = h is not None
+        ctx.wgrad_scale = wgrad_scale
         return y
 
     @staticmethod
@@ -102,8 +107,9 @@ class _ExpertMLP(torch.autograd.Function):
         h = saved[-1] if ctx.keep_h else None
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2],
                  ctx.glu and ctx.needs_input_grad[3])
-        dx, dw1, dw2, dv1 = mlp_backward(dy.contiguous(), x, w1, w2, v1, bins, ctx.act, (z1, z2, h), needs)
-        return dx, dw1, dw2, dv1, None, None, None
+        dx, dw1, dw2, dv1 = mlp_backward(dy.contiguous(), x, w1, w2, v1, bins, ctx.act, (z1, z2, h), needs,
+                                         wgrad_scale=ctx.wgrad_scale)
+        return dx, dw1, dw2, dv1, None, None, None, None
 
 
 def _generic(x, w1, w2, v1, bins, activation_fn: Callable):
@@ -117,12 +123,17 @@ def _generic(x, w1, w2, v1, bins, activation_fn: Callable):
 
 def expert_mlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, bins: torch.Tensor,
                activation_fn: Optional[Callable], memory_optimized: bool = False,
-               v1: Optional[torch.Tensor] = None) -> torch.Tensor:
+               v1: Optional[torch.Tensor] = None, wgrad_scale: float = 1.0) -> torch.Tensor:
     """Apply every expert's MLP (or GLU when ``v1`` is given) to its group of rows.
 
-    ``w1``/``v1``/``w2`` are ``[E, f, h]`` views of the layer parameters.
+    ``w1``/``v1``/``w2`` are ``[E, f, h]`` views of the layer parameters; their gradients come out
+    multiplied by ``wgrad_scale``.
     """
     act = G.activation_id(activation_fn)
     if act is None:
+        if wgrad_scale != 1.0:
+            from megablocks_b200.layers.mlp import scale_gradient
+            w1, w2 = scale_gradient(w1, wgrad_scale), scale_gradient(w2, wgrad_scale)
+            v1 = scale_gradient(v1, wgrad_scale) if v1 is not None else None
         return _generic(x, w1, w2, v1, bins, activation_fn)
-    return _ExpertMLP.apply(x, w1, w2, v1, bins, act, memory_optimized)
+    return _ExpertMLP.apply(x, w1, w2, v1, bins, act, memory_optimized, wgrad_scale)

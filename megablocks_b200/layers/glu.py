@@ -33,12 +33,19 @@ class SparseGLU(SparseMLP):
         v1 = resolve_dtensor(self.scale_grad(self.v1))
         return w1, v1, w2
 
+    def _raw_glu_weights(self):
+        """Weights without the gradient-scaling node (pair with ``wgrad_scale()``)."""
+        w1, w2 = self._raw_weights()
+        return w1, resolve_dtensor(self.v1), w2
+
     def forward(self, x: torch.Tensor, topo) -> torch.Tensor:
-        w1, v1, w2 = self._glu_weights()
         padded_bins = getattr(topo, 'padded_bins', None)
         if padded_bins is not None:
+            w1, v1, w2 = self._raw_glu_weights()
             return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), padded_bins,
-                              self.args.activation_fn, self.args.memory_optimized_mlp, v1=self._grouped_view(v1))
+                              self.args.activation_fn, self.args.memory_optimized_mlp, v1=self._grouped_view(v1),
+                              wgrad_scale=self.wgrad_scale())
+        w1, v1, w2 = self._glu_weights()
         gate = sparse.sdd(x, w1.t(), topo)
         up = sparse.sdd(x, v1.t(), topo)
         hidden = sparse.mul(sparse.with_data(gate, self.args.activation_fn(gate.data)), up)
@@ -48,10 +55,10 @@ class SparseGLU(SparseMLP):
 class GroupedGLU(SparseGLU):
 
     def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
-        w1, v1, w2 = self._glu_weights()
+        w1, v1, w2 = self._raw_glu_weights()
         bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
         return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), bins, self.args.activation_fn,
-                          self.args.memory_optimized_mlp, v1=self._grouped_view(v1))
+                          self.args.memory_optimized_mlp, v1=self._grouped_view(v1), wgrad_scale=self.wgrad_scale())
 
 
 def memory_optimized_grouped_glu(x, w1, v1, w2, batch_sizes, activation_fn):

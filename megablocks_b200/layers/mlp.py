@@ -106,6 +106,10 @@ class _ExpertWeights(torch.nn.Module):
             return w
         return scale_gradient(w, self.gradient_scale)
 
+    def wgrad_scale(self) -> float:
+        """Factor for the fused expert MLP, which scales weight gradients inside their GEMMs."""
+        return 1.0 if self.gradient_scale is None else float(self.gradient_scale)
+
 
 class MLP(_ExpertWeights):
     """Experts applied to a dense ``[E_local, capacity, hidden]`` batch."""
@@ -170,6 +174,10 @@ class SparseMLP(_ExpertWeights):
         w2 = resolve_dtensor(self.scale_grad(self.w2))
         return w1, w2
 
+    def _raw_weights(self):
+        """Weights without the gradient-scaling node (pair with :meth:`wgrad_scale`)."""
+        return resolve_dtensor(self.w1), resolve_dtensor(self.w2)
+
     def _grouped_view(self, w: torch.Tensor) -> torch.Tensor:
         return w.view(mpu.experts_per_rank(self.args), -1, self.args.hidden_size)
 
@@ -180,11 +188,13 @@ class SparseMLP(_ExpertWeights):
         ``padded_bins``; they go straight to the grouped kernel.  Any other
         topology runs the general sdd / dsd products.
         """
-        w1, w2 = self._weights()
         padded_bins = getattr(topo, 'padded_bins', None)
         if padded_bins is not None:
+            w1, w2 = self._raw_weights()
             return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), padded_bins,
-                              self.args.activation_fn, self.args.memory_optimized_mlp)
+                              self.args.activation_fn, self.args.memory_optimized_mlp,
+                              wgrad_scale=self.wgrad_scale())
+        w1, w2 = self._weights()
         hidden = sparse.sdd(x, w1.t(), topo)
         hidden = sparse.with_data(hidden, self.args.activation_fn(hidden.data))
         return sparse.dsd(hidden, w2)
@@ -195,10 +205,10 @@ class GroupedMLP(SparseMLP):
 
     def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
         """``tokens_per_expert`` is the per-expert row count (device tensor; no host copy is made)."""
-        w1, w2 = self._weights()
+        w1, w2 = self._raw_weights()
         bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
         return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), bins, self.args.activation_fn,
-                          self.args.memory_optimized_mlp)
+                          self.args.memory_optimized_mlp, wgrad_scale=self.wgrad_scale())
 
 
 def memory_optimized_mlp(x, w1, w2, topo, activation_fn):

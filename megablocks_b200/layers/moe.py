@@ -62,10 +62,14 @@ def batched_load_balancing_loss(args: Arguments) -> torch.Tensor:
     for scores, counts in zip(expert_scores, tokens_per_expert):
         assert scores.dim() == 2 and scores.shape == (tokens, args.moe_num_experts)
         assert counts.dim() == 1 and counts.shape[0] == args.moe_num_experts
-    scores = torch.cat(expert_scores, dim=1)
-    if args.moe_lbl_in_fp32:
-        scores = scores.float()
-    scores = scores.mean(dim=0) if tokens != 0 else scores.sum(dim=0)
+    # Column means layer by layer, then one concatenation of the [E] vectors: the same numbers as
+    # reducing the concatenated [T, L * E] matrix, without materialising it.
+    reduced = []
+    for layer_scores in expert_scores:
+        if args.moe_lbl_in_fp32:
+            layer_scores = layer_scores.float()
+        reduced.append(layer_scores.mean(dim=0) if tokens != 0 else layer_scores.sum(dim=0))
+    scores = torch.cat(reduced)
     counts = torch.cat(tokens_per_expert).to(scores.dtype)
     scale = (args.moe_num_experts * args.moe_loss_weight) / (args.num_layers * tokens * args.moe_top_k)
     return scale * torch.dot(counts, scores)

@@ -180,7 +180,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
                  c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
-                 rows_hint: int = 0, scatter=None):
+                 rows_hint: int = 0, scatter=None, alpha: float = 1.0):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -196,6 +196,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     seq])`` (NN layout) stores every output row into the return buffer of the rank it came from
     instead of ``c`` and releases that rank's flag after its last row: the expert-parallel combine
     fused into the GEMM epilogue.  The returned ``c`` is then empty.
+    ``alpha`` multiplies every accumulator before the epilogue (e.g. the 1 / expert-parallel-world
+    factor of expert weight gradients, applied for free instead of by a separate pass).
     """
     if num_groups is None:
         num_groups = bins.numel()
@@ -205,7 +207,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
                                   int(count), int(stride), int(seq), int(rows_hint), _PAIR_MODE,
                                   scatter[0] if scatter is not None else None,
-                                  scatter[1] if scatter is not None else [])
+                                  scatter[1] if scatter is not None else [], float(alpha))
     if scatter is not None:
         raise RuntimeError('grouped_gemm: the fused combine needs the CUDA kernel (unsupported shape or dtype)')
     if wait is not None:
@@ -214,6 +216,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     # are not a multiple of 8 elements, more than 1024 groups) and every CPU tensor:
     # per-group matmuls in fp32.  On CUDA this reads the group sizes back to the host.
     acc = _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups)
+    if alpha != 1.0:
+        acc = acc * alpha
     out, out2, out3 = _cpu_epilogue(acc, epilogue, act, aux1, aux2, a.dtype)
     if not trans_a:
         # Rows past the last bin belong to no group: defined as zero.

@@ -277,10 +277,13 @@ class _FusedExpertParallel(torch.autograd.Function):
 
 
 def fused_expert_parallel(x, expert_weights, w1, w2, v1, workspace: EpWorkspace, indices, bin_ids, bins, tpe,
-                          top_k: int, act: int, memory_optimized: bool) -> torch.Tensor:
-    """``x[tokens, hidden]`` -> ``out[tokens, hidden]`` through the expert-parallel group of ``workspace``."""
+                          top_k: int, act: int, memory_optimized: bool, wgrad_scale: float = 1.0) -> torch.Tensor:
+    """``x[tokens, hidden]`` -> ``out[tokens, hidden]`` through the expert-parallel group of ``workspace``.
+
+    The gradients of ``w1`` / ``w2`` / ``v1`` come out multiplied by ``wgrad_scale``.
+    """
     return _FusedExpertParallel.apply(x, expert_weights, w1, w2, v1, workspace, indices, bin_ids, bins, tpe, top_k,
-                                      act, not memory_optimized)
+                                      act, not memory_optimized, wgrad_scale)
 
 
 def fused_path_available(args, x: torch.Tensor) -> bool:

@@ -45,7 +45,7 @@ def _ref_gmm(a, b, counts, trans_b):
 
 
 SHAPES = [(1, 128, 128, 128), (8, 1024, 256, 512), (4, 777, 192, 320), (16, 4096, 768, 3072), (64, 8192, 768, 3072),
-          (3, 100, 64, 64)]
+          (3, 100, 64, 64), (300, 6000, 64, 128)]   # last: more groups than the kernel's small tables hold
 
 
 @pytest.mark.parametrize('device', DEVICES)
