@@ -19,14 +19,16 @@ constexpr int kOptThreads = 256;
 template <typename T>
 __device__ __forceinline__ void load8f(const T* p, float (&out)[8]) {
   struct alignas(16) Raw { T v[8]; } raw;
-  *reinterpret_cast<uint4*>(&raw) = *reinterpret_cast<const uint4*>(p);
+  *reinterpret_cast<uint4*>(&raw) = __ldcs(reinterpret_cast<const uint4*>(p));
 #pragma unroll
   for (int i = 0; i < 8; ++i) out[i] = to_float(raw.v[i]);
 }
+// Optimizer state is touched once per step: streaming loads and stores keep it from displacing
+// anything useful in L2.
 template <>
 __device__ __forceinline__ void load8f<float>(const float* p, float (&out)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcs(reinterpret_cast<const float4*>(p + 4));
   out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
   out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
 }
@@ -39,8 +41,8 @@ __device__ __forceinline__ void store8f(T* p, const float (&in)[8]) {
 }
 template <>
 __device__ __forceinline__ void store8f<float>(float* p, const float (&in)[8]) {
-  *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(in[4], in[5], in[6], in[7]);
+  __stcs(reinterpret_cast<float4*>(p), make_float4(in[0], in[1], in[2], in[3]));
+  __stcs(reinterpret_cast<float4*>(p + 4), make_float4(in[4], in[5], in[6], in[7]));
 }
 
 // grad_scale_ptr[0] multiplies every gradient (clip coefficient x 1/accumulation).
@@ -68,7 +70,33 @@ adam_kernel(const AdamTensor* __restrict__ tensors, const int2* __restrict__ blo
   };
   // Chunks start at multiples of the chunk size, so alignment carries over from the base.
   const int64_t vec_end = vec_ok ? begin + ((end - begin) / 8) * 8 : begin;
-  for (int64_t i = begin + int64_t(threadIdx.x) * 8; i < vec_end; i += kOptThreads * 8) {
+  // Two independent 8-element batches per iteration: fourteen 16-byte loads in flight per thread.
+  int64_t i = begin + int64_t(threadIdx.x) * 8;
+  for (; i + kOptThreads * 8 < vec_end; i += 2 * kOptThreads * 8) {
+    const int64_t i2 = i + kOptThreads * 8;
+    float g[8], w[8], m[8], v[8], g2[8], w2[8], m2[8], v2[8];
+    load8f<G>(grad + i, g);
+    load8f<float>(t.master + i, w);
+    load8f<float>(t.exp_avg + i, m);
+    load8f<float>(t.exp_avg_sq + i, v);
+    load8f<G>(grad + i2, g2);
+    load8f<float>(t.master + i2, w2);
+    load8f<float>(t.exp_avg + i2, m2);
+    load8f<float>(t.exp_avg_sq + i2, v2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) update(g[j], w[j], m[j], v[j]);
+    store8f<float>(t.master + i, w);
+    store8f<float>(t.exp_avg + i, m);
+    store8f<float>(t.exp_avg_sq + i, v);
+    store8f<P>(param + i, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) update(g2[j], w2[j], m2[j], v2[j]);
+    store8f<float>(t.master + i2, w2);
+    store8f<float>(t.exp_avg + i2, m2);
+    store8f<float>(t.exp_avg_sq + i2, v2);
+    store8f<P>(param + i2, w2);
+  }
+  for (; i < vec_end; i += kOptThreads * 8) {
     float g[8], w[8], m[8], v[8];
     load8f<G>(grad + i, g);
     load8f<float>(t.master + i, w);
