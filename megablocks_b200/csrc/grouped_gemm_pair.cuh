@@ -43,14 +43,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairTileBytes);
+  // Staging buffers directly after the operand ring (1024-byte aligned for the swizzled TMA stores).
+  uint8_t* staging = smem + kPairTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpilogueWarps * 2048);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tmem_full_bar = bars + 2 * kStages;
   uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  int* s_row_end = reinterpret_cast<int*>(smem + kPairTileBytes + 256);
+  int* s_row_end = reinterpret_cast<int*>(staging + kEpilogueWarps * 2048 + 256);
   int* s_pair_end = s_row_end + kMaxGroups;      // inclusive prefix sum of 256-row blocks per group
 
   const int warp = threadIdx.x >> 5;
@@ -219,7 +221,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // ======================= epilogue warps (both CTAs, own 128 rows) ============
     const int quarter = warp & 3;
     const int half = warp >> 2;
-    uint8_t* stage_buf = smem + kPairTileBytes + 256 + 2 * kMaxGroups * 4 + warp * 2048;
+    uint8_t* stage_buf = staging + warp * 2048;
     Staging stage{stage_buf, 0};
     constexpr int kChunks = BLOCK_N / 32;
     int acc_stage = 0;
@@ -229,6 +231,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const Tile tile = decode(t);
       const int rows_ok = max(0, min(32, tile.rows_valid - quarter * 32));
       const int64_t row_off = int64_t(tile.row0 + quarter * 32) * p.N;
+      const TmaOut tma{p.store_tma != 0 && rows_ok == 32, tile.row0 + quarter * 32};
       const bool need1 = p.epilogue == kEpiDAct || p.epilogue == kEpiGlu || p.epilogue == kEpiDGlu ||
                          p.epilogue == kEpiAdd;
       const bool need2 = p.epilogue == kEpiDGlu;
@@ -263,6 +266,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (rows_ok > 0) {
           const int cols = min(32, p.N - col);
           if (need1) {
+            if (p.store_tma) stage_acquire(stage, lane);
             stage_load<T>(stage_buf, static_cast<const T*>(p.aux1) + row_off + col, p.N, rows_ok, cols, lane);
             __syncwarp();
             stage_read_row(stage_buf, lane, a1);
@@ -283,7 +287,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * p.alpha);
         }
         if (rows_ok > 0)
-          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p);
+          epilogue_dispatch<T>(raw, a1, a2, stage, row_off + col, p.N, rows_ok, min(32, p.N - col), lane, p, nullptr,
+                               col, tma);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -291,6 +296,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc_stage]), 0));
       if (++acc_stage == 2) { acc_stage = 0; acc_phase ^= 1u; }
     }
+    if (p.store_tma && lane == 0) bulk_wait_all();   // bulk stores complete before the CTA retires
     // Rows past the last group are defined as zero.
     if (p.zero_tail) {
       const int last = G > 0 ? s_row_end[G - 1] : 0;

@@ -602,6 +602,14 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   bool pair = layout != kTN && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
   if (pair_mode == 0) pair = false;
   else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048;
+  if (!scatter.has_value() && store_tma_enabled()) {
+    // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
+    const int64_t out_rows = out_numel / p.N;
+    bool ok = make_output_map(&p.out_map[0], p.c, bf16, out_rows, p.N);
+    if (ok && p.out2) ok = make_output_map(&p.out_map[1], p.out2, bf16, out_rows, p.N);
+    if (ok && p.out3) ok = make_output_map(&p.out_map[2], p.out3, bf16, out_rows, p.N);
+    p.store_tma = ok ? 1 : 0;
+  }
   CUtensorMap ta, tb;
   int64_t tiles_bound;
   const int64_t num_nb = ceil_div(p.N, block_n);
@@ -627,14 +635,6 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.M, 64);
     tb = make_tensor_map(b.data_ptr(), bf16, b.size(0), p.N, 64);
     tiles_bound = num_groups * ceil_div(p.M, kBlockM) * num_nb;
-  }
-  if (!scatter.has_value() && store_tma_enabled()) {
-    // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
-    const int64_t out_rows = out_numel / p.N;
-    bool ok = make_output_map(&p.out_map[0], p.c, bf16, out_rows, p.N);
-    if (ok && p.out2) ok = make_output_map(&p.out_map[1], p.out2, bf16, out_rows, p.N);
-    if (ok && p.out3) ok = make_output_map(&p.out_map[2], p.out3, bf16, out_rows, p.N);
-    p.store_tma = ok ? 1 : 0;
   }
   const int grid = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count())));
   MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, grid, stream()));
