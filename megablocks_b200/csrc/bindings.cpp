@@ -79,9 +79,11 @@ std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at
 void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
                              const c10::optional<at::Tensor>& scale, double scale_mul);
 std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
-                                          double eps);
+                                          double eps, const c10::optional<at::Tensor>& res);
 std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                           const at::Tensor& mean, const at::Tensor& rstd);
+                                           const at::Tensor& mean, const at::Tensor& rstd,
+                                           const c10::optional<at::Tensor>& dres);
+bool layernorm_can_fuse(const at::Tensor& x);
 
 // torch_glue.cpp: optimizer
 int64_t adam_record_size();
@@ -121,6 +123,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy_backward_", &mb::cross_entropy_backward_);
   m.def("layernorm_forward", &mb::layernorm_forward);
   m.def("layernorm_backward", &mb::layernorm_backward);
+  m.def("layernorm_can_fuse", &mb::layernorm_can_fuse);
   m.def("symm_alloc", &mb::symm_alloc);
   m.def("symm_open", &mb::symm_open);
   m.def("symm_close", &mb::symm_close);

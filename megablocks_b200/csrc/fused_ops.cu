@@ -201,7 +201,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32, 2)
 layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                          const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
-                         T* __restrict__ dx, float* __restrict__ partial) {
+                         T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dres) {
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float acc[];          // [2][cols]
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
@@ -258,12 +258,17 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
     for (int j = 0; j < MAXV; ++j) {
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) {
-        Pack<T, VEC> po;
+        // `dres`: gradient that reaches the normalised tensor on a second path (the residual
+        // stream); adding it here saves the separate accumulation pass.
+        Pack<T, VEC> po, pr;
+        if (dres != nullptr) pr = *reinterpret_cast<const Pack<T, VEC>*>(dres + r * cols + c);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
           const float xh = (to_float(px[j].v[k]) - mu) * rs;
           const float dg = to_float(pd[j].v[k]) * to_float(pg[j].v[k]);
-          po.v[k] = from_float<T>(rs * (dg - s2 - xh * s1));
+          float out = rs * (dg - s2 - xh * s1);
+          if (dres != nullptr) out += to_float(pr.v[k]);
+          po.v[k] = from_float<T>(out);
         }
         *reinterpret_cast<Pack<T, VEC>*>(dxr + c) = po;
       }
@@ -291,7 +296,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                          int64_t rows, int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
-                         float* __restrict__ rstd_out) {
+                         float* __restrict__ rstd_out, const T* __restrict__ res, T* __restrict__ sum_out) {
   constexpr int VEC = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   Pack<T, VEC> pg[MAXV], pb[MAXV];
@@ -312,6 +317,20 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
     for (int j = 0; j < MAXV; ++j) {
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) px[j] = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
+    }
+    if (res != nullptr) {
+      // Residual add fused in: the sum (rounded to the storage type, as a separate add would
+      // leave it) is written out and normalised.
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int c = (j * 32 + lane) * VEC;
+        if (c < cols) {
+          const Pack<T, VEC> pr = *reinterpret_cast<const Pack<T, VEC>*>(res + r * cols + c);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]));
+          *reinterpret_cast<Pack<T, VEC>*>(sum_out + r * cols + c) = px[j];
+        }
+      }
     }
     float s = 0.f, ss = 0.f;
 #pragma unroll
@@ -354,34 +373,39 @@ __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, i
 }
 
 template <typename T>
-void launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
-                          float* mean, float* rstd, int sms, cudaStream_t stream) {
+bool launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
+                          float* mean, float* rstd, const T* res, T* sum_out, int sms, cudaStream_t stream) {
   constexpr int kVec = 16 / sizeof(T);
   const int grid = max(1, min(ceil_div(rows, kLnWarps), sms * 6));
   const int packs = ceil_div(cols, 32 * kVec);
   switch (packs) {
-    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
-    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
-    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
-    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd); break;
+    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
+    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
+    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
+    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
     default:
+      if (res != nullptr) return false;   // the wide-row kernel has no fused add
       layernorm_fwd_kernel<T><<<max(1, min(ceil_div(rows, kLnWarps), sms * 2)), kLnWarps * 32, 0, stream>>>(
           x, gamma, beta, rows, cols, eps, y, mean, rstd);
   }
+  return true;
 }
 
 template <typename T>
-void launch_layernorm_bwd(const T* dy, const T* x, const T* gamma, const float* mean, const float* rstd, int64_t rows,
-                          int cols, T* dx, float* partial, int grid, size_t smem, cudaStream_t stream) {
+bool launch_layernorm_bwd(const T* dy, const T* x, const T* gamma, const float* mean, const float* rstd, int64_t rows,
+                          int cols, T* dx, float* partial, const T* dres, int grid, size_t smem, cudaStream_t stream) {
   constexpr int kVec = 16 / sizeof(T);
   const int packs = ceil_div(cols, 32 * kVec);
   switch (packs) {
-    case 1: layernorm_bwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
-    case 2: layernorm_bwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
-    case 3: layernorm_bwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
-    case 4: layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial); break;
-    default: layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial);
+    case 1: layernorm_bwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
+    case 2: layernorm_bwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
+    case 3: layernorm_bwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
+    case 4: layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
+    default:
+      if (dres != nullptr) return false;
+      layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial);
   }
+  return true;
 }
 
 }  // namespace
@@ -409,28 +433,38 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
 
 int layernorm_grid(int64_t rows, int sms) { return max(1, min(ceil_div(rows, kLnWarps), sms * 2)); }
 
+bool layernorm_fusable(DType type, int cols) {
+  const int vec = type == kF32 ? 4 : 8;
+  return cols % vec == 0 && cols <= 32 * 4 * vec;
+}
+
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, int sms, cudaStream_t stream) {
+                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, int sms,
+                          cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    launch_layernorm_fwd<T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), rows,
-                            cols, eps, static_cast<T*>(y), mean, rstd, sms, stream);
+    if (!launch_layernorm_fwd<T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),
+                                 rows, cols, eps, static_cast<T*>(y), mean, rstd, static_cast<const T*>(res),
+                                 static_cast<T*>(sum_out), sms, stream))
+      return cudaErrorInvalidValue;
   })
   return cudaGetLastError();
 }
 
 cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
-                          float* partial, int sms, cudaStream_t stream) {
+                          float* partial, const void* dres, int sms, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   const int grid = layernorm_grid(rows, sms);
   const size_t smem = size_t(2) * cols * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean,
-                            rstd, rows, cols, static_cast<T*>(dx), partial, grid, smem, stream);
+    if (!launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
+                                 mean, rstd, rows, cols, static_cast<T*>(dx), partial, static_cast<const T*>(dres),
+                                 grid, smem, stream))
+      return cudaErrorInvalidValue;
     layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
   })

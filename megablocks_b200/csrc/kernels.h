@@ -86,11 +86,15 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
                               const float* scale_ptr, float scale_mul, int64_t rows, int64_t vocab,
                               cudaStream_t stream);
 int layernorm_grid(int64_t rows, int sms);   // CTAs (= rows of `partial`) the backward uses
+// Optional fusions (rows short enough for the register kernels, see layernorm_fusable): forward
+// normalises x + res and writes the sum to sum_out; backward adds dres to dx.
+bool layernorm_fusable(DType type, int cols);
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, int sms, cudaStream_t stream);
+                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, int sms,
+                          cudaStream_t stream);
 cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
-                          float* partial, int sms, cudaStream_t stream);
+                          float* partial, const void* dres, int sms, cudaStream_t stream);
 
 // ---- ep_comm.cu ---------------------------------------------------------------
 // Geometry of one expert-parallel workspace.  `peer_base[r]` is the address at which

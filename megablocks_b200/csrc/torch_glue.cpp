@@ -739,33 +739,52 @@ void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const
   MB_LAUNCHED(1);
 }
 
+bool layernorm_can_fuse(const at::Tensor& x) {
+  return x.is_cuda() && x.dim() == 2 && layernorm_fusable(float_code(x.scalar_type()), int(x.size(1)));
+}
+
+// Returns {y, mean, rstd, s}: s = x + res (or x itself without res) is the tensor that was normalised.
 std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
-                                          double eps) {
+                                          double eps, const c10::optional<at::Tensor>& res) {
   MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CONTIG(gamma); MB_CHECK_CONTIG(beta);
   TORCH_CHECK(x.dim() == 2 && gamma.numel() == x.size(1) && beta.numel() == x.size(1) &&
                   gamma.scalar_type() == x.scalar_type() && beta.scalar_type() == x.scalar_type(),
               "layernorm expects x[rows, cols] and weight / bias of length cols in the dtype of x");
   c10::cuda::CUDAGuard guard(x.device());
   at::Tensor y = at::empty_like(x);
+  at::Tensor sum = x;
+  if (res.has_value()) {
+    TORCH_CHECK(res->is_cuda() && res->is_contiguous() && res->sizes() == x.sizes() &&
+                    res->scalar_type() == x.scalar_type() && layernorm_can_fuse(x),
+                "layernorm: the fused residual needs a tensor like x and rows the register kernel holds");
+    sum = at::empty_like(x);
+  }
   auto fopts = x.options().dtype(at::kFloat);
   at::Tensor mean = at::empty({x.size(0)}, fopts), rstd = at::empty({x.size(0)}, fopts);
   MB_CUDA_OK(layernorm_fwd(float_code(x.scalar_type()), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), x.size(0),
                            int(x.size(1)), float(eps), y.data_ptr(), mean.data_ptr<float>(),
-                           rstd.data_ptr<float>(), sm_count(), stream()));
+                           rstd.data_ptr<float>(), res.has_value() ? res->data_ptr() : nullptr,
+                           res.has_value() ? sum.data_ptr() : nullptr, sm_count(), stream()));
   MB_LAUNCHED(1);
-  return {y, mean, rstd};
+  return {y, mean, rstd, sum};
 }
 
 std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                           const at::Tensor& mean, const at::Tensor& rstd) {
+                                           const at::Tensor& mean, const at::Tensor& rstd,
+                                           const c10::optional<at::Tensor>& dres) {
   MB_CHECK_CUDA(dy); MB_CHECK_CONTIG(dy); MB_CHECK_CONTIG(x);
   c10::cuda::CUDAGuard guard(x.device());
+  if (dres.has_value())
+    TORCH_CHECK(dres->is_cuda() && dres->is_contiguous() && dres->sizes() == x.sizes() &&
+                    dres->scalar_type() == x.scalar_type() && layernorm_can_fuse(x),
+                "layernorm: the fused gradient add needs a tensor like x and rows the register kernel holds");
   at::Tensor dx = at::empty_like(x), dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
   const int grid = layernorm_grid(x.size(0), sm_count());
   at::Tensor partial = at::empty({grid, 2 * x.size(1)}, x.options().dtype(at::kFloat));
   MB_CUDA_OK(layernorm_bwd(float_code(x.scalar_type()), dy.data_ptr(), x.data_ptr(), gamma.data_ptr(),
                            mean.data_ptr<float>(), rstd.data_ptr<float>(), x.size(0), int(x.size(1)), dx.data_ptr(),
-                           dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(), sm_count(), stream()));
+                           dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(),
+                           dres.has_value() ? dres->data_ptr() : nullptr, sm_count(), stream()));
   MB_LAUNCHED(2);
   return {dx, dgamma, dbeta};
 }

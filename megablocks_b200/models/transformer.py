@@ -172,6 +172,15 @@ class Attention(nn.Module):
         return self.proj(out.transpose(1, 2).reshape(b, s, -1))
 
 
+def _add_norm(norm: nn.Module, x: torch.Tensor, delta):
+    """``(x + delta, norm(x + delta))``."""
+    if hasattr(norm, 'add_forward'):
+        return norm.add_forward(x, delta)
+    if delta is not None:
+        x = x + delta
+    return x, norm(x)
+
+
 class Block(nn.Module):
 
     def __init__(self, cfg: TransformerConfig, moe_args: Arguments):
@@ -183,11 +192,14 @@ class Block(nn.Module):
         self.ln2 = norm(cfg.hidden_size, **kw)
         self.moe = (dMoE if cfg.dropless else MoE)(moe_args)
 
-    def forward(self, x: torch.Tensor, rope) -> torch.Tensor:
-        x = x + self.attn(self.ln1(x), rope)
+    def forward(self, x: torch.Tensor, delta, rope):
+        """The residual stream arrives as ``x + delta`` (``delta`` may be ``None``) and leaves the same
+        way, so every residual add rides in the following norm's kernels."""
+        x, normed = _add_norm(self.ln1, x, delta)
+        x, normed = _add_norm(self.ln2, x, self.attn(normed, rope))
         # The MoE layer is token-wise: it flattens every leading dimension, so the
         # [batch, seq, hidden] activations go in as they are (no transpose copy).
-        return x + self.moe(self.ln2(x))
+        return x, self.moe(normed)
 
 
 class MoETransformer(nn.Module):
@@ -227,12 +239,13 @@ class MoETransformer(nn.Module):
         if self.wpe is not None:
             x = x + self.wpe(torch.arange(s, device=tokens.device))
         rope = self._rope_for(s, tokens.device)
+        delta = None
         for block in self.blocks:
             if self.cfg.activation_checkpointing and self.training:
-                x = checkpoint(block, x, rope, use_reentrant=False)
+                x, delta = checkpoint(block, x, delta, rope, use_reentrant=False)
             else:
-                x = block(x, rope)
-        return self.ln_f(x)
+                x, delta = block(x, delta, rope)
+        return _add_norm(self.ln_f, x, delta)[1]
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         weight = self.lm_head.weight if self.lm_head is not None else self.wte.weight

@@ -49,7 +49,7 @@ class _LayerNorm(torch.autograd.Function):
     def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).contiguous()
-        y, mean, rstd = ext().layernorm_forward(x2, weight, bias, eps)
+        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, bias, eps, None)
         ctx.save_for_backward(x2, weight, mean, rstd)
         ctx.shape = shape
         return y.view(shape)
@@ -57,8 +57,32 @@ class _LayerNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx: Any, dy: torch.Tensor):
         x2, weight, mean, rstd = ctx.saved_tensors
-        dx, dw, db = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd)
+        dx, dw, db = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd, None)
         return dx.view(ctx.shape), dw, db, None
+
+
+class _AddLayerNorm(torch.autograd.Function):
+    """``s = a + b; y = LayerNorm(s)`` in one pass; the backward adds ``ds`` while it writes ``dx``."""
+
+    @staticmethod
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
+        shape = a.shape
+        a2 = a.reshape(-1, shape[-1]).contiguous()
+        b2 = b.reshape(-1, shape[-1]).contiguous()
+        y, mean, rstd, s = ext().layernorm_forward(a2, weight, bias, eps, b2)
+        ctx.save_for_backward(s, weight, mean, rstd)
+        ctx.shape = shape
+        return s.view(shape), y.view(shape)
+
+    @staticmethod
+    def backward(ctx: Any, ds, dy):
+        s, weight, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return ds, ds, None, None, None
+        dres = ds.reshape(s.shape).contiguous() if ds is not None else None
+        dx, dw, db = ext().layernorm_backward(dy.reshape(s.shape).contiguous(), s, weight, mean, rstd, dres)
+        dx = dx.view(ctx.shape)
+        return dx, dx, dw, db, None
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -70,8 +94,26 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: f
     return F.layer_norm(x, (cols,), weight, bias, eps)
 
 
+def add_layer_norm(a: torch.Tensor, b, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
+    """``(a + b, LayerNorm(a + b))``; ``b`` may be ``None``.  On CUDA the add rides in the norm's kernels."""
+    if b is None:
+        return a, layer_norm(a, weight, bias, eps)
+    cols = a.shape[-1]
+    fused = (a.is_cuda and b.is_cuda and a.dtype == b.dtype == weight.dtype and bias is not None
+             and a.shape == b.shape and a.dtype in (torch.bfloat16, torch.float16, torch.float32)
+             and ext().layernorm_can_fuse(a.reshape(-1, cols)))
+    if fused:
+        return _AddLayerNorm.apply(a, b, weight, bias, eps)
+    s = a + b
+    return s, layer_norm(s, weight, bias, eps)
+
+
 class LayerNorm(torch.nn.LayerNorm):
     """``nn.LayerNorm`` (same parameters and state dict) running the fused kernels on CUDA."""
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return layer_norm(x, self.weight, self.bias, self.eps)
+
+    def add_forward(self, a: torch.Tensor, b):
+        """``(a + b, self(a + b))`` with the add fused into the kernels; ``b`` may be ``None``."""
+        return add_layer_norm(a, b, self.weight, self.bias, self.eps)

@@ -47,3 +47,37 @@ def test_layer_norm(device, rows, cols, dtype):
     wtol = dict(rtol=3e-2, atol=3e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
     torch.testing.assert_close(ln.weight.grad.float().cpu(), wr.grad, **wtol)
     torch.testing.assert_close(ln.bias.grad.float().cpu(), br.grad, **wtol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,cols', [(1000, 768), (77, 1024), (64, 4096)])   # last: too wide to fuse, falls back
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_add_layer_norm(device, rows, cols, dtype):
+    """``(a + b, LN(a + b))`` with both results used downstream, against the unfused fp32 chain."""
+    ln = fused.LayerNorm(cols).to(device=device, dtype=dtype)
+    with torch.no_grad():
+        ln.weight.copy_(torch.randn(cols) * 0.5 + 1)
+        ln.bias.copy_(torch.randn(cols) * 0.5)
+    a = torch.randn(rows, cols).to(dtype).to(device).requires_grad_(True)
+    b = (torch.randn(rows, cols) * 0.5).to(dtype).to(device).requires_grad_(True)
+    p1 = torch.randn(rows, cols).to(dtype).to(device)
+    p2 = torch.randn(rows, cols).to(dtype).to(device)
+    s, y = ln.add_forward(a, b)
+    ((y.float() * p1.float()).sum() + (s.float() * p2.float()).sum()).backward()
+    ar = a.detach().float().cpu().requires_grad_(True)
+    br = b.detach().float().cpu().requires_grad_(True)
+    sr = (ar + br).to(dtype).float() if dtype == torch.bfloat16 else ar + br
+    # Straight-through for the rounding of the sum, as autograd sees the 16-bit add.
+    sr = (ar + br) + (sr - (ar + br)).detach()
+    yr = F.layer_norm(sr, (cols,), ln.weight.detach().float().cpu(), ln.bias.detach().float().cpu(), ln.eps)
+    ((yr * p1.float().cpu()).sum() + (sr * p2.float().cpu()).sum()).backward()
+    tol = dict(rtol=2e-2, atol=4e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(s.detach().float().cpu(), sr.detach(), **tol)
+    torch.testing.assert_close(y.detach().float().cpu(), yr.detach(), **tol)
+    torch.testing.assert_close(a.grad.float().cpu(), ar.grad, **tol)
+    torch.testing.assert_close(b.grad.float().cpu(), br.grad, **tol)
+    # Only the normalised output used: the residual gradient is absent.
+    a.grad = b.grad = None
+    s2, y2 = ln.add_forward(a, b)
+    (y2.float() * p1.float()).sum().backward()
+    assert a.grad is not None and torch.equal(a.grad, b.grad)
