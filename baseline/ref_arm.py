@@ -76,7 +76,7 @@ class RefBlock(nn.Module):
 
 class RefGPT(nn.Module):
 
-    def __init__(self, cfg, device, ep_group=None):
+    def __init__(self, cfg, device, ep_group=None, memory_optimized_mlp=False):
         super().__init__()
         Arguments, dmoe_mod, self.moe_mod = import_reference()
         dtype = torch.bfloat16
@@ -85,7 +85,7 @@ class RefGPT(nn.Module):
             return_bias=False, activation_fn=partial(F.gelu, approximate='tanh'),
             moe_num_experts=cfg['experts'], moe_top_k=cfg['top_k'], moe_loss_weight=0.1, moe_lbl_in_fp32=True,
             moe_expert_model_parallelism=ep_group is not None, expert_parallel_group=ep_group,
-            memory_optimized_mlp=True, mlp_type='mlp', mlp_impl='grouped', fp16=False, bf16=True, device=device,
+            memory_optimized_mlp=memory_optimized_mlp, mlp_type='mlp', mlp_impl='grouped', fp16=False, bf16=True, device=device,
             init_method=partial(nn.init.normal_, mean=0.0, std=0.02),
             output_layer_init_method=partial(nn.init.normal_, mean=0.0, std=0.02 / math.sqrt(2.0 * cfg['layers'])))
         self.wte = nn.Embedding(cfg['vocab'], cfg['hidden'], device=device, dtype=dtype)

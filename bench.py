@@ -204,14 +204,14 @@ def run_ours(args):
     group = dist.group.WORLD if world > 1 else None
     fused = {'auto': None, 'fused': True, 'nccl': False}[args.ep_comm]
     cfg = preset('dmoe-125m', device=torch.device('cuda', local), expert_parallel_group=group,
-                 mlp_impl=args.mlp_impl, memory_optimized_mlp=True, ep_fused_comm=fused)
+                 mlp_impl=args.mlp_impl, memory_optimized_mlp=args.memory_optimized_mlp, ep_fused_comm=fused)
     model = MoETransformer(cfg)
     trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000), dp_group=group)
     out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count)
     status.check()
     if rank == 0:
         _emit('megablocks_b200', args.gpus, args.steps, args.warmup, *out,
-              extra_config={'mlp_impl': args.mlp_impl,
+              extra_config={'mlp_impl': args.mlp_impl, 'memory_optimized_mlp': args.memory_optimized_mlp,
                             'ep_comm': ('none' if world == 1 else
                                         'fused peer-memory kernels (remote stores + flags, no NCCL all-to-all)'
                                         if model.blocks[0].moe.experts._ep_workspace is not None else
@@ -235,12 +235,14 @@ def run_reference(args):
     rank, world, local = _dist_setup(args.gpus)
     torch.manual_seed(1234)
     group = dist.group.WORLD if world > 1 else None
-    model = ref_arm.RefGPT(MODEL, torch.device('cuda', local), ep_group=group)
+    model = ref_arm.RefGPT(MODEL, torch.device('cuda', local), ep_group=group,
+                           memory_optimized_mlp=args.memory_optimized_mlp)
     trainer = ref_arm.RefTrainer(model, world=world, group=group)
     out = _measure(trainer, world, rank, local, args.steps, args.warmup, lambda: 0)
     if rank == 0:
         _emit('reference', args.gpus, args.steps, args.warmup, *out,
-              extra_config={'mlp_impl': 'grouped', 'ep_comm': 'nccl all_to_all' if world > 1 else 'none',
+              extra_config={'mlp_impl': 'grouped', 'memory_optimized_mlp': args.memory_optimized_mlp,
+                            'ep_comm': 'nccl all_to_all' if world > 1 else 'none',
                             'note': 'unmodified reference library from baseline/_ref; grouped_gemm and stk '
                                     'are import shims (per-expert cuBLAS loop), backbone/optimizer plain PyTorch'})
     if world > 1:
@@ -256,6 +258,9 @@ def main():
     ap.add_argument('--mlp-impl', dest='mlp_impl', choices=['grouped', 'sparse'], default='grouped')
     ap.add_argument('--ep-comm', dest='ep_comm', choices=['auto', 'fused', 'nccl'], default='auto',
                     help='expert-parallel exchange: peer-memory kernels (auto/fused) or NCCL all-to-all')
+    ap.add_argument('--memory-optimized-mlp', dest='memory_optimized_mlp', action='store_true',
+                    help='recompute the expert activation in backward (both arms); off, as in the '
+                         "reference's Arguments default and its experiment scripts")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

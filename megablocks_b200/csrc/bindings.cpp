@@ -84,6 +84,7 @@ std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tenso
                                            const at::Tensor& mean, const at::Tensor& rstd,
                                            const c10::optional<at::Tensor>& dres);
 bool layernorm_can_fuse(const at::Tensor& x);
+at::Tensor column_sum_op(const at::Tensor& x);
 
 // torch_glue.cpp: optimizer
 int64_t adam_record_size();
@@ -124,6 +125,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_forward", &mb::layernorm_forward);
   m.def("layernorm_backward", &mb::layernorm_backward);
   m.def("layernorm_can_fuse", &mb::layernorm_can_fuse);
+  m.def("column_sum", &mb::column_sum_op, "Sum over rows of x[rows, cols] (bias gradient)");
   m.def("symm_alloc", &mb::symm_alloc);
   m.def("symm_open", &mb::symm_open);
   m.def("symm_close", &mb::symm_close);

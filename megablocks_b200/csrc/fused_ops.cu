@@ -372,6 +372,68 @@ __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, i
   if (c < cols) dgamma[c] = from_float<T>(s); else dbeta[c - cols] = from_float<T>(s);
 }
 
+// ---------------------------------------------------------------------------
+// Column sums of a [rows, cols] matrix (bias gradients): every CTA owns a strip of 32 * VEC
+// columns and a slice of rows; a warp reads 32 consecutive 16-byte groups of one row, eight
+// row lanes accumulate in registers, partial sums meet in `partial[slices][cols]`, and a
+// second kernel adds the slices (deterministic, no atomics).
+// ---------------------------------------------------------------------------
+constexpr int kColsumRowLanes = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kColsumRowLanes)
+colsum_partial_kernel(const T* __restrict__ x, int64_t rows, int cols, float* __restrict__ partial) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float red[kColsumRowLanes][32 * VEC + 1];
+  const int group = threadIdx.x & 31, row_lane = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + group) * VEC;
+  const int64_t per = (rows + gridDim.y - 1) / gridDim.y;
+  const int64_t r0 = int64_t(blockIdx.y) * per, r1 = min(rows, r0 + per);
+  float acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+  if (c < cols) {
+    int64_t r = r0 + row_lane;
+    // Four rows in flight per thread.
+    for (; r + 3 * kColsumRowLanes < r1; r += 4 * kColsumRowLanes) {
+      Pack<T, VEC> p[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        p[u] = *reinterpret_cast<const Pack<T, VEC>*>(x + (r + u * kColsumRowLanes) * cols + c);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] += to_float(p[u].v[k]);
+    }
+    for (; r < r1; r += kColsumRowLanes) {
+      const Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(x + r * cols + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] += to_float(p.v[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) red[row_lane][group * VEC + k] = acc[k];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * VEC; i += blockDim.x) {
+    const int col = blockIdx.x * 32 * VEC + i;
+    if (col < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int l = 0; l < kColsumRowLanes; ++l) s += red[l][i];
+      partial[int64_t(blockIdx.y) * cols + col] = s;
+    }
+  }
+}
+
+template <typename T>
+__global__ void colsum_reduce_kernel(const float* __restrict__ partial, int slices, int cols, T* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < slices; ++p) s += partial[int64_t(p) * cols + c];
+  out[c] = from_float<T>(s);
+}
+
 template <typename T>
 bool launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
                           float* mean, float* rstd, const T* res, T* sum_out, int sms, cudaStream_t stream) {
@@ -467,6 +529,28 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
       return cudaErrorInvalidValue;
     layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
+  })
+  return cudaGetLastError();
+}
+
+int colsum_slices(int64_t rows, int cols, int elem_size, int sms) {
+  const int strips = ceil_div(cols, 32 * (16 / elem_size));
+  int64_t want = (int64_t(sms) * 4) / strips;
+  const int64_t cap = (rows + 63) / 64;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  return int(want);
+}
+
+cudaError_t column_sum(DType type, const void* x, int64_t rows, int cols, void* out, float* partial, int slices,
+                       cudaStream_t stream) {
+  if (cols == 0) return cudaSuccess;
+  MB_SWITCH_FLOAT(type, T, {
+    constexpr int kVec = 16 / sizeof(T);
+    if (cols % kVec != 0) return cudaErrorInvalidValue;
+    const dim3 grid(ceil_div(cols, 32 * kVec), slices);
+    colsum_partial_kernel<T><<<grid, 32 * kColsumRowLanes, 0, stream>>>(static_cast<const T*>(x), rows, cols, partial);
+    colsum_reduce_kernel<T><<<ceil_div(cols, 256), 256, 0, stream>>>(partial, slices, cols, static_cast<T*>(out));
   })
   return cudaGetLastError();
 }

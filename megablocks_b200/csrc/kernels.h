@@ -96,6 +96,12 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
                           float* partial, const void* dres, int sms, cudaStream_t stream);
 
+// Column sums of x[rows, cols] (cols a multiple of 16 bytes): `partial` holds slices x cols floats,
+// slices = colsum_slices(...).
+int colsum_slices(int64_t rows, int cols, int elem_size, int sms);
+cudaError_t column_sum(DType type, const void* x, int64_t rows, int cols, void* out, float* partial, int slices,
+                       cudaStream_t stream);
+
 // ---- ep_comm.cu ---------------------------------------------------------------
 // Geometry of one expert-parallel workspace.  `peer_base[r]` is the address at which
 // rank r's symmetric heap is mapped in this process (device array of `world` entries);

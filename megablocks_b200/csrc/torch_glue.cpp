@@ -596,12 +596,13 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
 
   const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
   // CTA pairs (256-row tiles, six 32 KB stages per CTA) hide more load latency but waste up to
-  // 255 rows per group; measured, they win once groups are a few thousand rows long.
+  // 255 rows per group; measured, they win once groups are a few thousand rows long and the
+  // contraction is deep enough for the mainloop, not the epilogue, to set the pace.
   // pair_mode: -1 = decide here, 0 = never, 1 = whenever the kernel supports the problem.
   const int64_t rows_expected = rows_hint > 0 ? rows_hint : a.size(0);
   bool pair = layout != kTN && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
   if (pair_mode == 0) pair = false;
-  else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048;
+  else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048 && p.K >= 2048;
   if (!scatter.has_value() && store_tma_enabled()) {
     // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
     const int64_t out_rows = out_numel / p.N;
@@ -787,6 +788,22 @@ std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tenso
                            dres.has_value() ? dres->data_ptr() : nullptr, sm_count(), stream()));
   MB_LAUNCHED(2);
   return {dx, dgamma, dbeta};
+}
+
+// Sum over the rows of x[rows, cols]: the bias gradient of a linear layer.
+at::Tensor column_sum_op(const at::Tensor& x) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  TORCH_CHECK(x.dim() == 2 && (x.size(1) * x.element_size()) % 16 == 0,
+              "column_sum expects x[rows, cols] with rows of a multiple of 16 bytes");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({x.size(1)}, x.options());
+  const int slices = colsum_slices(x.size(0), int(x.size(1)), int(x.element_size()), sm_count());
+  at::Tensor partial = at::empty({slices, x.size(1)}, x.options().dtype(at::kFloat));
+  if (x.size(0) == 0) return out.zero_();
+  MB_CUDA_OK(column_sum(float_code(x.scalar_type()), x.data_ptr(), x.size(0), int(x.size(1)), out.data_ptr(),
+                        partial.data_ptr<float>(), slices, stream()));
+  MB_LAUNCHED(2);
+  return out;
 }
 
 // ---------------------------------------------------------------------------

@@ -149,8 +149,8 @@ class Attention(nn.Module):
         kw = dict(device=cfg.device, dtype=cfg.dtype)
         bias = cfg.flavour == 'gpt2'
         qkv_out = (cfg.num_heads + 2 * cfg.kv_heads) * self.head_dim
-        self.qkv = nn.Linear(cfg.hidden_size, qkv_out, bias=bias, **kw)
-        self.proj = nn.Linear(cfg.hidden_size, cfg.hidden_size, bias=bias, **kw)
+        self.qkv = fused.Linear(cfg.hidden_size, qkv_out, bias=bias, **kw)
+        self.proj = fused.Linear(cfg.hidden_size, cfg.hidden_size, bias=bias, **kw)
         nn.init.normal_(self.qkv.weight, std=cfg.init_std)
         nn.init.normal_(self.proj.weight, std=cfg.init_std / math.sqrt(2.0 * cfg.num_layers))
         if bias:

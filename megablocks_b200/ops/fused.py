@@ -9,7 +9,10 @@
 * :func:`layer_norm` - LayerNorm whose backward reduces the weight and bias
   gradients through shared memory in the same pass that produces ``dx``.
 
-Both fall back to the PyTorch ops on CPU tensors.
+* :func:`linear` / :class:`Linear` - ``nn.Linear`` whose bias gradient is one column-sum kernel
+  at memory bandwidth (the library route reduces the same tensor at a third of that).
+
+All fall back to the PyTorch ops on CPU tensors.
 """
 
 from typing import Any
@@ -117,3 +120,44 @@ class LayerNorm(torch.nn.LayerNorm):
     def add_forward(self, a: torch.Tensor, b):
         """``(a + b, self(a + b))`` with the add fused into the kernels; ``b`` may be ``None``."""
         return add_layer_norm(a, b, self.weight, self.bias, self.eps)
+
+
+class _Linear(torch.autograd.Function):
+    """``x @ w.T + b`` with library GEMMs; the bias gradient is the fused column sum."""
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor):
+        ctx.save_for_backward(x, weight)
+        return F.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (dy2 @ weight).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = dy2.t() @ x.reshape(-1, x.shape[-1])
+        if ctx.needs_input_grad[2]:
+            db = ext().column_sum(dy2)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias=None) -> torch.Tensor:
+    """``F.linear`` with the bias gradient computed by one bandwidth-bound kernel on CUDA."""
+    fused = (bias is not None and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+             and weight.dtype == x.dtype and bias.dtype == x.dtype and (weight.shape[0] * x.element_size()) % 16 == 0
+             and not torch.is_autocast_enabled())
+    if fused:
+        return _Linear.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+class Linear(torch.nn.Linear):
+    """``nn.Linear`` (same parameters and state dict) routed through :func:`linear`."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return linear(x, self.weight, self.bias)

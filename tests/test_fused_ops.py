@@ -81,3 +81,26 @@ def test_add_layer_norm(device, rows, cols, dtype):
     s2, y2 = ln.add_forward(a, b)
     (y2.float() * p1.float()).sum().backward()
     assert a.grad is not None and torch.equal(a.grad, b.grad)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,cin,cout', [(1000, 64, 768), (4099, 128, 2304), (7, 32, 8)])
+def test_linear_bias_gradient(device, rows, cin, cout):
+    """``fused.Linear`` against ``nn.Linear`` in fp32: outputs and all three gradients."""
+    dtype = torch.bfloat16 if device == 'cuda' else torch.float32
+    lin = fused.Linear(cin, cout).to(device=device, dtype=dtype)
+    x = torch.randn(rows, cin).to(dtype).to(device).requires_grad_(True)
+    probe = torch.randn(rows, cout).to(dtype).to(device)
+    y = lin(x)
+    (y.float() * probe.float()).sum().backward()
+    xr = x.detach().float().cpu().requires_grad_(True)
+    wr = lin.weight.detach().float().cpu().requires_grad_(True)
+    br = lin.bias.detach().float().cpu().requires_grad_(True)
+    (F.linear(xr, wr, br) * probe.float().cpu()).sum().backward()
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(y.detach().float().cpu(), F.linear(xr, wr, br).detach(), **tol)
+    torch.testing.assert_close(x.grad.float().cpu(), xr.grad, **tol)
+    scale = dict(rtol=2e-2, atol=2e-2 * float(br.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(lin.bias.grad.float().cpu(), br.grad, **scale)
+    wscale = dict(rtol=2e-2, atol=2e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(lin.weight.grad.float().cpu(), wr.grad, **wscale)
