@@ -210,7 +210,7 @@ class _FusedExpertParallel(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, x, expert_weights, w1, w2, v1, ws: EpWorkspace, indices, bin_ids, bins, tpe, top_k: int,
-                act: int, keep_h: bool):
+                act: int, keep_h: bool, wgrad_scale: float = 1.0):
         seq = ws.next_seq()
         ws.begin_use(seq)
         x = x.contiguous()
@@ -239,6 +239,7 @@ class _FusedExpertParallel(torch.autograd.Function):
             tensors.append(h)
         ctx.save_for_backward(*tensors)
         ctx.ws, ctx.seq, ctx.top_k, ctx.act, ctx.tokens = ws, seq, top_k, act, tokens
+        ctx.wgrad_scale = wgrad_scale
         ctx.mark_non_differentiable()
         return out
 
@@ -263,7 +264,8 @@ class _FusedExpertParallel(torch.autograd.Function):
         dxr, dw1, dw2, dv1 = mlp_backward(ws.recv_dy, ws.recv_x, w1, w2, v1, recv_bins, ctx.act, (z1, z2, h),
                                           (True,) + needs[1:], wait=ws.arrival(1, seq), zero_tail=False,
                                           rows_hint=ws.copies,
-                                          scatter=ws.scatter_args(counts, 1, seq, done_ret) if fuse else None)
+                                          scatter=ws.scatter_args(counts, 1, seq, done_ret) if fuse else None,
+                                          wgrad_scale=ctx.wgrad_scale)
         # Every read of both receive buffers is enqueued above; only now may peers learn
         # (through the return flags / the free flag) that they can be overwritten.
         if not fuse:
@@ -273,7 +275,7 @@ class _FusedExpertParallel(torch.autograd.Function):
         dx = None
         if needs[0]:
             dx = ext().scatter_rows(ws.ret_dx, indices, bin_ids, None, bins, bins, top_k, ctx.tokens)
-        return dx, dweights, dw1, dw2, dv1, None, None, None, None, None, None, None, None
+        return dx, dweights, dw1, dw2, dv1, None, None, None, None, None, None, None, None, None
 
 
 def fused_expert_parallel(x, expert_weights, w1, w2, v1, workspace: EpWorkspace, indices, bin_ids, bins, tpe,
