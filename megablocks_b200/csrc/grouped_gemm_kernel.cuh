@@ -370,7 +370,7 @@ __device__ __forceinline__ void dact_values(float acc, float z, float& dz, float
 
 // One pass over the chunk for the activation-backward epilogue: dz goes to the staging buffer as
 // it is produced, h waits packed in registers until the buffer is free again.
-template <typename T, int ACT>
+template <typename T, int ACT, bool WANT_H>
 __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], const PackedRow& a1, Staging& stage,
                                                    T* out, T* out2, int64_t row_stride, int rows_ok, int cols,
                                                    int lane, int col, const CUtensorMap* maps, TmaOut tma) {
@@ -395,8 +395,10 @@ __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], co
     }
     uint4 w;
     w.x = pack2<T>(dz[0], dz[1]); w.y = pack2<T>(dz[2], dz[3]); w.z = pack2<T>(dz[4], dz[5]); w.w = pack2<T>(dz[6], dz[7]);
-    hw[v].x = pack2<T>(h[0], h[1]); hw[v].y = pack2<T>(h[2], h[3]);
-    hw[v].z = pack2<T>(h[4], h[5]); hw[v].w = pack2<T>(h[6], h[7]);
+    if constexpr (WANT_H) {
+      hw[v].x = pack2<T>(h[0], h[1]); hw[v].y = pack2<T>(h[2], h[3]);
+      hw[v].z = pack2<T>(h[4], h[5]); hw[v].w = pack2<T>(h[6], h[7]);
+    }
     *reinterpret_cast<uint4*>(stage.buf + stage_offset(lane, v)) = w;
   }
   if (tma.on) {
@@ -412,7 +414,7 @@ __device__ __forceinline__ void epilogue_emit_dact(const uint32_t (&raw)[32], co
     stage_store<T>(stage.buf, out, row_stride, rows_ok, cols, lane);
     __syncwarp();
   }
-  if (out2 == nullptr) return;
+  if constexpr (!WANT_H) return;
   if (maps != nullptr) stage_acquire(stage, lane);
 #pragma unroll
   for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(stage.buf + stage_offset(lane, v)) = hw[v];
@@ -493,9 +495,15 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&raw)[32], const 
                                                TmaOut tma) {
   const CUtensorMap* maps = p.store_tma ? p.out_map : nullptr;
   if constexpr (EPI == kEpiDAct) {
-    epilogue_emit_dact<T, ACT>(raw, a1, stage, static_cast<T*>(p.c) + base_off,
-                               p.out2 ? static_cast<T*>(p.out2) + base_off : nullptr, row_stride, rows_ok, cols,
-                               lane, col, maps, tma);
+    // Without the second output (the activation was kept by the forward pass) its arithmetic
+    // is compiled out.
+    if (p.out2)
+      epilogue_emit_dact<T, ACT, true>(raw, a1, stage, static_cast<T*>(p.c) + base_off,
+                                       static_cast<T*>(p.out2) + base_off, row_stride, rows_ok, cols, lane, col,
+                                       maps, tma);
+    else
+      epilogue_emit_dact<T, ACT, false>(raw, a1, stage, static_cast<T*>(p.c) + base_off, nullptr, row_stride,
+                                        rows_ok, cols, lane, col, maps, tma);
     return;
   }
   epilogue_emit<T, EPI, ACT, 0>(raw, a1, a2, stage, static_cast<T*>(p.c) + base_off, row_stride, rows_ok, cols,
