@@ -142,6 +142,7 @@ def _measure(trainer, world, rank, local, steps, warmup, launch_counter):
     for i in range(steps):
         b = dev_batches[i % len(dev_batches)]
         trainer.step(b[:, :-1], b[:, 1:])
+    _flush(trainer)   # deferred optimizer work of the last step belongs to the timed region
     end.record()
     barrier()
     launches = launch_counter() - launches0
@@ -155,12 +156,19 @@ def _measure(trainer, world, rank, local, steps, warmup, launch_counter):
     last = None
     for i in range(steps):
         last = trainer.step_from_host(host_batches[i % len(host_batches)])
+    _flush(trainer)
     end2.record()
     barrier()
     clocks = sampler.stop()
     e2e_ms = max_over_ranks(start2.elapsed_time(end2) / steps)
     h2d = host_batches[0].numel() * host_batches[0].element_size()
     return device_ms, e2e_ms, clocks, launches, h2d, 4, last
+
+
+def _flush(trainer):
+    flush = getattr(trainer, 'flush', None)
+    if flush is not None:
+        flush()
 
 
 def _emit(impl, n_gpus, steps, warmup, device_ms, e2e_ms, clocks, launches, h2d, d2h, loss, extra_config=None):

@@ -805,12 +805,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint8_t* a_tile = smem_a + stage * kABytes;
         uint8_t* b_tile = smem_b + stage * Cfg::kBBytes;
         if constexpr (LAYOUT == kTN) {
-          // Rows of the last K block that belong to the next group (or lie past the
-          // tensor) must not contribute: zero them in both operands.
+          // Rows of the last K block that belong to the next group (or lie past the tensor)
+          // must not contribute.  Zero rows in ONE operand cancel finite rows of the other, and
+          // the rows after any group but the last are the next group's data, so only the A side
+          // is cleared there; after the last group the rows may never have been written, and
+          // both sides are cleared.
           const int valid = tile.k_len - kb * kBlockK;
           if (valid < kBlockK) {
             const int tail_chunks = (kBlockK - valid) * 8;   // 16-byte chunks per box
-            for (int box = 0; box < kBlockM / 64 + BLOCK_N / 64; ++box) {
+            const int boxes = tile.group == G - 1 ? kBlockM / 64 + BLOCK_N / 64 : kBlockM / 64;
+            for (int box = 0; box < boxes; ++box) {
               uint8_t* base = (box < kBlockM / 64) ? a_tile + box * kBoxBytes
                                                    : b_tile + (box - kBlockM / 64) * kBoxBytes;
               uint4* rows = reinterpret_cast<uint4*>(base + valid * 128);

@@ -72,7 +72,9 @@ class FusedAdam:
         assert ext().adam_record_size() == _RECORD.itemsize
         rec = np.zeros(len(self.params), dtype=_RECORD)
         blocks = []
+        self._block_start = []          # first job of every tensor (plus the total at the end)
         for i, (p, off) in enumerate(zip(self.params, self.offsets)):
+            self._block_start.append(len(blocks))
             rec[i]['param'] = p.data_ptr()
             rec[i]['master'] = self.master.data_ptr() + 4 * off
             rec[i]['exp_avg'] = self.exp_avg.data_ptr() + 4 * off
@@ -81,6 +83,7 @@ class FusedAdam:
             rec[i]['norm_weight'] = self.norm_weights[i]
             for c in range((p.numel() + _CHUNK - 1) // _CHUNK):
                 blocks.append((i, c))
+        self._block_start.append(len(blocks))
         self._records = rec
         self._blocks = torch.tensor(blocks, dtype=torch.int32).reshape(-1, 2).to(self.device)
         self._host_ring = [torch.empty(rec.nbytes, dtype=torch.uint8).pin_memory() for _ in range(4)]
@@ -125,19 +128,39 @@ class FusedAdam:
         if not self.params:
             return
         grads = self.grads() if grads is None else grads
+        self.begin_step(grads)
+        self.step_range(0, len(self.params), grad_scale, grads)
+
+    def begin_step(self, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        """Advance the step counter (bias corrections) and publish the gradient addresses.
+
+        Followed by :meth:`step_range` calls that together cover every tensor once; the ranges
+        may be launched on another stream (the table upload happens here, on the current one).
+        """
+        if not self.params:
+            return
         self.step_count += 1
+        if self.device.type == 'cuda':
+            if not getattr(self, '_table_fresh', False):
+                self._upload_table(self.grads() if grads is None else grads)
+            self._table_fresh = False
+
+    def step_range(self, lo: int, hi: int, grad_scale: Optional[torch.Tensor] = None,
+                   grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        """Update tensors ``lo .. hi-1`` (after :meth:`begin_step`)."""
+        if not self.params or hi <= lo:
+            return
+        grads = self.grads() if grads is None else grads
         b1, b2 = self.betas
         bias1 = 1.0 - b1**self.step_count
         bias2 = 1.0 - b2**self.step_count
         if self.device.type == 'cuda':
-            if not getattr(self, '_table_fresh', False):
-                self._upload_table(grads)
-            self._table_fresh = False
-            ext().adam_step(self._table, self._blocks, _CHUNK, _CODES[self.dtype], _CODES[grads[0].dtype], self.lr, b1,
+            blocks = self._blocks[self._block_start[lo]:self._block_start[hi]]
+            ext().adam_step(self._table, blocks, _CHUNK, _CODES[self.dtype], _CODES[grads[0].dtype], self.lr, b1,
                             b2, self.eps, self.weight_decay, bias1, bias2, grad_scale)
             return
         scale = float(grad_scale[0]) if grad_scale is not None else 1.0
-        for p, g, off in zip(self.params, grads, self.offsets):
+        for p, g, off in list(zip(self.params, grads, self.offsets))[lo:hi]:
             n = p.numel()
             w, m, v = (t[off:off + n] for t in (self.master, self.exp_avg, self.exp_avg_sq))
             gf = g.detach().reshape(-1).float() * scale
