@@ -66,8 +66,8 @@ class Trainer:
         self._update_stream = None
         self._update_groups = []     # (module, first tensor, one past the last tensor) in forward order
         self._pending_updates = {}   # module -> event recorded after its expert weights were updated
-        if cfg.overlap_expert_update and self.device.type == 'cuda' and self.expert_params:
-            self._plan_expert_update_groups()
+        if self.expert_params:
+            self._plan_expert_update_groups(cfg.overlap_expert_update and self.device.type == 'cuda')
         self.flat = self.reducer = None
         kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
         if self.world > 1:
@@ -92,8 +92,9 @@ class Trainer:
         self._h2d = None
 
     # -- deferred expert update ------------------------------------------------------
-    def _plan_expert_update_groups(self) -> None:
-        """Order the expert weights by the MoE layer that owns them and hook those layers."""
+    def _plan_expert_update_groups(self, deferred: bool) -> None:
+        """Order the expert weights by the MoE layer that owns them; with ``deferred`` also hook those
+        layers so each waits for its own side-stream update."""
         from megablocks_b200.layers.moe import MoE
         is_expert = {id(p) for p in self.expert_params}
         ordered, groups, seen = [], [], set()
@@ -111,9 +112,10 @@ class Trainer:
             ordered = rest + ordered
         self.expert_params = ordered
         self._update_groups = groups
-        self._update_stream = torch.cuda.Stream(device=self.device)
-        for module, _, _ in groups:
-            module.register_forward_pre_hook(self._wait_for_update)
+        if deferred:
+            self._update_stream = torch.cuda.Stream(device=self.device)
+            for module, _, _ in groups:
+                module.register_forward_pre_hook(self._wait_for_update)
 
     def _wait_for_update(self, module, _inputs):
         event = self._pending_updates.pop(module, None)

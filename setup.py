@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 # MB200_GEMM_TIMING=1: diagnostic build whose grouped GEMM records per-role wait cycles
 # (read back with `_C.gemm_role_timers`).
 DEFINES = ['-DMB_GEMM_TIMING'] if os.environ.get('MB200_GEMM_TIMING') == '1' else []
-if os.environ.get('MB200_GEMM_NO_STORE') == '1':
+if os.environ.get('MB200_GEMM_NO_STORE') == '1':   # diagnostic: epilogue without its global stores
     DEFINES.append('-DMB_GEMM_NO_STORE')
 NVCC_FLAGS += DEFINES
 
