@@ -29,11 +29,10 @@ def _run(overlap: bool, steps: int = 4):
 def test_deferred_expert_update_matches_inline_update():
     losses_a, params_a, m_a = _run(overlap=False)
     losses_b, params_b, m_b = _run(overlap=True)
-    # Not bitwise: some gradients are accumulated with atomics, and a last-bit difference can flip a
-    # top-1 routing decision; the two runs must still follow the same trajectory.
-    torch.testing.assert_close(torch.tensor(losses_a), torch.tensor(losses_b), rtol=2e-2, atol=2e-2)
-    assert abs(m_a - m_b) <= 5e-2 * max(1.0, abs(m_a))
+    # Both modes order the expert parameters the same way, so the only difference left is the
+    # order of a few shared-memory atomics (LayerNorm weight gradients): last-bit noise.
+    torch.testing.assert_close(torch.tensor(losses_a), torch.tensor(losses_b), rtol=1e-4, atol=1e-4)
+    assert abs(m_a - m_b) <= 1e-3 * max(1.0, abs(m_a))
     for name in params_a:
-        diff = (params_a[name] - params_b[name]).norm()
-        assert diff <= 5e-2 * max(1.0, float(params_a[name].norm())), name
+        torch.testing.assert_close(params_a[name], params_b[name], rtol=0, atol=2e-3, msg=name)
     assert losses_a[-1] < losses_a[0] + 1.0   # the run trained (no NaN, no blow-up)
