@@ -233,6 +233,22 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
         pd[j] = *reinterpret_cast<const Pack<T, VEC>*>(dr + c);
       }
     }
+    // Ask for the next row of this warp (and this row's residual gradient) now: a warp holds one
+    // row at a time, so without this every row would pay the full memory latency.
+    {
+      const int64_t rn = r + stride;
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int c = (j * 32 + lane) * VEC;
+        if (c < cols) {
+          if (dres != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(dres + r * cols + c));
+          if (rn < rows) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(x + rn * cols + c));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(dy + rn * cols + c));
+          }
+        }
+      }
+    }
     const float mu = mean[r], rs = rstd[r];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -318,6 +334,19 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) px[j] = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
     }
+    {
+      const int64_t rn = r + stride;   // next row of this warp: have it in L1 when its turn comes
+      if (rn < rows) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = (j * 32 + lane) * VEC;
+          if (c < cols) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(x + rn * cols + c));
+            if (res != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(res + rn * cols + c));
+          }
+        }
+      }
+    }
     if (res != nullptr) {
       // Residual add fused in: the sum (rounded to the storage type, as a separate add would
       // leave it) is written out and normalised.
@@ -361,15 +390,24 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
   }
 }
 
-// dgamma / dbeta = column sums of the per-CTA partials.
+// dgamma / dbeta = column sums of the per-CTA partials: 32 columns x 8 partial lanes per CTA.
 template <typename T>
-__global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int cols,
-                                            T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * cols) return;
+__global__ void __launch_bounds__(256)
+layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int cols,
+                            T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float red[8][33];
+  const int col_lane = threadIdx.x & 31, part_lane = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + col_lane;
   float s = 0.f;
-  for (int p = 0; p < num_partials; ++p) s += partial[int64_t(p) * 2 * cols + c];
-  if (c < cols) dgamma[c] = from_float<T>(s); else dbeta[c - cols] = from_float<T>(s);
+  if (c < 2 * cols)
+    for (int p = part_lane; p < num_partials; p += 8) s += partial[int64_t(p) * 2 * cols + c];
+  red[part_lane][col_lane] = s;
+  __syncthreads();
+  if (part_lane == 0 && c < 2 * cols) {
+#pragma unroll
+    for (int l = 1; l < 8; ++l) s += red[l][col_lane];
+    if (c < cols) dgamma[c] = from_float<T>(s); else dbeta[c - cols] = from_float<T>(s);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -527,7 +565,7 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
                                  mean, rstd, rows, cols, static_cast<T*>(dx), partial, static_cast<const T*>(dres),
                                  grid, smem, stream))
       return cudaErrorInvalidValue;
-    layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 256), 256, 0, stream>>>(
+    layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 32), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
   })
   return cudaGetLastError();
