@@ -44,8 +44,16 @@ cross_entropy_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict
   if (vec_ok) {
     for (int64_t i = int64_t(threadIdx.x) * VEC; i < vocab; i += kCeThreads * VEC) {
       Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(row + i);
+      // One running-maximum update per pack (the exponential unit is the scarce resource here:
+      // VEC + 1 exponentials per VEC elements instead of up to 2 * VEC).
+      float v[VEC], pm = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) add(to_float(p.v[k]));
+      for (int k = 0; k < VEC; ++k) { v[k] = to_float(p.v[k]); pm = fmaxf(pm, v[k]); }
+      if (pm > m) { s *= __expf(m - pm); m = pm; }
+      if (m != -INFINITY) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) s += __expf(v[k] - m);
+      }
     }
   } else {
     for (int64_t i = threadIdx.x; i < vocab; i += kCeThreads) add(to_float(row[i]));
