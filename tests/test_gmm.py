@@ -185,3 +185,24 @@ print('PAIR-OK')
     env['PYTHONPATH'] = root + os.pathsep + env.get('PYTHONPATH', '')
     res = subprocess.run([sys.executable, '-c', code], env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and 'PAIR-OK' in res.stdout, res.stderr[-2000:]
+
+
+@pytest.mark.parametrize('device', DEVICES)
+def test_alpha_scales_the_accumulators(device):
+    """``alpha`` multiplies the product before the epilogue: NT output and TN (ragged-K) weight gradient."""
+    dtype = _dtype_for(device)
+    z, m, k, n = 4, 700, 128, 256
+    counts, bins = _sizes(z, m, device)
+    a = torch.randn(m, k).mul(0.5).to(dtype).to(device)
+    w = torch.randn(z, n, k).mul(0.2).to(dtype).to(device)
+    plain, _, _ = G.grouped_gemm(a, w, bins, trans_b=True)
+    scaled, _, _ = G.grouped_gemm(a, w, bins, trans_b=True, alpha=0.25)
+    _close(scaled, _ref_gmm(a.cpu(), w.cpu(), counts, True) * 0.25, dtype)
+    _close(scaled, plain.float() * 0.25, dtype)
+    g = torch.randn(m, n).mul(0.5).to(dtype).to(device)
+    dw, _, _ = G.grouped_gemm(g, a, bins, trans_a=True, num_groups=z, alpha=0.125)
+    ref, start = [], 0
+    for c in counts.tolist():
+        ref.append(g[start:start + c].float().cpu().t() @ a[start:start + c].float().cpu())
+        start += c
+    _close(dw, torch.stack(ref) * 0.125, dtype)
