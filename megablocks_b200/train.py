@@ -248,6 +248,8 @@ def main(argv=None):
     ap.add_argument('--min-lr', type=float, default=6e-5)
     ap.add_argument('--zero1', action='store_true', help='shard the optimizer state of the replicated parameters')
     ap.add_argument('--recompute', action='store_true', help='activation checkpointing of every block')
+    ap.add_argument('--defer-expert-update', action='store_true',
+                    help='run the expert Adam update on a side stream, layer by layer, under the next forward')
     ap.add_argument('--ep-comm', choices=['auto', 'fused', 'nccl'], default='auto')
     ap.add_argument('--log', type=str, default=None, help='JSONL metrics file')
     ap.add_argument('--log-interval', type=int, default=10)
@@ -284,7 +286,8 @@ def main(argv=None):
         overrides.update(dropless=False, moe_capacity_factor=args.capacity_factor)
     cfg = preset(args.preset, **overrides)
     model = MoETransformer(cfg)
-    trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1),
+    trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1,
+                                           overlap_expert_update=args.defer_expert_update),
                       dp_group=group)
     if args.load:
         state = checkpoint.load(args.load, rank, world, map_location=device)
