@@ -222,7 +222,7 @@ def run_ours(args):
               extra_config={'mlp_impl': args.mlp_impl, 'memory_optimized_mlp': args.memory_optimized_mlp,
                             'ep_comm': ('none' if world == 1 else
                                         'fused peer-memory kernels (remote stores + flags, no NCCL all-to-all)'
-                                        if model.blocks[0].moe.experts._ep_workspace is not None else
+                                        if model.blocks[0].moe.experts._ep_workspaces else
                                         'nccl all_to_all')})
     if world > 1:
         dist.destroy_process_group()

@@ -6,7 +6,7 @@ configurations.  Reports milliseconds, TFLOP/s and the fraction of the measured
 dense bf16 peak (``MEASURED_PEAKS.json`` at the repository root when present).
 
     python -m megablocks_b200.benchmarks.matmul_benchmark [--shape T H F E] [--iters N] [--zipf S]
-                                                          [--case PREFIX] [--warmup N]
+                                                          [--case PREFIX] [--warmup N] [--pair 0|1]
 """
 
 import argparse
@@ -47,7 +47,7 @@ def routed_bins(tokens, experts, zipf, device):
     return torch.cumsum(counts, 0).to(torch.int32).to(device)
 
 
-def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16, only=None, warmup=5):
+def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16, only=None, warmup=5, pair=None):
     dev = torch.device('cuda')
     peak, kind = measured_peak_tflops()
     bins = routed_bins(tokens, experts, zipf, dev)
@@ -56,15 +56,15 @@ def run_shape(tokens, hidden, ffn, experts, iters, zipf, dtype=torch.bfloat16, o
     w = torch.randn(experts, ffn, hidden, device=dev, dtype=dtype) * 0.02
     flops = 2.0 * tokens * hidden * ffn
     cases = {
-        'NT  x @ w1^T': lambda: G.grouped_gemm(x, w, bins, trans_b=True),
+        'NT  x @ w1^T': lambda: G.grouped_gemm(x, w, bins, trans_b=True, pair=pair),
         'NT  + gelu epilogue (2 outputs)': lambda: G.grouped_gemm(x, w, bins, trans_b=True, epilogue=G.EPI_ACT,
-                                                                  act=G.ACT_GELU_TANH),
+                                                                  act=G.ACT_GELU_TANH, pair=pair),
         'NT  + gelu-backward epilogue': lambda: G.grouped_gemm(x, w, bins, trans_b=True, epilogue=G.EPI_DACT,
-                                                               act=G.ACT_GELU_TANH, aux1=h),
-        'NN  h @ w2': lambda: G.grouped_gemm(h, w, bins),
-        'TN  h^T @ x (weight grad)': lambda: G.grouped_gemm(h, x, bins, trans_a=True, num_groups=experts),
+                                                               act=G.ACT_GELU_TANH, aux1=h, pair=pair),
+        'NN  h @ w2': lambda: G.grouped_gemm(h, w, bins, pair=pair),
+        'TN  h^T @ x (weight grad)': lambda: G.grouped_gemm(h, x, bins, trans_a=True, num_groups=experts, pair=pair),
     }
-    print(f'shape tokens={tokens} hidden={hidden} ffn={ffn} experts={experts} zipf={zipf}')
+    print(f'shape tokens={tokens} hidden={hidden} ffn={ffn} experts={experts} zipf={zipf} pair={pair}')
     for name, fn in cases.items():
         if only is not None and not name.startswith(only):
             continue
@@ -80,10 +80,12 @@ def main():
     ap.add_argument('--zipf', type=float, default=0.0)
     ap.add_argument('--case', type=str, default=None, help='run only the cases whose name starts with this')
     ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--pair', type=int, default=None, choices=(0, 1),
+                    help='force the single-CTA (0) or the CTA-pair (1) kernel; default: automatic')
     args = ap.parse_args()
     shapes = [tuple(args.shape)] if args.shape else SHAPES
     for shape in shapes:
-        run_shape(*shape, iters=args.iters, zipf=args.zipf, only=args.case, warmup=args.warmup)
+        run_shape(*shape, iters=args.iters, zipf=args.zipf, only=args.case, warmup=args.warmup, pair=args.pair)
 
 
 if __name__ == '__main__':

@@ -53,6 +53,9 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
 int64_t read_status(bool clear);
 int64_t launch_count();
 at::Tensor gemm_role_timers(const at::Tensor& like);
+at::Tensor bsmm_op(int64_t mode, const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn,
+                   const at::Tensor& idx0, const c10::optional<at::Tensor>& idx1,
+                   const c10::optional<at::Tensor>& idx2, int64_t out_rows, int64_t out_cols);
 
 // torch_glue.cpp: symmetric heap and expert-parallel exchange
 std::vector<at::Tensor> symm_alloc(int64_t nbytes);
@@ -70,7 +73,7 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
 void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
-                       int64_t off_flags, int64_t seq, at::Tensor done);
+                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done);
 void ep_set_flag_op(at::Tensor flag, int64_t value);
 void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code);
 
@@ -129,6 +132,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_alloc", &mb::symm_alloc);
   m.def("symm_open", &mb::symm_open);
   m.def("symm_close", &mb::symm_close);
+  m.def("bsmm", &mb::bsmm_op,
+        "Block-sparse sdd (0) / dsd (1) / dds (2) over 128 x 128 blocks on tcgen05 tensor cores");
   m.def("ep_exchange_counts", &mb::ep_exchange_counts_op);
   m.def("ep_push_rows", &mb::ep_push_rows_op);
   m.def("ep_return_rows", &mb::ep_return_rows_op);

@@ -54,9 +54,13 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int target, int* stat
   const uint64_t t0 = ep_timer_ns();
   uint32_t spins = 0;
   while (ld_acquire_sys(flag) < target) {
-    if ((++spins & 63u) == 0u && ep_timer_ns() - t0 > kEpWaitLimitNs) {
-      atomicCAS(status, 0, code);
-      return false;
+    if ((++spins & 63u) == 0u) {
+      // A failure already recorded on this device ends every later wait at once.
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (ep_timer_ns() - t0 > kEpWaitLimitNs) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
     }
   }
   return true;
@@ -88,28 +92,46 @@ exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int* __
   // (b) release one flag per peer, (c) wait for every peer's flag.
   if (threadIdx.x < L.world)
     st_release_sys(peer_ptr<int>(L.peer_base, threadIdx.x, L.off_count_flags) + L.rank, seq);
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = 1;
+  __shared__ int ok_s, dead_s;
+  if (threadIdx.x == 0) {
+    ok_s = 1;
+    dead_s = *reinterpret_cast<volatile int*>(status) != 0;   // an earlier failure on this device
+  }
   __syncthreads();
   if (threadIdx.x < L.world) {
     const int* mine = peer_ptr<int>(L.peer_base, L.rank, L.off_count_flags) + threadIdx.x;
     if (!wait_flag(mine, seq, status, kEpErrCounts)) ok_s = 0;
   }
   __syncthreads();
-  if (!ok_s) return;
-  // (d) local copy of the matrix and receive-side prefix sums.
+  if (!ok_s || dead_s) {
+    // Fail closed: with an all-zero count matrix every kernel that follows on this stream
+    // (push, expert GEMMs, return) finds nothing to move and stores nothing anywhere.
+    for (int i = threadIdx.x; i < L.world * L.num_experts; i += blockDim.x) counts_out[i] = 0;
+    for (int j = threadIdx.x; j < L.experts_per_rank; j += blockDim.x) recv_bins[j] = 0;
+    return;
+  }
+  // (d) local copy of the matrix and receive-side prefix sums.  A count outside [0, copy_bound]
+  // cannot come from a healthy peer; it is treated like an overflow.
   const int* counts = peer_ptr<int>(L.peer_base, L.rank, counts_off);
-  for (int i = threadIdx.x; i < L.world * L.num_experts; i += blockDim.x)
-    counts_out[i] = ld_acquire_sys(counts + i);
+  __shared__ int bad_s;
+  if (threadIdx.x == 0) bad_s = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < L.world * L.num_experts; i += blockDim.x) {
+    int v = ld_acquire_sys(counts + i);
+    if (v < 0 || v > L.capacity_rows) { v = 0; bad_s = 1; }
+    counts_out[i] = v;
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int j = 0; j < L.experts_per_rank; ++j) {
       const int e = L.rank * L.experts_per_rank + j;
       for (int s = 0; s < L.world; ++s) acc += counts_out[s * L.num_experts + e];
-      recv_bins[j] = acc;
+      // More rows than the buffer holds: the senders skip them (see push_rows_kernel), the
+      // receiver's groups end at the capacity, and the status word reports the overflow.
+      recv_bins[j] = min(acc, L.capacity_rows);
     }
-    if (acc > L.capacity_rows) atomicCAS(status, 0, kEpErrOverflow);
+    if (acc > L.capacity_rows || bad_s) atomicCAS(status, 0, kEpErrOverflow);
   }
 }
 
@@ -126,6 +148,9 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
   int* dst_start = smem;                    // [E] first row of (me, e) in the owner's buffer
   int* src_start = smem + L.num_experts;    // [E] first sorted position of e here
   const int E = L.num_experts, W = L.world, epr = L.experts_per_rank;
+  // A recorded failure (a peer that never answered, an overflow) makes the exchange inert:
+  // nothing is stored into any peer and no flag is released.
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int first = (e / epr) * epr;
     int acc = 0;
@@ -161,7 +186,9 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
     const int owner = e / epr;
     const int copy = __ldg(indices + i);
     const T* src = x + int64_t(copy / top_k) * cols;
-    T* dst = peer_ptr<T>(data_base, owner, off_recv) + int64_t(dst_start[e] + (i - src_start[e])) * cols;
+    const int dst_row = dst_start[e] + (i - src_start[e]);
+    if (e >= E || dst_row < 0 || dst_row >= L.capacity_rows) continue;   // never store outside the owner's buffer
+    T* dst = peer_ptr<T>(data_base, owner, off_recv) + int64_t(dst_row) * cols;
     const float scale = weights != nullptr ? to_float(weights[copy]) : 1.f;
     // Four 16-byte loads in flight per lane before the first (remote) store.
     for (int c0 = lane * VEC; c0 < cols; c0 += 4 * 32 * VEC) {
@@ -209,9 +236,10 @@ template <typename T>
 __global__ void __launch_bounds__(kPushWarps * 32)
 return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLayout L,
                    const uint64_t* __restrict__ data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
-                   int* __restrict__ done) {
+                   int rows_bound, int ret_rows, int* __restrict__ done, const int* status) {
   extern __shared__ int smem[];
   const int E = L.num_experts, W = L.world, epr = L.experts_per_rank;
+  if (*reinterpret_cast<const volatile int*>(status) != 0) return;   // inert after a recorded failure
   int* seg_end = smem;                 // [epr * W] inclusive end row of segment (j, s) here
   int* remote_start = smem + epr * W;  // [epr * W] first sorted position of (s, e_j) at source s
   int* per_source = smem + 2 * epr * W;  // [W] rows I return to source s
@@ -238,7 +266,7 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
       st_release_sys(peer_ptr<int>(L.peer_base, s, off_flags) + L.rank, seq);
   }
   __syncthreads();
-  const int total = seg_end[epr * W - 1];
+  const int total = min(seg_end[epr * W - 1], rows_bound);   // never read past y
   const int lane = threadIdx.x & 31;
   constexpr int VEC = 16 / sizeof(T);
   // Contiguous row range per CTA; one system-scope fence per CTA (see push_rows_kernel).
@@ -254,6 +282,7 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
     const int s = lo % W;
     const int seg_begin = lo ? seg_end[lo - 1] : 0;
     const int remote_row = remote_start[lo] + (row - seg_begin);
+    if (lo >= epr * W || remote_row < 0 || remote_row >= ret_rows) continue;   // outside the source's buffer
     const T* src = y + int64_t(row) * cols;
     T* dst = peer_ptr<T>(data_base, s, off_ret) + int64_t(remote_row) * cols;
     for (int c0 = lane * VEC; c0 < cols; c0 += 4 * 32 * VEC) {
@@ -330,7 +359,8 @@ cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const vo
 
 cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const EpLayout& layout,
                            const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
-                           int rows_bound, int* done, int sms, cudaStream_t stream) {
+                           int rows_bound, int ret_rows, int* done, const int* status, int sms,
+                           cudaStream_t stream) {
   const int elem = type == kF32 ? 4 : 2;
   if ((int64_t(cols) * elem) % 16 != 0) return cudaErrorInvalidValue;
   const int segs = layout.experts_per_rank * layout.world;
@@ -339,7 +369,8 @@ cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const E
   const int grid = max(1, min(ceil_div(max(rows_bound, 1), kPushWarps), sms * 4));
   MB_SWITCH_FLOAT(type, T, {
     return_rows_kernel<T><<<grid, kPushWarps * 32, smem, stream>>>(static_cast<const T*>(y), counts, layout,
-                                                                  data_base, off_ret, off_flags, seq, cols, done);
+                                                                  data_base, off_ret, off_flags, seq, cols, rows_bound,
+                                                                  ret_rows, done, status);
   })
   return cudaGetLastError();
 }

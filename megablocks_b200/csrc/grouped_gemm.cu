@@ -19,6 +19,8 @@ cudaError_t launch(bool bf16, int layout, int block_n, const CUtensorMap& ta, co
     if (bf16 && layout == kNN) return launch_pair<__nv_bfloat16, kNN>(ta, tb, p, grid, stream);
     if (!bf16 && layout == kNT) return launch_pair<__half, kNT>(ta, tb, p, grid, stream);
     if (!bf16 && layout == kNN) return launch_pair<__half, kNN>(ta, tb, p, grid, stream);
+    if (bf16 && layout == kTN) return launch_pair<__nv_bfloat16, kTN>(ta, tb, p, grid, stream);
+    if (!bf16 && layout == kTN) return launch_pair<__half, kTN>(ta, tb, p, grid, stream);
     return cudaErrorInvalidValue;
   }
   if (block_n != 64 && block_n != 128 && block_n != 256) return cudaErrorInvalidValue;

@@ -595,6 +595,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   uint64_t* scatter_bar = bars + 2 * kStages + 6;  // [2] fused combine: "all warps stored this tile"
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  volatile int* dead_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 8);
   const bool scatter_on = LAYOUT == kNN && p.scatter_base != nullptr;
   // Up to kSmallGroups groups the tables fit behind the barriers; more groups, or the segment tables
   // of the fused combine, take the place of the alternate staging buffers.
@@ -616,6 +617,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   for (int g = threadIdx.x; g < G; g += kThreads) s_row_end[g] = __ldg(p.bins + g);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    // A launch that takes part in the expert-parallel exchange does nothing once a failure has
+    // been recorded on this device: its row counts and peer offsets may then be meaningless.
+    *dead_flag = (p.wait_flags != nullptr || scatter_on) && *reinterpret_cast<volatile int*>(p.status) != 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -631,16 +635,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
   if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_base_slot), Cfg::kTmemCols);
   __syncthreads();
-  if (LAYOUT != kTN && threadIdx.x == 0) {
+  const bool dead = *dead_flag != 0;
+  if (threadIdx.x == 0) {
+    // Group ends are forced to be non-decreasing and inside the operand, so no tile can start or
+    // end outside a or c whatever `bins` holds.
     int acc = 0, prev = 0;
     for (int g = 0; g < G; ++g) {
-      const int end = s_row_end[g];
-      acc += (end - prev + kBlockM - 1) / kBlockM;
-      s_mblk_end[g] = acc;
+      const int end = min(max(s_row_end[g], prev), p.rows_total);
+      s_row_end[g] = end;
+      if (LAYOUT != kTN) {
+        acc += (end - prev + kBlockM - 1) / kBlockM;
+        s_mblk_end[g] = acc;
+      }
       prev = end;
     }
   }
-  if (scatter_on) {
+  if (scatter_on && !dead) {
     const int W = p.scatter_world, E = p.scatter_experts, epr = G;
     if (threadIdx.x == 0) {
       int acc = 0;
@@ -675,7 +685,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   // ---- tile schedule (every role decodes the same sequence) ---------------------
   const int num_nb = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int num_mb_tn = (p.M + kBlockM - 1) / kBlockM;
-  const int total_tiles = (LAYOUT == kTN) ? G * num_mb_tn * num_nb : (G > 0 ? s_mblk_end[G - 1] : 0) * num_nb;
+  const int total_tiles =
+      dead ? 0 : ((LAYOUT == kTN) ? G * num_mb_tn * num_nb : (G > 0 ? s_mblk_end[G - 1] : 0) * num_nb);
 
   auto decode = [&](int t) {
     Tile tile;
@@ -808,12 +819,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // Rows of the last K block that belong to the next group (or lie past the tensor)
           // must not contribute.  Zero rows in ONE operand cancel finite rows of the other, and
           // the rows after any group but the last are the next group's data, so only the A side
-          // is cleared there; after the last group the rows may never have been written, and
-          // both sides are cleared.
+          // is cleared there; after the last group that has rows the memory may never have been
+          // written, and both sides are cleared.
           const int valid = tile.k_len - kb * kBlockK;
           if (valid < kBlockK) {
             const int tail_chunks = (kBlockK - valid) * 8;   // 16-byte chunks per box
-            const int boxes = tile.group == G - 1 ? kBlockM / 64 + BLOCK_N / 64 : kBlockM / 64;
+            const bool at_end = tile.k_begin + tile.k_len >= s_row_end[G - 1];   // no later group has rows
+            const int boxes = at_end ? kBlockM / 64 + BLOCK_N / 64 : kBlockM / 64;
             for (int box = 0; box < boxes; ++box) {
               uint8_t* base = (box < kBlockM / 64) ? a_tile + box * kBoxBytes
                                                    : b_tile + (box - kBlockM / 64) * kBoxBytes;
@@ -900,7 +912,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int seg = tile.group * W + s2;
             const int seg_begin = seg ? s_seg_end[seg - 1] : 0;
             const int64_t remote_row = s_remote_start[seg] + (grow - seg_begin);
-            targets.row[i] = reinterpret_cast<T*>(p.scatter_base[s2] + p.scatter_off) + remote_row * p.N;
+            if (remote_row >= 0 && remote_row < p.scatter_rows)   // never store outside the source's buffer
+              targets.row[i] = reinterpret_cast<T*>(p.scatter_base[s2] + p.scatter_off) + remote_row * p.N;
           }
         }
       }
@@ -1036,7 +1049,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       MB_T_WRITE(11, t_aux);
     }
     // Rows past the last group belong to nobody: defined as zero (NT / NN only).
-    if (LAYOUT != kTN && p.zero_tail) {
+    if (LAYOUT != kTN && p.zero_tail && !dead) {
       const int last = G > 0 ? s_row_end[G - 1] : 0;
       const int64_t begin = int64_t(last) * p.N, end = int64_t(p.rows_total) * p.N;
       const int64_t tid = int64_t(blockIdx.x) * (kEpilogueWarps * 32) + threadIdx.x;

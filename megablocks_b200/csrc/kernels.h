@@ -112,7 +112,7 @@ struct EpLayout {
   int rank;
   int num_experts;
   int experts_per_rank;
-  int capacity_rows;        // rows the receive buffers can hold
+  int capacity_rows;        // rows the receive buffers can hold (stores past it are skipped)
   int64_t off_counts;       // int32 [2][world][num_experts]
   int64_t off_count_flags;  // int32 [world]
 };
@@ -129,7 +129,8 @@ cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const vo
                          int* status, int sms, cudaStream_t stream);
 cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const EpLayout& layout,
                            const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
-                           int rows_bound, int* done, int sms, cudaStream_t stream);
+                           int rows_bound, int ret_rows, int* done, const int* status, int sms,
+                           cudaStream_t stream);
 cudaError_t ep_set_flag(int* flag, int value, cudaStream_t stream);
 cudaError_t ep_wait_flags(const int* flags, int count, int seq, int* status, int code, cudaStream_t stream);
 
@@ -183,6 +184,7 @@ struct GemmParams {
   int scatter_rank;
   int scatter_experts;                // global number of experts
   int scatter_seq;
+  int scatter_rows;                   // rows of every rank's return buffer (stores past it are skipped)
   // Optional TMA stores of the outputs (single-CTA kernel): tensor maps of c / out2 / out3 viewed as
   // [rows, N] with 32 x 32 boxes and 64-byte swizzle.  Warps whose 32 rows of a tile all exist hand
   // their staged chunk to the TMA unit instead of storing it with the LSU.  0 = off.
@@ -194,10 +196,47 @@ struct GemmParams {
 
 // block_n is 64, 128 or 256.  The tensor maps describe a and b as row-major 16-bit
 // matrices with 64-column boxes and 128-byte swizzle.
-// `pair`: run the CTA-pair kernel (cta_group::2, 256-row tiles; NT / NN with block_n 256, even
-// grid; the B tensor map must then have 128-row boxes for NT).
+// `pair`: run the CTA-pair kernel (cta_group::2, 256-row tiles; block_n 256, even grid; for NT
+// the B tensor map must then have 128-row boxes, NN and TN use the 64-row boxes of the single-CTA
+// kernel).
 cudaError_t launch(bool bf16, int layout, int block_n, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                    const GemmParams& params, int grid, cudaStream_t stream, bool pair = false);
 
 }  // namespace gemm
+
+// ---- block-sparse products (bsmm.cu) ------------------------------------------------
+namespace bsmm {
+
+enum Mode : int { kSdd = 0, kDsd = 1, kDds = 2 };
+constexpr int kBlock = 128;   // block size of the topology = edge of an output tile
+
+// One launch computes every 128 x 128 output tile of one product over a BCSR topology with
+// 128 x 128 blocks.  All index arrays are int32 device arrays.
+struct BsmmParams {
+  int mode;
+  int num_tiles;
+  int tiles_inner;             // dsd: column tiles per block row; dds: row tiles per block column
+  int K;                       // sdd: dense contraction length
+  const int* row_indices;      // sdd: block row of every stored block
+  const int* column_indices;   // sdd: block column of every stored block
+  // dsd / dds: per output block row (dsd) or block column (dds) j, the stored blocks
+  // seg_offsets[j] .. seg_offsets[j + 1) to accumulate: seg_block[idx] is the position of the
+  // block in the value array (null = idx itself), seg_k[idx] the 128-wide slice of the dense
+  // operand it multiplies.
+  const int* seg_offsets;
+  const int* seg_block;
+  const int* seg_k;
+  void* out;                   // row-major 16-bit output
+  int64_t out_ld;              // its row stride in elements
+  int out_rows;
+  int out_cols;
+  int* status;
+};
+
+// The tensor maps describe the stored (row-major, 16-bit) operands with 64-column boxes and
+// 128-byte swizzle: 128-row boxes for a K-major operand, 64-row boxes for an MN-major one.
+cudaError_t launch(bool bf16, bool a_mn_major, bool b_mn_major, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                   const BsmmParams& params, int grid, cudaStream_t stream);
+
+}  // namespace bsmm
 }  // namespace mb

@@ -565,10 +565,10 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   if (scatter.has_value()) {
     // scatter = {data heap bases, flag heap bases, counts, done}; scatter_args = {data offset, flag
-    // offset, world, rank, experts, seq}.
+    // offset, world, rank, experts, seq, rows of the return buffer}.
     TORCH_CHECK(epilogue == kEpiNone || epilogue == kEpiAdd, "the fused combine supports the plain and the add epilogue");
-    TORCH_CHECK(layout == kNN && scatter->size() == 4 && scatter_args.size() == 6,
-                "the fused combine needs the NN layout, four tensors and six integers");
+    TORCH_CHECK(layout == kNN && scatter->size() == 4 && scatter_args.size() == 7,
+                "the fused combine needs the NN layout, four tensors and seven integers");
     const auto& bases = (*scatter)[0];
     const auto& flag_bases = (*scatter)[1];
     const auto& counts = (*scatter)[2];
@@ -590,6 +590,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     p.scatter_rank = int(scatter_args[3]);
     p.scatter_experts = int(scatter_args[4]);
     p.scatter_seq = int(scatter_args[5]);
+    p.scatter_rows = int(scatter_args[6]);
     p.zero_tail = 0;   // there is no local output to clear
   }
   if (out_numel == 0) return {c, out2, out3};
@@ -600,9 +601,14 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   // contraction is deep enough for the mainloop, not the epilogue, to set the pace.
   // pair_mode: -1 = decide here, 0 = never, 1 = whenever the kernel supports the problem.
   const int64_t rows_expected = rows_hint > 0 ? rows_hint : a.size(0);
-  bool pair = layout != kTN && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
+  bool pair = block_n == 256 && sm_count() >= 2 && !scatter.has_value();
   if (pair_mode == 0) pair = false;
-  else if (pair_mode < 0) pair = pair && rows_expected / num_groups >= 2048 && p.K >= 2048;
+  else if (pair_mode < 0) {
+    // NT / NN: long groups and a deep contraction.  TN (weight gradients): M and N are fixed, so
+    // 256-row tiles lose nothing to group quantisation; taken when the output has whole pair tiles.
+    if (layout == kTN) pair = pair && p.M >= 256 && rows_expected / num_groups >= 256;
+    else pair = pair && rows_expected / num_groups >= 2048 && p.K >= 2048;
+  }
   if (!scatter.has_value() && store_tma_enabled()) {
     // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
     const int64_t out_rows = out_numel / p.N;
@@ -615,10 +621,16 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   int64_t tiles_bound;
   const int64_t num_nb = ceil_div(p.N, block_n);
   if (pair) {
-    ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
-    tb = layout == kNT ? make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n / 2)
-                       : make_tensor_map(b.data_ptr(), bf16, num_groups * p.K, p.N, 64);
-    tiles_bound = (ceil_div(a.size(0), 2 * kBlockM) + num_groups) * num_nb;
+    if (layout == kTN) {
+      ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.M, 64);
+      tb = make_tensor_map(b.data_ptr(), bf16, b.size(0), p.N, 64);
+      tiles_bound = num_groups * ceil_div(p.M, 2 * kBlockM) * num_nb;
+    } else {
+      ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
+      tb = layout == kNT ? make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n / 2)
+                         : make_tensor_map(b.data_ptr(), bf16, num_groups * p.K, p.N, 64);
+      tiles_bound = (ceil_div(a.size(0), 2 * kBlockM) + num_groups) * num_nb;
+    }
     const int pairs = int(std::max<int64_t>(1, std::min<int64_t>(tiles_bound, sm_count() / 2)));
     MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, 2 * pairs, stream(), true));
     MB_LAUNCHED(1);
@@ -641,6 +653,94 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   MB_CUDA_OK(launch(bf16, layout, block_n, ta, tb, p, grid, stream()));
   MB_LAUNCHED(1);
   return {c, out2, out3};
+}
+
+// ---------------------------------------------------------------------------
+// block-sparse products
+// ---------------------------------------------------------------------------
+// `a` and `b` are the operands as stored (contiguous, row-major, 16-bit):
+//   sdd  a = [M, K] (or [K, M] with a_mn), b = [K, N] with b_mn (or [N, K]); idx0 / idx1 = block row /
+//        block column of every stored block; returns the block values [nnz, 128, 128];
+//   dsd  a = block values [nnz, 128, 128] (a_mn = the topology is used transposed), b dense as for sdd;
+//   dds  a dense as for sdd, b = block values (b_mn = the topology is NOT transposed);
+//        idx0 = segment offsets, idx1 = position of every listed block in the value array (optional:
+//        absent = the list is in storage order), idx2 = 128-wide slice of the dense operand per block;
+//        returns the dense [out_rows, out_cols] product.
+at::Tensor bsmm_op(int64_t mode, const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn,
+                   const at::Tensor& idx0, const c10::optional<at::Tensor>& idx1,
+                   const c10::optional<at::Tensor>& idx2, int64_t out_rows, int64_t out_cols) {
+  using namespace bsmm;
+  MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b);
+  TORCH_CHECK((a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf) && a.scalar_type() == b.scalar_type(),
+              "bsmm: operands must both be bf16 or both fp16");
+  auto check_idx = [](const at::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kInt, name, " must be a contiguous CUDA int32 tensor");
+  };
+  check_idx(idx0, "bsmm index 0");
+  c10::cuda::CUDAGuard guard(a.device());
+  const bool bf16 = a.scalar_type() == at::kBFloat16;
+  auto as2d = [](const at::Tensor& t) { return t.dim() == 3 ? t.view({t.size(0) * t.size(1), t.size(2)}) : t; };
+  const at::Tensor a2 = as2d(a), b2 = as2d(b);
+  TORCH_CHECK(a2.dim() == 2 && b2.dim() == 2, "bsmm: operands must be matrices or [nnz, 128, 128] block arrays");
+
+  BsmmParams p{};
+  p.mode = int(mode);
+  p.status = status_word(a.device()).data_ptr<int>();
+  at::Tensor out;
+  if (mode == kSdd) {
+    TORCH_CHECK(idx1.has_value(), "sdd needs row and column indices");
+    check_idx(*idx1, "bsmm index 1");
+    const int64_t nnz = idx0.numel();
+    TORCH_CHECK(idx1->numel() == nnz, "sdd: row and column index arrays differ in length");
+    const int64_t ka = a_mn ? a2.size(0) : a2.size(1), kb = b_mn ? b2.size(0) : b2.size(1);
+    TORCH_CHECK(ka == kb, "sdd: contraction lengths differ");
+    const int64_t m = a_mn ? a2.size(1) : a2.size(0), n = b_mn ? b2.size(1) : b2.size(0);
+    TORCH_CHECK(m % kBlock == 0 && n % kBlock == 0, "sdd: output dimensions must be multiples of 128");
+    out = at::empty({nnz, kBlock, kBlock}, a.options());
+    p.K = int(ka);
+    p.row_indices = idx0.data_ptr<int>();
+    p.column_indices = idx1->data_ptr<int>();
+    p.num_tiles = int(nnz);
+    p.tiles_inner = 1;
+    p.out_ld = kBlock;
+    p.out_rows = int(nnz * kBlock);
+    p.out_cols = kBlock;
+  } else {
+    TORCH_CHECK(mode == kDsd || mode == kDds, "bsmm: unknown mode");
+    TORCH_CHECK(idx2.has_value(), "dsd / dds need the segment list");
+    check_idx(*idx2, "bsmm index 2");
+    if (idx1.has_value()) check_idx(*idx1, "bsmm index 1");
+    const at::Tensor& values = mode == kDsd ? a2 : b2;
+    TORCH_CHECK(values.size(1) == kBlock && values.size(0) % kBlock == 0, "bsmm: block values must be [nnz, 128, 128]");
+    TORCH_CHECK(idx2->numel() <= values.size(0) / kBlock && (!idx1.has_value() || idx1->numel() == idx2->numel()),
+                "bsmm: the segment list is longer than the block array");
+    out = at::empty({out_rows, out_cols}, a.options());
+    const int64_t lists = idx0.numel() - 1;
+    p.seg_offsets = idx0.data_ptr<int>();
+    p.seg_block = idx1.has_value() ? idx1->data_ptr<int>() : nullptr;
+    p.seg_k = idx2->data_ptr<int>();
+    if (mode == kDsd) {
+      TORCH_CHECK(lists * kBlock == out_rows, "dsd: one segment list per 128 output rows expected");
+      TORCH_CHECK((b_mn ? b2.size(1) : b2.size(0)) == out_cols, "dsd: dense operand does not match the output width");
+      p.tiles_inner = int(ceil_div(out_cols, kBlock));
+    } else {
+      TORCH_CHECK(lists * kBlock == out_cols, "dds: one segment list per 128 output columns expected");
+      TORCH_CHECK((a_mn ? a2.size(1) : a2.size(0)) == out_rows, "dds: dense operand does not match the output height");
+      p.tiles_inner = int(ceil_div(out_rows, kBlock));
+    }
+    p.num_tiles = int(lists * p.tiles_inner);
+    p.out_ld = out_cols;
+    p.out_rows = int(out_rows);
+    p.out_cols = int(out_cols);
+  }
+  p.out = out.data_ptr();
+  if (out.numel() == 0 || p.num_tiles == 0) return out;
+  const CUtensorMap ta = make_tensor_map(a2.data_ptr(), bf16, a2.size(0), a2.size(1), a_mn ? 64 : 128);
+  const CUtensorMap tb = make_tensor_map(b2.data_ptr(), bf16, b2.size(0), b2.size(1), b_mn ? 64 : 128);
+  const int grid = std::max(1, std::min(p.num_tiles, sm_count()));
+  MB_CUDA_OK(launch(bf16, a_mn, b_mn, ta, tb, p, grid, stream()));
+  MB_LAUNCHED(1);
+  return out;
 }
 
 // ---------------------------------------------------------------------------
@@ -907,7 +1007,7 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
 void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
-                       int64_t off_flags, int64_t seq, at::Tensor done) {
+                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done) {
   MB_CHECK_CUDA(y); MB_CHECK_CONTIG(y);
   c10::cuda::CUDAGuard guard(y.device());
   const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
@@ -916,7 +1016,8 @@ void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::
               "data_base must be a CUDA int64 tensor with one address per rank");
   MB_CUDA_OK(ep_return_rows(float_code(y.scalar_type()), y.data_ptr(), counts.data_ptr<int>(), L,
                             reinterpret_cast<const uint64_t*>(data_base.data_ptr<int64_t>()), off_ret, off_flags,
-                            int(seq), int(y.size(1)), int(y.size(0)), done.data_ptr<int>(), sm_count(), stream()));
+                            int(seq), int(y.size(1)), int(y.size(0)), int(ret_rows), done.data_ptr<int>(),
+                            status_ptr(y), sm_count(), stream()));
   MB_LAUNCHED(1);
 }
 

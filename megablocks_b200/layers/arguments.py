@@ -92,6 +92,16 @@ class Arguments:
     # NCCL all-to-all.  ``None`` picks the fused path whenever a symmetric
     # workspace can be created for ``expert_parallel_group``.
     ep_fused_comm: Optional[bool] = None
+    # Fused route only.  ``ep_max_copies``: upper bound of routed copies (tokens x top_k) any rank
+    # sends in one call; the symmetric buffers are sized from it once.  ``None`` sizes them from
+    # the largest first call over the group; a later call with more copies raises instead of
+    # overrunning a peer's buffer.  ``ep_capacity_rows``: rows the receive buffer of a rank holds
+    # (default: world x max copies, which can never overflow).  ``ep_inflight_microbatches``:
+    # workspaces kept per layer, for schedules that run several forwards of a layer before the
+    # first of their backwards (pipeline schedules, forward-forward-backward-backward loops).
+    ep_max_copies: Optional[int] = None
+    ep_capacity_rows: Optional[int] = None
+    ep_inflight_microbatches: int = 1
 
     def __post_init__(self):
         if self.mlp_type not in _MLP_TYPES:

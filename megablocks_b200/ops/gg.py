@@ -180,7 +180,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
                  c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
-                 rows_hint: int = 0, scatter=None, alpha: float = 1.0):
+                 rows_hint: int = 0, scatter=None, alpha: float = 1.0, pair: Optional[int] = None):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -193,11 +193,13 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     ``rows_hint`` is the expected number of occupied rows when ``a`` is a worst-case sized
     buffer (it only steers the choice between the single-CTA and the CTA-pair kernel).
     ``scatter = ([data_bases, flag_bases, counts, done], [data_off, flag_off, world, rank, experts,
-    seq])`` (NN layout) stores every output row into the return buffer of the rank it came from
+    seq, return_rows])`` (NN layout) stores every output row into the return buffer of the rank it came from
     instead of ``c`` and releases that rank's flag after its last row: the expert-parallel combine
     fused into the GEMM epilogue.  The returned ``c`` is then empty.
     ``alpha`` multiplies every accumulator before the epilogue (e.g. the 1 / expert-parallel-world
     factor of expert weight gradients, applied for free instead of by a separate pass).
+    ``pair`` overrides the kernel choice for this call: 1 = CTA pairs (``cta_group::2``, 256-row
+    tiles) whenever the problem allows, 0 = single-CTA kernel, ``None`` = the module default.
     """
     if num_groups is None:
         num_groups = bins.numel()
@@ -205,7 +207,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
         flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
-                                  int(count), int(stride), int(seq), int(rows_hint), _PAIR_MODE,
+                                  int(count), int(stride), int(seq), int(rows_hint),
+                                  _PAIR_MODE if pair is None else int(pair),
                                   scatter[0] if scatter is not None else None,
                                   scatter[1] if scatter is not None else [], float(alpha))
     if scatter is not None:

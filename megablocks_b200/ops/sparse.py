@@ -16,13 +16,22 @@ Products:
 All are differentiable with respect to their dense operands and the block
 values.  A matrix whose topology was produced by the dropless-MoE layer is
 block-diagonal per expert; it carries ``padded_bins`` and the expert MLPs then
-run the tcgen05 grouped kernel directly on it.  Arbitrary topologies run the
-gather-blocks + batched-matmul formulation below on either device.
+run the tcgen05 grouped kernel directly on it.  Any other topology with 128 x 128
+blocks and 16-bit CUDA operands runs the BCSR-driven tcgen05 kernel of
+``csrc/bsmm_kernel.cuh`` (transposed dense operands and transposed topologies are
+read in place, as K-major or MN-major tiles).  Everything else - CPU tensors,
+fp32, other block sizes - runs the gather-blocks + batched-matmul formulation
+below, which is also the oracle of the tests.
 """
 
 from typing import Any, Optional, Tuple
 
 import torch
+
+from megablocks_b200._ext import ext
+
+_KERNEL_BLOCK = 128
+_MODE_SDD, _MODE_DSD, _MODE_DDS = 0, 1, 2
 
 
 class Matrix:
@@ -156,6 +165,64 @@ def random_mask(rows: int, cols: int, sparsity: float, blocking: int = 128, devi
 
 
 # ----------------------------------------------------------------------------
+# tcgen05 route (CUDA, 16-bit, 128 x 128 blocks)
+# ----------------------------------------------------------------------------
+def _stored(x: torch.Tensor):
+    """``(storage, transposed)``: a contiguous row-major tensor that is ``x`` or ``x.t()``, without a copy if possible."""
+    if x.is_contiguous():
+        return x, False
+    if x.dim() == 2 and x.t().is_contiguous():
+        return x.t(), True
+    return x.contiguous(), False
+
+
+def _kernel_ok(blocking: int, *tensors: torch.Tensor) -> bool:
+    if blocking != _KERNEL_BLOCK:
+        return False
+    first = tensors[0]
+    for t in tensors:
+        if not (t.is_cuda and t.dtype == first.dtype and t.dtype in (torch.bfloat16, torch.float16)):
+            return False
+        stored, _ = _stored(t)
+        if stored.shape[-1] % 8 or stored.data_ptr() % 16:
+            return False
+    return True
+
+
+def _i32(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.int32 and t.is_contiguous() else t.to(torch.int32).contiguous()
+
+
+def _segments(s: Matrix, transposed_list: bool):
+    """Segment list ``(offsets, block position or None, k-block)`` of the rows of ``s`` or of ``s^T``."""
+    if transposed_list:
+        return _i32(s.offsets_t), _i32(s.block_offsets_t), _i32(s.column_indices_t)
+    return _i32(s.offsets), None, _i32(s.column_indices)
+
+
+def _sdd_kernel(a: torch.Tensor, b: torch.Tensor, topo: Matrix) -> torch.Tensor:
+    sa, a_t = _stored(a)
+    sb, b_t = _stored(b)
+    # a is [M, K]: stored transposed = MN-major.  b is [K, N]: stored as given = MN-major.
+    return ext().bsmm(_MODE_SDD, sa, a_t, sb, not b_t, _i32(topo.row_indices), _i32(topo.column_indices), None, 0, 0)
+
+
+def _dsd_kernel(s: Matrix, data: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    sb, b_t = _stored(b)
+    offsets, block, kblock = _segments(s, s.is_transposed)
+    return ext().bsmm(_MODE_DSD, data.contiguous(), s.is_transposed, sb, not b_t, offsets, block, kblock, s.size(0),
+                      b.shape[1])
+
+
+def _dds_kernel(a: torch.Tensor, s: Matrix, data: torch.Tensor) -> torch.Tensor:
+    sa, a_t = _stored(a)
+    # Columns of s are the rows of its transpose: a plain topology needs the transposed list.
+    offsets, block, kblock = _segments(s, not s.is_transposed)
+    return ext().bsmm(_MODE_DDS, sa, a_t, data.contiguous(), not s.is_transposed, offsets, block, kblock, a.shape[0],
+                      s.size(1))
+
+
+# ----------------------------------------------------------------------------
 # Products on raw block arrays.  (r, c) index blocks of the *stored* matrix.
 # ----------------------------------------------------------------------------
 def _rc(m: Matrix):
@@ -164,6 +231,8 @@ def _rc(m: Matrix):
 
 def _sdd_blocks(a: torch.Tensor, b: torch.Tensor, topo: Matrix) -> torch.Tensor:
     """Blocks of ``a @ b`` at the nonzero positions of ``topo`` (not transposed)."""
+    if _kernel_ok(topo.blocking, a, b):
+        return _sdd_kernel(a, b, topo)
     blk = topo.blocking
     r, c = _rc(topo)
     a_rows = a.reshape(a.shape[0] // blk, blk, a.shape[1])[r]
@@ -173,6 +242,8 @@ def _sdd_blocks(a: torch.Tensor, b: torch.Tensor, topo: Matrix) -> torch.Tensor:
 
 def _dsd_dense(s: Matrix, data: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """``op(s) @ b`` where ``op`` transposes when ``s`` is flagged transposed."""
+    if _kernel_ok(s.blocking, data, b):
+        return _dsd_kernel(s, data, b)
     blk = s.blocking
     r, c = _rc(s)
     out_rows = s.size(0)
@@ -188,6 +259,8 @@ def _dsd_dense(s: Matrix, data: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 def _dds_dense(a: torch.Tensor, s: Matrix, data: torch.Tensor) -> torch.Tensor:
     """``a @ op(s)``."""
+    if _kernel_ok(s.blocking, a, data):
+        return _dds_kernel(a, s, data)
     blk = s.blocking
     r, c = _rc(s)
     out_cols = s.size(1)
@@ -216,7 +289,7 @@ class _SDD(torch.autograd.Function):
         topo = ctx.topo
         da = db = None
         if ctx.needs_input_grad[0]:
-            da = _dsd_dense(topo, dblocks, b.t().contiguous())
+            da = _dsd_dense(topo, dblocks, b.t())
         if ctx.needs_input_grad[1]:
             db = _dsd_dense(topo.t(), dblocks, a).t()
         return da, db, None
@@ -238,9 +311,9 @@ class _DSD(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             if s.is_transposed:
                 # out = S^T b  =>  dS = b dout^T sampled at S's topology.
-                ddata = _sdd_blocks(b, dout.t().contiguous(), s.t())
+                ddata = _sdd_blocks(b, dout.t(), s.t())
             else:
-                ddata = _sdd_blocks(dout, b.t().contiguous(), s)
+                ddata = _sdd_blocks(dout, b.t(), s)
         if ctx.needs_input_grad[1]:
             db = _dsd_dense(s.t(), data, dout)
         return ddata, db, None
@@ -263,9 +336,9 @@ class _DDS(torch.autograd.Function):
             da = _dds_dense(dout, s.t(), data)
         if ctx.needs_input_grad[1]:
             if s.is_transposed:
-                ddata = _sdd_blocks(dout.t().contiguous(), a, s.t())
+                ddata = _sdd_blocks(dout.t(), a, s.t())
             else:
-                ddata = _sdd_blocks(a.t().contiguous(), dout, s)
+                ddata = _sdd_blocks(a.t(), dout, s)
         return da, ddata, None
 
 

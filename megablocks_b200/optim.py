@@ -185,6 +185,151 @@ class FusedAdam:
             p.data.copy_(self.master[off:off + p.numel()].view_as(p))
 
 
+class Adafactor:
+    """Adafactor (Shazeer & Stern, 2018) with fp32 master weights, for the reference's 760M recipe
+    (``--optimizer adafactor``, exp/dmoe/dmoe_760m_8gpu.sh:70).
+
+    Tensors with two or more dimensions keep one row statistic and one column statistic of the
+    squared gradient over their last two dimensions instead of a full second moment; vectors keep
+    the full moment.  The step size is the external learning rate (no relative step, no parameter
+    scaling), the update is clipped to unit RMS and there is no first moment, which is how an
+    absolute-lr trainer with its own schedule uses the method.  The interface is the one
+    :class:`FusedAdam` offers the trainer.
+    """
+
+    def __init__(self, params: Iterable[torch.Tensor], lr: float = 1e-3, decay_rate: float = 0.8,
+                 eps: float = 1e-30, clip_threshold: float = 1.0, weight_decay: float = 0.0,
+                 norm_weights: Optional[Sequence[float]] = None, **_unused):
+        self.params: List[torch.Tensor] = [p for p in params]
+        self.lr, self.decay_rate, self.eps, self.clip_threshold = lr, decay_rate, eps, clip_threshold
+        self.weight_decay = weight_decay
+        self.step_count = 0
+        self.norm_weights = list(norm_weights) if norm_weights is not None else [1.0] * len(self.params)
+        self.device = self.params[0].device if self.params else torch.device('cpu')
+        self.master = [p.detach().float().clone() for p in self.params]
+        self.row, self.col, self.full = [], [], []
+        for p in self.params:
+            if p.dim() >= 2:
+                self.row.append(torch.zeros(p.shape[:-1], dtype=torch.float32, device=p.device))
+                self.col.append(torch.zeros(p.shape[:-2] + p.shape[-1:], dtype=torch.float32, device=p.device))
+                self.full.append(None)
+            else:
+                self.row.append(None)
+                self.col.append(None)
+                self.full.append(torch.zeros_like(p, dtype=torch.float32))
+
+    def grads(self) -> List[torch.Tensor]:
+        out = []
+        for p in self.params:
+            if p.grad is None:
+                raise RuntimeError('Adafactor.step: a parameter has no gradient')
+            out.append(p.grad)
+        return out
+
+    def add_sqnorm(self, accum: torch.Tensor, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        grads = self.grads() if grads is None else grads
+        for g, w in zip(grads, self.norm_weights):
+            accum[0] += w * g.float().square().sum()
+
+    def begin_step(self, grads=None) -> None:
+        self.step_count += 1
+
+    def step(self, grad_scale: Optional[torch.Tensor] = None, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        if not self.params:
+            return
+        self.begin_step()
+        self.step_range(0, len(self.params), grad_scale, grads)
+
+    def step_range(self, lo: int, hi: int, grad_scale: Optional[torch.Tensor] = None,
+                   grads: Optional[Sequence[torch.Tensor]] = None) -> None:
+        grads = self.grads() if grads is None else grads
+        beta2 = 1.0 - float(self.step_count)**(-self.decay_rate)
+        for i in range(lo, hi):
+            p, w = self.params[i], self.master[i]
+            g = grads[i].detach().float()
+            if grad_scale is not None:
+                g = g * grad_scale[0]
+            sq = g * g + self.eps
+            if self.full[i] is None:
+                row, col = self.row[i], self.col[i]
+                row.mul_(beta2).add_(sq.mean(dim=-1), alpha=1.0 - beta2)
+                col.mul_(beta2).add_(sq.mean(dim=-2), alpha=1.0 - beta2)
+                # v ~ row x col / mean(row): the rank-one reconstruction of the second moment.
+                r = (row / row.mean(dim=-1, keepdim=True)).rsqrt_().unsqueeze(-1)
+                c = col.rsqrt().unsqueeze(-2)
+                update = g * r * c
+            else:
+                v = self.full[i]
+                v.mul_(beta2).add_(sq, alpha=1.0 - beta2)
+                update = g * v.rsqrt()
+            rms = update.square().mean().sqrt()
+            update = update / torch.clamp(rms / self.clip_threshold, min=1.0)
+            if self.weight_decay:
+                w.mul_(1.0 - self.lr * self.weight_decay)
+            w.add_(update, alpha=-self.lr)
+            p.data.copy_(w.view_as(p))
+
+    def state_dict(self):
+        return {'step': self.step_count, 'lr': self.lr, 'master': self.master, 'row': self.row, 'col': self.col,
+                'full': self.full}
+
+    def load_state_dict(self, state):
+        self.step_count = int(state['step'])
+        self.lr = state.get('lr', self.lr)
+        for name in ('master', 'row', 'col', 'full'):
+            for dst, src in zip(getattr(self, name), state[name]):
+                if dst is not None:
+                    dst.copy_(src)
+        for p, w in zip(self.params, self.master):
+            p.data.copy_(w.view_as(p))
+
+
+class DynamicLossScaler:
+    """Loss scaling for fp16 training: the loss is multiplied by ``scale`` before backward and the
+    gradients divided by it inside the optimizer's gradient coefficient.
+
+    A step whose gradient norm is not finite is skipped and halves the scale (after ``hysteresis``
+    such steps in a row); ``growth_interval`` clean steps in a row double it.  These are the rules of
+    the mixed-precision trainer the reference's fp16 recipes run under (``--fp16`` in
+    exp/moe/moe_125m_8gpu.sh and exp/dmoe/dmoe_760m_8gpu.sh; ``Arguments.fp16`` defaults to true,
+    megablocks/layers/arguments.py:53).
+    """
+
+    def __init__(self, init_scale: float = 2.0**16, growth_factor: float = 2.0, backoff_factor: float = 0.5,
+                 growth_interval: int = 1000, hysteresis: int = 2, min_scale: float = 1.0):
+        self.scale = float(init_scale)
+        self.growth_factor, self.backoff_factor = growth_factor, backoff_factor
+        self.growth_interval, self.hysteresis, self.min_scale = growth_interval, hysteresis, min_scale
+        self._good_steps = 0
+        self._bad_budget = hysteresis
+        self.skipped_steps = 0
+
+    def update(self, found_inf: bool) -> None:
+        if found_inf:
+            self.skipped_steps += 1
+            self._good_steps = 0
+            self._bad_budget -= 1
+            if self._bad_budget <= 0:
+                self.scale = max(self.scale * self.backoff_factor, self.min_scale)
+                self._bad_budget = self.hysteresis
+            return
+        self._good_steps += 1
+        if self._good_steps >= self.growth_interval:
+            self.scale *= self.growth_factor
+            self._good_steps = 0
+            self._bad_budget = self.hysteresis
+
+    def state_dict(self):
+        return {'scale': self.scale, 'good_steps': self._good_steps, 'bad_budget': self._bad_budget,
+                'skipped_steps': self.skipped_steps}
+
+    def load_state_dict(self, state):
+        self.scale = float(state['scale'])
+        self._good_steps = int(state['good_steps'])
+        self._bad_budget = int(state['bad_budget'])
+        self.skipped_steps = int(state.get('skipped_steps', 0))
+
+
 def clip_coefficient(sqnorm: torch.Tensor, max_norm: float, extra_scale: float = 1.0) -> torch.Tensor:
     """``[coeff, norm]`` on the device of ``sqnorm``: ``coeff = min(1, max_norm / norm) * extra_scale``."""
     out = torch.empty(2, dtype=torch.float32, device=sqnorm.device)

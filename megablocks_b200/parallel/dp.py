@@ -91,6 +91,9 @@ class GradReducer:
         self._launched = [False] * len(self.buckets)
         self._stream = torch.cuda.Stream() if flat.grad.is_cuda else None
         self._works = []
+        # With gradient accumulation only the last micro-batch's backward may start the collectives:
+        # the trainer clears `active` for the earlier ones.
+        self.active = True
         for i, p in enumerate(flat.params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
 
@@ -102,6 +105,8 @@ class GradReducer:
 
     def _make_hook(self, index: int):
         def hook(_param):
+            if not self.active:
+                return
             bi = self._bucket_of[index]
             self._remaining[bi] -= 1
             if self._remaining[bi] == 0:

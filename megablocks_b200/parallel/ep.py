@@ -88,6 +88,11 @@ class EpWorkspace:
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.num_experts, self.epr = num_experts, num_experts // self.world
+        # Every rank sizes its buffers for the largest copy count of the group: a rank with a
+        # short batch must still be able to receive what the others send.
+        agreed = torch.tensor([int(copies)], dtype=torch.int64, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=group)
+        copies = int(agreed.item())
         self.copies, self.hidden, self.dtype, self.device = copies, hidden, dtype, device
         self.capacity = int(capacity_rows) if capacity_rows else self.world * copies
         elem = torch.empty((), dtype=dtype).element_size()
@@ -163,17 +168,17 @@ class EpWorkspace:
         """Store my expert-ordered rows ``y`` back into the sources' sorted order."""
         if direction == 0:
             ext().ep_return_rows(y, counts, *self._layout(), self.heap.peer_base, self.off_ret_y,
-                                 self.off_ret_flags[0], seq, done)
+                                 self.off_ret_flags[0], seq, self.copies, done)
         else:
             ext().ep_return_rows(y, counts, *self._layout(), self.bwd_heap.peer_base, self.off_ret_dx,
-                                 self.off_ret_flags[1], seq, done)
+                                 self.off_ret_flags[1], seq, self.copies, done)
 
     def scatter_args(self, counts, direction: int, seq: int, done):
         """``scatter`` argument of the grouped GEMM: return the output rows to their sources from the epilogue."""
         heap = self.heap if direction == 0 else self.bwd_heap
         off = self.off_ret_y if direction == 0 else self.off_ret_dx
         return ([heap.peer_base, self.heap.peer_base, counts, done],
-                [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq])
+                [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq, self.copies])
 
     def fuse_combine(self) -> bool:
         """Whether the kernel's segment tables can hold this workspace's (expert, rank) pairs."""
@@ -191,6 +196,10 @@ class EpWorkspace:
         if seq > self.released_seq:
             ext().ep_set_flag(self.flags(self.off_free, 1), seq)
             self.released_seq = seq
+
+    def close(self) -> None:
+        """Unmap the peers' views of this workspace's own heap (the shared backward heap stays)."""
+        self.heap.close()
 
     def begin_use(self, seq: int) -> None:
         """Called at the start of use ``seq`` of the forward receive buffer.
@@ -246,6 +255,14 @@ class _FusedExpertParallel(torch.autograd.Function):
     @staticmethod
     def backward(ctx: Any, dout):
         ws, seq, top_k = ctx.ws, ctx.seq, ctx.top_k
+        if seq != ws.seq:
+            # A newer forward has reused this workspace: its receive buffers and flags no longer
+            # belong to this call, and running on would silently produce wrong gradients.
+            raise RuntimeError(
+                f'fused expert parallelism: backward of use {seq} of a layer workspace after use {ws.seq} '
+                'started.  Several forwards of one layer are in flight (pipeline schedule, '
+                'forward-forward-backward-backward accumulation, retain_graph): raise '
+                'Arguments.ep_inflight_microbatches to their number or set ep_fused_comm=False.')
         saved = list(ctx.saved_tensors)
         expert_weights, w1, w2, indices, bin_ids, bins, counts, recv_bins, z1, done_push, done_ret = saved[:11]
         v1 = z2 = None

@@ -187,6 +187,70 @@ print('PAIR-OK')
     assert res.returncode == 0 and 'PAIR-OK' in res.stdout, res.stderr[-2000:]
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize('z,rows,m,n', [(1, 64, 256, 256), (3, 1000, 320, 256), (5, 3000, 768, 512),
+                                        (8, 8192, 3072, 768), (6, 200, 128, 384), (64, 4096, 256, 1024)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_cta_pair_weight_gradient(z, rows, m, n, dtype):
+    """TN (ragged-K) layout on CTA pairs against per-group fp32 products; some groups are empty."""
+    from megablocks_b200.utils import status
+    torch.manual_seed(z * 1000 + rows)
+    idx = torch.randint(0, z, (rows,))
+    if z > 2:
+        idx[idx == 1] = 0                       # an empty group in the middle
+    if z > 3:
+        idx[idx == z - 1] = z - 2               # and an empty last group
+    counts = torch.bincount(idx, minlength=z)
+    bins = torch.cumsum(counts, 0).int().cuda()
+    # Rows past the last group exist in the buffers and hold NaN: they must not contribute.
+    a = torch.full((rows + 70, m), float('nan'), dtype=dtype, device='cuda')
+    b = torch.full((rows + 70, n), float('nan'), dtype=dtype, device='cuda')
+    a[:rows] = (torch.randn(rows, m) * 0.5).to(dtype)
+    b[:rows] = (torch.randn(rows, n) * 0.5).to(dtype)
+    out, _, _ = G.grouped_gemm(a, b, bins, trans_a=True, num_groups=z, alpha=0.5, pair=1)
+    single, _, _ = G.grouped_gemm(a, b, bins, trans_a=True, num_groups=z, alpha=0.5, pair=0)
+    ref, start = [], 0
+    for c in counts.tolist():
+        ref.append(a[start:start + c].float().cpu().t() @ b[start:start + c].float().cpu() * 0.5)
+        start += c
+    ref = torch.stack(ref)
+    status.check()
+    _close(out, ref, dtype)
+    _close(single, ref, dtype)
+
+
+@pytest.mark.gpu
+def test_cta_pair_short_groups():
+    """Pair tiles whose second half holds no rows of the group (its A tile is not loaded)."""
+    from megablocks_b200.utils import status
+    torch.manual_seed(5)
+    counts = torch.tensor([100, 0, 300, 129, 128, 1, 512, 257])
+    z, m, k, n = counts.numel(), int(counts.sum()), 256, 512
+    bins = torch.cumsum(counts, 0).int().cuda()
+    a = (torch.randn(m, k) * 0.5).bfloat16().cuda()
+    for trans_b in (True, False):
+        b = (torch.randn(z, n, k) if trans_b else torch.randn(z, k, n)).mul(0.1).bfloat16().cuda()
+        out, _, _ = G.grouped_gemm(a, b, bins, trans_b=trans_b, pair=1)
+        status.check()
+        _close(out, _ref_gmm(a.cpu(), b.cpu(), counts, trans_b), torch.bfloat16)
+
+
+@pytest.mark.gpu
+def test_bins_outside_the_operand_are_clamped():
+    """Group ends beyond the row count (or decreasing) never make the kernel touch rows that do not exist."""
+    from megablocks_b200.utils import status
+    a = (torch.randn(256, 128) * 0.5).bfloat16().cuda()
+    w = (torch.randn(3, 128, 128) * 0.1).bfloat16().cuda()
+    guard = torch.zeros(4096, 128, dtype=torch.bfloat16, device='cuda')
+    c = guard[:256]
+    bins = torch.tensor([128, 64, 100000], dtype=torch.int32, device='cuda')     # treated as [128, 128, 256]
+    G.grouped_gemm(a, w, bins, trans_b=True, c=c)
+    status.check()
+    assert not guard[256:].any()
+    ref = torch.cat([a[:128].float() @ w[0].float().t(), a[128:].float() @ w[2].float().t()])
+    _close(c, ref, torch.bfloat16)
+
+
 @pytest.mark.parametrize('device', DEVICES)
 def test_alpha_scales_the_accumulators(device):
     """``alpha`` multiplies the product before the epilogue: NT output and TN (ragged-K) weight gradient."""
