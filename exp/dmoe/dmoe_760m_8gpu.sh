@@ -1,8 +1,8 @@
 #!/bin/bash
-# Dropless MoE, 760m backbone, 8 GPUs
-# Counterpart of the reference's exp/dmoe/dmoe_760m_8gpu.sh: same model, batch (512 x 1024 tokens per
-# step on 8 GPUs), optimizer and schedule, run by this library's own trainer on
-# synthetic tokens (no dataset is needed).
+# Dropless MoE, 760m backbone, 8 GPUs, fp16, adafactor
+# Counterpart of the reference's exp/dmoe/dmoe_760m_8gpu.sh: same model, global batch (512 x 1024
+# tokens per optimizer step, reached with gradient accumulation), precision, optimizer and
+# schedule, run by this library's own trainer on synthetic tokens (no dataset is needed).
 #
 #   bash exp/dmoe/dmoe_760m_8gpu.sh [steps] [experts] [top_k] [loss_weight] [micro_batch]
 set -e
@@ -15,4 +15,5 @@ GPUS=${GPUS:-8}
 cd "$(dirname "$0")/../.."
 python -m torch.distributed.run --nnodes=1 --nproc-per-node "$GPUS" --master-addr 127.0.0.1 --master-port 29500 \
     -m megablocks_b200.train --preset dmoe-760m --steps "$STEPS" --experts "$EXPERTS" --top-k "$TOP_K" \
-    --loss-weight "$LOSS_WEIGHT" --micro-batch "$MICRO_BATCH" --lr 4e-4 --min-lr 4e-5 "${@:6}"
+    --loss-weight "$LOSS_WEIGHT" --micro-batch "$MICRO_BATCH" --global-batch 512 --precision fp16 \
+    --optimizer adafactor --lr 4e-4 --min-lr 4e-5 --init-std 0.01 "${@:6}"

@@ -596,19 +596,14 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   if (out_numel == 0) return {c, out2, out3};
 
   const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
-  // CTA pairs (256-row tiles, six 32 KB stages per CTA) hide more load latency but waste up to
-  // 255 rows per group; measured, they win once groups are a few thousand rows long and the
-  // contraction is deep enough for the mainloop, not the epilogue, to set the pace.
-  // pair_mode: -1 = decide here, 0 = never, 1 = whenever the kernel supports the problem.
-  const int64_t rows_expected = rows_hint > 0 ? rows_hint : a.size(0);
-  bool pair = block_n == 256 && sm_count() >= 2 && !scatter.has_value();
-  if (pair_mode == 0) pair = false;
-  else if (pair_mode < 0) {
-    // NT / NN: long groups and a deep contraction.  TN (weight gradients): M and N are fixed, so
-    // 256-row tiles lose nothing to group quantisation; taken when the output has whole pair tiles.
-    if (layout == kTN) pair = pair && p.M >= 256 && rows_expected / num_groups >= 256;
-    else pair = pair && rows_expected / num_groups >= 2048 && p.K >= 2048;
-  }
+  // CTA pairs (cta_group::2, 256-row tiles, six 32 KB stages per CTA) pull a third less operand
+  // traffic through L2, but measured back to back against the single-CTA kernel (alternating
+  // launches, L2 flushed, medians) they are 0-8 % slower on every shape tried, from 64 ragged groups
+  // of 512 rows to 8 groups of 4096 rows with a 14336-deep contraction, in all three layouts.  They
+  // are therefore only taken on request.  pair_mode: 1 = whenever the kernel supports the problem,
+  // anything else = never.
+  (void)rows_hint;
+  const bool pair = pair_mode == 1 && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
   if (!scatter.has_value() && store_tma_enabled()) {
     // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
     const int64_t out_rows = out_numel / p.N;

@@ -12,12 +12,19 @@ from typing import Any, List, Optional
 import torch
 import torch.distributed as dist
 
+from megablocks_b200.utils.metrics import comm_timer
+
 
 def _exchange(x, out_splits, in_splits, group, async_op):
     out = torch.empty((sum(out_splits),) + tuple(x.shape[1:]), device=x.device, dtype=x.dtype)
-    handle = dist.all_to_all_single(out, x.contiguous(), output_split_sizes=out_splits,
-                                    input_split_sizes=in_splits, group=group, async_op=async_op)
-    return out, handle
+    x = x.contiguous()
+    if async_op:    # the caller's wait() is the exposed part and is timed there
+        handle = dist.all_to_all_single(out, x, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                                        group=group, async_op=True)
+        return out, handle
+    with comm_timer.region():
+        dist.all_to_all_single(out, x, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+    return out, None
 
 
 class AllToAllOp(torch.autograd.Function):

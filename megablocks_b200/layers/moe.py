@@ -27,6 +27,7 @@ from megablocks_b200 import ops
 from megablocks_b200.layers import common, mlp, mpu, router, sharedexpert_registry
 from megablocks_b200.layers.all_to_all import all_to_all
 from megablocks_b200.layers.arguments import Arguments
+from megablocks_b200.utils.metrics import comm_timer, nvtx_range
 
 _LOAD_BALANCING_LOSS = []
 
@@ -177,7 +178,8 @@ class ParallelMLP(torch.nn.Module):
         x = ops.gather(x, indices, bin_ids, bins, self.top_k)
 
         with torch.no_grad():
-            count_handle.wait()
+            with comm_timer.region():
+                count_handle.wait()
             send_tpe = send_tpe.view(world, epr)
             recv_tpe = recv_tpe.view(world, epr)
             recv_tpe_host = recv_tpe.cpu()
@@ -203,7 +205,8 @@ class ParallelMLP(torch.nn.Module):
                 capacity = int(torch.max(parallel_tpe).item())
 
         if x_handle is not None:
-            x_handle.wait()
+            with comm_timer.region():
+                x_handle.wait()
         parallel_x = self.permute_and_compute(parallel_x, parallel_tpe, parallel_indices, parallel_bin_ids, None,
                                               parallel_bins, capacity, top_k=1)
         x, _ = all_to_all(parallel_x, send_counts, recv_counts, group)
@@ -215,6 +218,7 @@ class ParallelMLP(torch.nn.Module):
                 top_experts: torch.Tensor):
         in_shape = x.size()
         x, tokens_per_expert = self.forward_fn(x, expert_weights, top_experts)
+        self.last_tokens_per_expert = tokens_per_expert      # device tensor, for load statistics in logs
         if self.training and self.args.moe_loss_weight > 0:
             save_load_balancing_loss((tokens_per_expert, scores))
         x = x.view(in_shape)
@@ -242,8 +246,10 @@ class MoE(torch.nn.Module):
     def forward(self, x: torch.Tensor):
         # Cast before the permutation: half the bytes to move.
         x = common.cast_if_autocast_enabled(x)
-        scores, expert_weights, top_experts = self.router(x)
-        out = self.experts(x, scores, expert_weights, top_experts)
+        with nvtx_range('moe.router'):
+            scores, expert_weights, top_experts = self.router(x)
+        with nvtx_range('moe.experts'):
+            out = self.experts(x, scores, expert_weights, top_experts)
         if self.shared_expert is not None:
             out = self.shared_expert.add_experts_sharedexpert(self.shared_expert(x), out)
         return out

@@ -56,6 +56,10 @@ class TransformerConfig:
     # expert parallelism
     expert_parallel_group: Optional[object] = None
     ep_fused_comm: Optional[bool] = None
+    ep_inflight_microbatches: int = 1
+    # pipeline parallelism: this process builds stage `pipeline_stage` of `pipeline_stages`
+    pipeline_stages: int = 1
+    pipeline_stage: int = 0
 
     @property
     def kv_heads(self) -> int:
@@ -89,6 +93,8 @@ class TransformerConfig:
             output_layer_init_method=partial(nn.init.normal_, mean=0.0,
                                              std=self.init_std / math.sqrt(2.0 * self.num_layers)),
             ep_fused_comm=self.ep_fused_comm,
+            ep_inflight_microbatches=self.ep_inflight_microbatches,
+            pipeline_model_parallel_size=self.pipeline_stages,
         )
 
 
@@ -100,6 +106,7 @@ PRESETS = {
     'dmoe-125m': dict(num_layers=12, hidden_size=768, num_heads=12, ffn_hidden_size=3072),
     'dmoe-356m': dict(num_layers=24, hidden_size=1024, num_heads=16, ffn_hidden_size=4096),
     'dmoe-760m': dict(num_layers=24, hidden_size=1536, num_heads=16, ffn_hidden_size=6144),
+    'dmoe-1315m': dict(num_layers=24, hidden_size=2048, num_heads=16, ffn_hidden_size=8192),
     'mixtral-8x7b': dict(flavour='mixtral', vocab_size=32000, max_seq_len=4096, num_layers=32, hidden_size=4096,
                          num_heads=32, num_kv_heads=8, ffn_hidden_size=14336, moe_num_experts=8, moe_top_k=2,
                          rope_theta=1e6),
@@ -210,19 +217,30 @@ class MoETransformer(nn.Module):
         self.cfg = cfg
         self.moe_args = cfg.moe_arguments()
         kw = dict(device=cfg.device, dtype=cfg.dtype)
-        self.wte = nn.Embedding(cfg.vocab_size, cfg.hidden_size, **kw)
-        nn.init.normal_(self.wte.weight, std=cfg.init_std)
-        self.wpe = None
-        if cfg.flavour == 'gpt2':
-            self.wpe = nn.Embedding(cfg.max_seq_len, cfg.hidden_size, **kw)
-            nn.init.normal_(self.wpe.weight, std=cfg.init_std)
-        self.blocks = nn.ModuleList([Block(cfg, self.moe_args) for _ in range(cfg.num_layers)])
+        # A pipeline stage owns a contiguous slice of the blocks; the first stage also owns the
+        # embeddings, the last one the final norm and the LM head (which is then a matrix of its
+        # own: the tied GPT-2 head would need the embedding of another process).
+        from megablocks_b200.parallel.pipeline import stage_layers
+        if cfg.pipeline_stages > 1 and cfg.num_layers % cfg.pipeline_stages:
+            raise ValueError('num_layers must be divisible by pipeline_stages (the load-balancing loss expects '
+                             'num_layers / pipeline_stages terms per stage)')
+        self.is_first_stage = cfg.pipeline_stage == 0
+        self.is_last_stage = cfg.pipeline_stage == cfg.pipeline_stages - 1
+        self.wte = self.wpe = self.ln_f = self.lm_head = None
+        if self.is_first_stage:
+            self.wte = nn.Embedding(cfg.vocab_size, cfg.hidden_size, **kw)
+            nn.init.normal_(self.wte.weight, std=cfg.init_std)
+            if cfg.flavour == 'gpt2':
+                self.wpe = nn.Embedding(cfg.max_seq_len, cfg.hidden_size, **kw)
+                nn.init.normal_(self.wpe.weight, std=cfg.init_std)
+        layers = stage_layers(cfg.num_layers, cfg.pipeline_stages, cfg.pipeline_stage)
+        self.blocks = nn.ModuleList([Block(cfg, self.moe_args) for _ in layers])
         norm = RMSNorm if cfg.flavour == 'mixtral' else fused.LayerNorm
-        self.ln_f = norm(cfg.hidden_size, **kw)
-        self.lm_head = None
-        if cfg.flavour == 'mixtral':
-            self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, **kw)
-            nn.init.normal_(self.lm_head.weight, std=cfg.init_std)
+        if self.is_last_stage:
+            self.ln_f = norm(cfg.hidden_size, **kw)
+            if cfg.flavour == 'mixtral' or not self.is_first_stage:
+                self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, **kw)
+                nn.init.normal_(self.lm_head.weight, std=cfg.init_std)
         self._rope = None
 
     def _rope_for(self, seq: int, device):
@@ -233,19 +251,53 @@ class MoETransformer(nn.Module):
             self._rope = _rope_tables(max(seq, self.cfg.max_seq_len), head_dim, self.cfg.rope_theta, device)
         return self._rope[0][:seq], self._rope[1][:seq]
 
-    def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
-        b, s = tokens.shape
+    def _embed(self, tokens: torch.Tensor) -> torch.Tensor:
         x = self.wte(tokens)
         if self.wpe is not None:
-            x = x + self.wpe(torch.arange(s, device=tokens.device))
-        rope = self._rope_for(s, tokens.device)
+            x = x + self.wpe(torch.arange(tokens.shape[1], device=tokens.device))
+        return x
+
+    def _run_blocks(self, x: torch.Tensor):
+        """Residual stream through this process's blocks; returns ``(x, delta)`` with the last
+        block's output still to be added."""
+        rope = self._rope_for(x.shape[1], x.device)
         delta = None
         for block in self.blocks:
             if self.cfg.activation_checkpointing and self.training:
                 x, delta = checkpoint(block, x, delta, rope, use_reentrant=False)
             else:
                 x, delta = block(x, delta, rope)
+        return x, delta
+
+    def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
+        x, delta = self._run_blocks(self._embed(tokens))
         return _add_norm(self.ln_f, x, delta)[1]
+
+    def _aux_loss(self):
+        """This stage's auxiliary losses of the forward pass just run (``None`` when there are none);
+        clears the per-step accumulators."""
+        aux = None
+        if self.training and self.moe_args.moe_loss_weight > 0:
+            aux = batched_load_balancing_loss(self.moe_args)
+        if self.training and self.moe_args.moe_zloss_weight > 0:
+            z = batched_router_zloss(self.moe_args).sum()
+            aux = z if aux is None else aux + z
+        clear_load_balancing_loss()
+        clear_router_zloss()
+        return aux
+
+    # -- pipeline stages ---------------------------------------------------------------
+    def stage_forward(self, inp: torch.Tensor):
+        """One pipeline stage: token ids (first stage) or the previous stage's activations in,
+        ``(activations for the next stage, auxiliary loss of this stage or None)`` out.  The last
+        stage returns the un-normalised residual stream for :meth:`stage_loss`."""
+        x, delta = self._run_blocks(self._embed(inp) if self.is_first_stage else inp)
+        return (x if delta is None else x + delta), self._aux_loss()
+
+    def stage_loss(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Last stage: final norm, LM head and cross entropy."""
+        logits = self.logits(self.ln_f(hidden))
+        return fused.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         weight = self.lm_head.weight if self.lm_head is not None else self.wte.weight
@@ -259,16 +311,13 @@ class MoETransformer(nn.Module):
 
         Returns ``(total, lm_loss)``.  Clears the per-step loss accumulators.
         """
+        if self.cfg.pipeline_stages > 1:
+            raise RuntimeError('a pipeline stage is driven through stage_forward / stage_loss')
         hidden = self.hidden_states(tokens)
         logits = self.logits(hidden)
         lm = fused.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
-        total = lm
-        if self.training and self.moe_args.moe_loss_weight > 0:
-            total = total + batched_load_balancing_loss(self.moe_args)
-        if self.training and self.moe_args.moe_zloss_weight > 0:
-            total = total + batched_router_zloss(self.moe_args).sum()
-        clear_load_balancing_loss()
-        clear_router_zloss()
+        aux = self._aux_loss()
+        total = lm if aux is None else lm + aux
         return total, lm.detach()
 
     def num_parameters(self, only_active: bool = False) -> int:

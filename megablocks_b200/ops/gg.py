@@ -54,9 +54,10 @@ _ACT_NAMES = {
 }
 
 
-# CTA-pair (cta_group::2) kernel selection: -1 = automatic (groups of >= 2048 rows on average),
-# 0 = never, 1 = whenever supported.  Overridable for experiments with MB200_GEMM_PAIR.
-_PAIR_MODE = int(os.environ.get('MB200_GEMM_PAIR', '-1'))
+# CTA-pair (cta_group::2) kernel selection: 1 = whenever supported, anything else = never (the
+# default: measured against the single-CTA kernel it does not win on any shape tried).  Overridable
+# for experiments with MB200_GEMM_PAIR or per call (`pair=`).
+_PAIR_MODE = int(os.environ.get('MB200_GEMM_PAIR', '0'))
 
 
 def activation_id(fn: Optional[Callable]) -> Optional[int]:
@@ -191,7 +192,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     group ``g``, until ``flags[s * stride + g] >= seq`` for every ``s < count``: the
     rows of ``a`` are then being delivered by peer GPUs (expert-parallel dispatch).
     ``rows_hint`` is the expected number of occupied rows when ``a`` is a worst-case sized
-    buffer (it only steers the choice between the single-CTA and the CTA-pair kernel).
+    buffer (kept for kernel-selection heuristics; currently unused).
     ``scatter = ([data_bases, flag_bases, counts, done], [data_off, flag_off, world, rank, experts,
     seq, return_rows])`` (NN layout) stores every output row into the return buffer of the rank it came from
     instead of ``c`` and releases that rank's flag after its last row: the expert-parallel combine

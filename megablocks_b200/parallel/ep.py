@@ -35,6 +35,7 @@ import torch.distributed as dist
 
 from megablocks_b200._ext import ext
 from megablocks_b200.layers.fused_mlp import mlp_backward, mlp_forward
+from megablocks_b200.utils.metrics import comm_timer, nvtx_range
 
 ERR_RETURN_WAIT = 19
 
@@ -224,15 +225,17 @@ class _FusedExpertParallel(torch.autograd.Function):
         ws.begin_use(seq)
         x = x.contiguous()
         tokens = x.shape[0]
-        counts, recv_bins, done = ws.exchange_counts(tpe, seq)
-        ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0])
+        with comm_timer.region(), nvtx_range('ep.dispatch'):
+            counts, recv_bins, done = ws.exchange_counts(tpe, seq)
+            ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0])
         fuse = ws.fuse_combine()
         y, saved = mlp_forward(ws.recv_x, w1, w2, v1, recv_bins, act, keep_h, wait=ws.arrival(0, seq),
                                zero_tail=False, rows_hint=ws.copies,
                                scatter=ws.scatter_args(counts, 0, seq, done[1]) if fuse else None)
-        if not fuse:
-            ws.return_rows(y, counts, 0, seq, done[1])
-        ws.wait_return(0, seq)
+        with comm_timer.region(), nvtx_range('ep.combine_wait'):
+            if not fuse:
+                ws.return_rows(y, counts, 0, seq, done[1])
+            ws.wait_return(0, seq)
         out = ext().scatter_rows(ws.ret_y, indices, bin_ids, expert_weights, bins, bins, top_k, tokens)
         will_backward = torch.is_grad_enabled() and any(
             t is not None and t.requires_grad for t in (x, expert_weights, w1, w2, v1))
@@ -272,7 +275,8 @@ class _FusedExpertParallel(torch.autograd.Function):
         dout = dout.contiguous()
         fuse = ws.fuse_combine()
         # d(out)/d(expert rows): each copy's gradient is its token's gradient times its router weight.
-        ws.push(dout, indices, expert_weights, bins, counts, 1, seq, top_k, done_push)
+        with comm_timer.region(), nvtx_range('ep.dispatch_grad'):
+            ws.push(dout, indices, expert_weights, bins, counts, 1, seq, top_k, done_push)
         dweights = None
         if ctx.needs_input_grad[1]:
             dweights = ext().scatter_wgrad(ws.ret_y, dout, indices, bin_ids, bins, bins, top_k)
@@ -285,10 +289,11 @@ class _FusedExpertParallel(torch.autograd.Function):
                                           wgrad_scale=ctx.wgrad_scale)
         # Every read of both receive buffers is enqueued above; only now may peers learn
         # (through the return flags / the free flag) that they can be overwritten.
-        if not fuse:
-            ws.return_rows(dxr, counts, 1, seq, done_ret)
-        ws.release_receive_buffer(seq)
-        ws.wait_return(1, seq)
+        with comm_timer.region(), nvtx_range('ep.combine_grad_wait'):
+            if not fuse:
+                ws.return_rows(dxr, counts, 1, seq, done_ret)
+            ws.release_receive_buffer(seq)
+            ws.wait_return(1, seq)
         dx = None
         if needs[0]:
             dx = ext().scatter_rows(ws.ret_dx, indices, bin_ids, None, bins, bins, top_k, ctx.tokens)

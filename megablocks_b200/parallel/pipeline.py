@@ -26,6 +26,7 @@ def stage_layers(num_layers: int, num_stages: int, stage: int) -> range:
 class PipelineStage:
 
     def __init__(self, group: Optional[dist.ProcessGroup], shape: Sequence[int], dtype: torch.dtype, device):
+        """``shape`` / ``dtype``: the activations that cross a stage boundary (one micro-batch)."""
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -59,33 +60,44 @@ class PipelineStage:
                 work.wait()
         return from_prev, from_next
 
-    def forward_backward(self, blocks: torch.nn.Module, micro_batches: Sequence[torch.Tensor], loss_fn=None):
+    def forward_backward(self, run_stage, num_micro_batches: int, loss_fn=None, scale: float = 1.0):
         """GPipe-style schedule: all forwards, then all backwards, activations kept per micro-batch.
 
-        ``blocks(x)`` maps the stage input to its output; the first stage receives the
-        elements of ``micro_batches`` itself, the last stage applies ``loss_fn(output)``
-        and returns the list of losses.
+        ``run_stage(x, i)`` maps the stage input of micro-batch ``i`` (``None`` on the first stage,
+        which fetches its own tokens) to ``(output, auxiliary loss or None)``; the auxiliary loss
+        (this stage's load-balancing terms) is back-propagated together with the gradient that
+        arrives from the next stage.  The last stage applies ``loss_fn(output, i)``.  Everything
+        that is back-propagated is multiplied by ``scale`` (1 / micro-batches, loss scaling).
+        Returns the last stage's list of losses (empty elsewhere).
         """
-        inputs, outputs, losses = [], [], []
-        for mb in micro_batches:
-            if self.is_first:
-                x = mb
-            else:
+        inputs, outputs, auxes, losses = [], [], [], []
+        for i in range(num_micro_batches):
+            x = None
+            if not self.is_first:
                 x, _ = self.exchange(recv_prev=True)
                 x.requires_grad_(True)
-            y = blocks(x)
+            y, aux = run_stage(x, i)
             if self.is_last:
-                losses.append(loss_fn(y))
+                losses.append(loss_fn(y, i))
             else:
                 self.exchange(send_next=y.detach())
             inputs.append(x)
             outputs.append(y)
-        for i in reversed(range(len(micro_batches))):
+            auxes.append(aux)
+        for i in reversed(range(num_micro_batches)):
+            roots, grads = [], []
             if self.is_last:
-                losses[i].backward()
+                roots.append(losses[i] * scale)
+                grads.append(None)
             else:
                 _, grad = self.exchange(recv_next=True)
-                outputs[i].backward(grad)
+                roots.append(outputs[i])
+                grads.append(grad)
+            if auxes[i] is not None and torch.is_tensor(auxes[i]) and auxes[i].requires_grad:
+                roots.append(auxes[i] * scale)
+                grads.append(None)
+            torch.autograd.backward(roots, grads)
             if not self.is_first:
                 self.exchange(send_prev=inputs[i].grad)
+            outputs[i] = auxes[i] = None      # free the micro-batch's graph
         return losses

@@ -22,8 +22,9 @@ import torch
 import torch.distributed as dist
 
 from megablocks_b200.layers import mpu
-from megablocks_b200.optim import FusedAdam, clip_coefficient, cosine_lr
+from megablocks_b200.optim import Adafactor, DynamicLossScaler, FusedAdam, clip_coefficient, cosine_lr
 from megablocks_b200.parallel.dp import FlatBuffer, GradReducer
+from megablocks_b200.utils.metrics import nvtx_range
 
 
 @dataclasses.dataclass
@@ -44,12 +45,26 @@ class TrainerConfig:
     # CUDA only.  Off by default: measured on B200 with the 125M dMoE it changes nothing, because
     # the forward's persistent GEMM CTAs occupy whole SMs and the update runs between them anyway.
     overlap_expert_update: bool = False
+    # One optimizer step covers `grad_accum_steps` micro-batches: `step` splits its batch along
+    # dimension 0, the gradients add up in place and the data-parallel reduction starts during the
+    # backward pass of the last micro-batch only (the reference's recipes: global batch 512 on
+    # 8 GPUs x micro-batch 32 = 2 micro-batches per step, exp/dmoe/dmoe_125m_8gpu.sh:5-9,63).
+    grad_accum_steps: int = 1
+    optimizer: str = 'adam'          # 'adam' | 'adafactor' (exp/dmoe/dmoe_760m_8gpu.sh)
+    # fp16 parameters train under dynamic loss scaling (None = on exactly when the model is fp16).
+    loss_scaling: Optional[bool] = None
+    init_loss_scale: float = 2.0**16
+    loss_scale_window: int = 1000
 
 
 class Trainer:
 
-    def __init__(self, model: torch.nn.Module, cfg: TrainerConfig, dp_group: Optional[dist.ProcessGroup] = None):
-        self.model, self.cfg, self.dp_group = model, cfg, dp_group
+    def __init__(self, model: torch.nn.Module, cfg: TrainerConfig, dp_group: Optional[dist.ProcessGroup] = None,
+                 pipeline=None):
+        """``pipeline``: a :class:`megablocks_b200.parallel.pipeline.PipelineStage` when ``model`` is one
+        stage of a pipeline (``TransformerConfig.pipeline_stages > 1``); ``dp_group`` then spans the
+        replicas of this stage only."""
+        self.model, self.cfg, self.dp_group, self.pipeline = model, cfg, dp_group, pipeline
         self.world = dist.get_world_size(dp_group) if (dist.is_initialized() and dp_group is not None) else 1
         params = [p for p in model.parameters() if p.requires_grad]
         # "Expert" parameters are the ones no other rank holds a replica of: the expert-parallel shards,
@@ -69,7 +84,17 @@ class Trainer:
         if self.expert_params:
             self._plan_expert_update_groups(cfg.overlap_expert_update and self.device.type == 'cuda')
         self.flat = self.reducer = None
-        kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
+        if cfg.optimizer == 'adafactor':
+            opt_cls, kw = Adafactor, dict(lr=cfg.lr, weight_decay=cfg.weight_decay)
+        elif cfg.optimizer == 'adam':
+            opt_cls, kw = FusedAdam, dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
+        else:
+            raise ValueError(f"optimizer must be 'adam' or 'adafactor', got {cfg.optimizer!r}")
+        if cfg.optimizer != 'adam' and self._update_stream is not None:
+            raise ValueError('overlap_expert_update needs the fused Adam optimizer')
+        scaling = cfg.loss_scaling if cfg.loss_scaling is not None else params[0].dtype == torch.float16
+        self.scaler = DynamicLossScaler(cfg.init_loss_scale, growth_interval=cfg.loss_scale_window) if scaling \
+            else None
         if self.world > 1:
             self.flat = FlatBuffer(self.dense_params, granule=self.world * 8)
             self.reducer = GradReducer(self.flat, dp_group, cfg.bucket_mb << 20, shard=cfg.zero1)
@@ -80,12 +105,12 @@ class Trainer:
                 lo, hi = self.reducer.shard_range(bi)
                 self._shard_params.append(self.flat.param[lo:hi])
                 self._shard_grads.append(self.flat.grad[lo:hi])
-            self.dense_opt = FusedAdam(self._shard_params, **kw)
+            self.dense_opt = opt_cls(self._shard_params, **kw)
         else:
             # Replicated tensors: count their norm once across the group.
-            self.dense_opt = FusedAdam(self.dense_params, norm_weights=[1.0 / self.world] * len(self.dense_params),
-                                       **kw)
-        self.expert_opt = FusedAdam(self.expert_params, **kw)
+            self.dense_opt = opt_cls(self.dense_params, norm_weights=[1.0 / self.world] * len(self.dense_params),
+                                     **kw)
+        self.expert_opt = opt_cls(self.expert_params, **kw)
         self._sqnorm = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.step_count = 0
         self.last_grad_norm = None
@@ -159,35 +184,110 @@ class Trainer:
         for p in self.expert_params:
             p.grad = None
 
+    def _forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """All micro-batches of one step; returns the mean language-model loss (device scalar)."""
+        n = max(1, int(self.cfg.grad_accum_steps))
+        scale = (self.scaler.scale if self.scaler is not None else 1.0) / n
+        if self.pipeline is not None:
+            return self._pipeline_forward_backward(tokens, targets, n, scale)
+        if n == 1:
+            with nvtx_range('forward'):
+                total, lm = self.model.loss(tokens, targets)
+            with nvtx_range('backward'):
+                (total if scale == 1.0 else total * scale).backward()
+            return lm
+        if tokens.shape[0] % n:
+            raise ValueError(f'batch of {tokens.shape[0]} rows does not split into {n} micro-batches')
+        lm_sum = None
+        for i, (tok, tgt) in enumerate(zip(tokens.chunk(n), targets.chunk(n))):
+            if self.reducer is not None:
+                self.reducer.active = i == n - 1
+            with nvtx_range('forward'):
+                total, lm = self.model.loss(tok, tgt)
+            with nvtx_range('backward'):
+                (total * scale).backward()
+            lm_sum = lm if lm_sum is None else lm_sum + lm
+        if self.reducer is not None:
+            self.reducer.active = True
+        return lm_sum / n
+
+    def _pipeline_forward_backward(self, tokens, targets, n: int, scale: float) -> torch.Tensor:
+        """One step of a pipeline stage: ``n`` micro-batches through ``PipelineStage.forward_backward``.
+
+        Every stage gets the same ``tokens`` / ``targets`` (the first uses the tokens, the last the
+        targets).  Each micro-batch adds this stage's own load-balancing terms to what it
+        back-propagates, which is why a stage must have collected exactly ``num_layers /
+        pipeline stages`` of them (the rule megablocks/layers/moe.py:39-60 checks).
+        """
+        stage = self.pipeline
+        if tokens.shape[0] % n:
+            raise ValueError(f'batch of {tokens.shape[0]} rows does not split into {n} micro-batches')
+        tok_chunks, tgt_chunks = tokens.chunk(n), targets.chunk(n)
+        lm_values = []
+
+        def run_stage(x, index):
+            return self.model.stage_forward(tok_chunks[index] if stage.is_first else x)
+
+        def loss_fn(hidden, index):
+            lm = self.model.stage_loss(hidden, tgt_chunks[index])
+            lm_values.append(lm.detach())
+            return lm
+
+        if self.reducer is not None:
+            self.reducer.active = False      # the schedule interleaves micro-batches: reduce once, at the end
+        stage.forward_backward(run_stage, n, loss_fn, scale=scale)
+        if self.reducer is not None:
+            self.reducer.active = True
+        if lm_values:
+            return torch.stack(lm_values).mean()
+        return torch.zeros((), device=self.device)
+
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Forward, backward, gradient reduction, clipping and the optimizer update.
 
-        Returns the language-model loss as a device scalar (no host sync).
+        ``tokens`` / ``targets`` hold this rank's whole share of the step: ``grad_accum_steps``
+        micro-batches stacked along dimension 0.  Returns the language-model loss as a device
+        scalar (no host sync, except under fp16 loss scaling, which reads one overflow flag).
         """
         cfg = self.cfg
         self.model.train()
         self._zero_grad()
-        total, lm = self.model.loss(tokens, targets)
-        total.backward()
-        if self.reducer is not None:
-            self.reducer.finish()
+        lm = self._forward_backward(tokens, targets)
+        with nvtx_range('grad_reduce_wait'):
+            if self.reducer is not None:
+                self.reducer.finish()
         lr = cosine_lr(self.step_count, cfg.total_steps, cfg.lr, cfg.min_lr, cfg.warmup_fraction) if cfg.schedule \
             else cfg.lr
         self.dense_opt.lr = self.expert_opt.lr = lr
 
         dense_grads = self._shard_grads if (self.world > 1 and cfg.zero1) else None
         self.flush()   # a layer that did not run this step may still have an update in flight
-        self._sqnorm.zero_()
-        self.dense_opt.add_sqnorm(self._sqnorm, dense_grads)
-        self.expert_opt.add_sqnorm(self._sqnorm)
-        if self.world > 1:
-            dist.all_reduce(self._sqnorm, group=self.dp_group)
-        coeff = clip_coefficient(self._sqnorm, cfg.max_grad_norm)
+        with nvtx_range('grad_norm'):
+            self._sqnorm.zero_()
+            self.dense_opt.add_sqnorm(self._sqnorm, dense_grads)
+            self.expert_opt.add_sqnorm(self._sqnorm)
+            if self.world > 1:
+                dist.all_reduce(self._sqnorm, group=self.dp_group)
+            if self.pipeline is not None and self.pipeline.world > 1:
+                dist.all_reduce(self._sqnorm, group=self.pipeline.group)
+        extra = 1.0
+        if self.scaler is not None:
+            # The squared norm was summed over every rank, so all ranks take the same decision.
+            overflow = not bool(torch.isfinite(self._sqnorm).all().item())
+            scale = self.scaler.scale
+            self.scaler.update(overflow)
+            if overflow:          # skip the update; the next step retries with a smaller scale
+                self.last_grad_norm = self._sqnorm.sqrt()
+                return lm
+            self._sqnorm.div_(scale * scale)
+            extra = 1.0 / scale
+        coeff = clip_coefficient(self._sqnorm, cfg.max_grad_norm, extra)
         self.last_grad_norm = coeff[1:2]
-        self.dense_opt.step(coeff[0:1], dense_grads)
-        self._step_experts(coeff[0:1])
-        if self.world > 1 and cfg.zero1:
-            self.reducer.gather_params()
+        with nvtx_range('optimizer'):
+            self.dense_opt.step(coeff[0:1], dense_grads)
+            self._step_experts(coeff[0:1])
+            if self.world > 1 and cfg.zero1:
+                self.reducer.gather_params()
         self.step_count += 1
         return lm
 
@@ -204,8 +304,11 @@ class Trainer:
 
     def state_dict(self):
         self.flush()
-        return {'model': self.model.state_dict(), 'dense_opt': self.dense_opt.state_dict(),
-                'expert_opt': self.expert_opt.state_dict(), 'step': self.step_count}
+        state = {'model': self.model.state_dict(), 'dense_opt': self.dense_opt.state_dict(),
+                 'expert_opt': self.expert_opt.state_dict(), 'step': self.step_count}
+        if self.scaler is not None:
+            state['loss_scaler'] = self.scaler.state_dict()
+        return state
 
     def load_state_dict(self, state):
         self.flush()
@@ -213,6 +316,8 @@ class Trainer:
         self.dense_opt.load_state_dict(state['dense_opt'])
         self.expert_opt.load_state_dict(state['expert_opt'])
         self.step_count = int(state['step'])
+        if self.scaler is not None and 'loss_scaler' in state:
+            self.scaler.load_state_dict(state['loss_scaler'])
 
 
 def synthetic_batch(micro_batch: int, seq_len: int, vocab_size: int, generator: Optional[torch.Generator] = None,
@@ -233,11 +338,21 @@ def main(argv=None):
     from megablocks_b200.models.transformer import MoETransformer, PRESETS, preset
     from megablocks_b200.utils import status
     from megablocks_b200.utils.health import Heartbeat
-    from megablocks_b200.utils.metrics import JsonlLogger, expert_load_stats, nvtx_range
+    from megablocks_b200.layers.moe import ParallelMLP
+    from megablocks_b200.parallel.pipeline import PipelineStage
+    from megablocks_b200.utils.metrics import JsonlLogger, expert_load_stats
 
     ap = argparse.ArgumentParser(description='Train a dMoE / MoE transformer on synthetic tokens.')
     ap.add_argument('--preset', choices=sorted(PRESETS), default='dmoe-125m')
     ap.add_argument('--micro-batch', type=int, default=32)
+    ap.add_argument('--global-batch', type=int, default=None,
+                    help='sequences per optimizer step over all data-parallel ranks; the step then runs '
+                         'global / (micro x data-parallel ranks) micro-batches with gradient accumulation')
+    ap.add_argument('--precision', choices=['bf16', 'fp16'], default='bf16',
+                    help='fp16 trains under dynamic loss scaling')
+    ap.add_argument('--optimizer', choices=['adam', 'adafactor'], default='adam')
+    ap.add_argument('--pp', type=int, default=1, help='pipeline stages (ranks are split stage-major)')
+    ap.add_argument('--init-std', type=float, default=None)
     ap.add_argument('--steps', type=int, default=100)
     ap.add_argument('--experts', type=int, default=None)
     ap.add_argument('--top-k', type=int, default=None)
@@ -267,17 +382,42 @@ def main(argv=None):
     if use_cuda:
         torch.cuda.set_device(local)
     group = None
+    pp = max(1, args.pp)
+    if world % pp:
+        raise SystemExit(f'--pp {pp} does not divide the {world} ranks')
+    dp_world = world // pp            # ranks per stage: data parallel for dense, expert parallel for MoE weights
+    stage_index, stage_rank = rank // dp_world, rank % dp_world
+    pp_group = None
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         os.environ.setdefault('MASTER_PORT', '29500')
         dist.init_process_group('nccl' if use_cuda else 'gloo', rank=rank, world_size=world)
         group = dist.group.WORLD
+        if pp > 1:
+            # Every rank creates every group, in the same order.
+            stage_groups = [dist.new_group(list(range(s * dp_world, (s + 1) * dp_world))) for s in range(pp)]
+            chain_groups = [dist.new_group([s * dp_world + r for s in range(pp)]) for r in range(dp_world)]
+            group = stage_groups[stage_index] if dp_world > 1 else None
+            pp_group = chain_groups[stage_rank]
 
     torch.manual_seed(args.seed)
     overrides = dict(device=device, expert_parallel_group=group, mlp_impl=args.mlp_impl,
                      moe_loss_weight=args.loss_weight, activation_checkpointing=args.recompute,
                      ep_fused_comm={'auto': None, 'fused': True, 'nccl': False}[args.ep_comm],
-                     dtype=torch.bfloat16 if use_cuda else torch.float32)
+                     dtype=(torch.float16 if args.precision == 'fp16' else torch.bfloat16) if use_cuda
+                     else torch.float32,
+                     pipeline_stages=pp, pipeline_stage=stage_index)
+    if args.init_std is not None:
+        overrides['init_std'] = args.init_std
+    accum = 1
+    if args.global_batch is not None:
+        per_pass = args.micro_batch * dp_world
+        if args.global_batch % per_pass:
+            raise SystemExit(f'--global-batch {args.global_batch} is not a multiple of micro-batch x '
+                             f'data-parallel ranks = {per_pass}')
+        accum = args.global_batch // per_pass
+    if pp > 1:
+        overrides['ep_inflight_microbatches'] = accum      # all forwards of a step precede its backwards
     if args.experts is not None:
         overrides['moe_num_experts'] = args.experts
     if args.top_k is not None:
@@ -286,23 +426,32 @@ def main(argv=None):
         overrides.update(dropless=False, moe_capacity_factor=args.capacity_factor)
     cfg = preset(args.preset, **overrides)
     model = MoETransformer(cfg)
+    stage = None
+    if pp > 1:
+        stage = PipelineStage(pp_group, (args.micro_batch, cfg.max_seq_len, cfg.hidden_size), cfg.dtype, device)
     trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1,
-                                           overlap_expert_update=args.defer_expert_update),
-                      dp_group=group)
+                                           overlap_expert_update=args.defer_expert_update,
+                                           grad_accum_steps=accum, optimizer=args.optimizer),
+                      dp_group=group, pipeline=stage)
     if args.load:
         state = checkpoint.load(args.load, rank, world, map_location=device)
         model.load_state_dict(state['model'])
         if 'dense_opt' in state:
             trainer.load_state_dict(state)
-    logger = JsonlLogger(args.log, rank)
+    # The loss lives on the last pipeline stage: its first rank reports.
+    reporter = stage_index == pp - 1 and stage_rank == 0
+    logger = JsonlLogger(args.log, 0 if reporter else 1)
     heartbeat = Heartbeat(timeout_s=60.0) if world > 1 else None
-    gen = torch.Generator().manual_seed(args.seed + rank)
-    tokens_per_step = world * args.micro_batch * cfg.max_seq_len
+    # Ranks of one pipeline chain must draw the same batch (first stage: tokens, last stage: targets).
+    gen = torch.Generator().manual_seed(args.seed + stage_rank)
+    rows = args.micro_batch * accum
+    tokens_per_step = dp_world * rows * cfg.max_seq_len
+    moe_layers = [m for m in model.modules() if isinstance(m, ParallelMLP)]
     t_last, loss = time.time(), None
     for step in range(trainer.step_count, args.steps):
         if heartbeat is not None:
             heartbeat.check()
-        batch = synthetic_batch(args.micro_batch, cfg.max_seq_len, cfg.vocab_size, gen)
+        batch = synthetic_batch(rows, cfg.max_seq_len, cfg.vocab_size, gen)
         with nvtx_range('train_step'):
             dev = batch.to(device, non_blocking=True)
             loss = trainer.step(dev[:, :-1], dev[:, 1:])
@@ -315,9 +464,16 @@ def main(argv=None):
             now = time.time()
             rate = tokens_per_step * args.log_interval / max(now - t_last, 1e-9)
             t_last = now
+            load = {}
+            for i, layer in enumerate(moe_layers):       # per-layer expert load of the last micro-batch
+                tpe = getattr(layer, 'last_tokens_per_expert', None)
+                if tpe is not None:
+                    load[f'layer{i}'] = expert_load_stats(tpe)
             logger.log(step=step + 1, loss=value, grad_norm=trainer.last_grad_norm, tokens_per_s=rate,
-                       lr=trainer.dense_opt.lr)
-            if rank == 0:
+                       lr=trainer.dense_opt.lr, expert_load=load,
+                       loss_scale=trainer.scaler.scale if trainer.scaler is not None else None,
+                       skipped_steps=trainer.scaler.skipped_steps if trainer.scaler is not None else 0)
+            if reporter:
                 print(f'step {step + 1:6d}  loss {value:8.4f}  grad-norm {float(trainer.last_grad_norm):7.3f}  '
                       f'{rate:12.0f} tokens/s', flush=True)
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:

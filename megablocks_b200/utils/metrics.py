@@ -93,3 +93,44 @@ class DeviceTimer:
     def ms(self) -> float:
         self._end.synchronize()
         return self._start.elapsed_time(self._end)
+
+
+class CommTimer:
+    """Device time spent in communication-only work on the compute stream.
+
+    The expert-parallel exchange brackets the kernels (or collectives) that move tokens but compute
+    nothing - count exchange, dispatch push, waits for returned rows, all-to-alls of the library route
+    - with :meth:`region`.  While :attr:`enabled` is false that costs nothing; while it is true every
+    region records two CUDA events on the current stream, and :meth:`total_ms` adds up their
+    distances after one synchronisation.  Because the regions sit on the stream the expert GEMMs
+    wait behind, the sum is the exchange time that is exposed, i.e. not hidden under compute.
+    """
+
+    def __init__(self):
+        self.enabled = False
+        self._pairs = []
+
+    @contextlib.contextmanager
+    def region(self):
+        if not self.enabled or not torch.cuda.is_available():
+            yield
+            return
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        try:
+            yield
+        finally:
+            end.record()
+            self._pairs.append((start, end))
+
+    def reset(self) -> None:
+        self._pairs = []
+
+    def total_ms(self) -> float:
+        if not self._pairs:
+            return 0.0
+        torch.cuda.synchronize()
+        return float(sum(s.elapsed_time(e) for s, e in self._pairs))
+
+
+comm_timer = CommTimer()
