@@ -9,8 +9,9 @@ installed offline; ``baseline/shims`` provides import-level stand-ins for them
 and decorators only).  The surrounding GPT-2 backbone, data-parallel all-reduce and
 mixed-precision Adam are plain PyTorch written here, standing in for the Megatron-LM
 fork the reference's scripts use (exp/dmoe/dmoe_125m_8gpu.sh of the reference): bf16
-parameters, fp32 main parameters, Adam, clip-grad 1.0, local (non-overlapped) DDP.
-Nothing from ``megablocks_b200`` is imported on this path.
+parameters, fp32 main parameters, Adam, clip-grad 1.0, local (non-overlapped) DDP, and the
+cosine schedule with 1 % warm-up of those scripts.  Nothing from ``megablocks_b200`` is imported
+on this path.
 """
 
 import math
@@ -108,11 +109,74 @@ class RefGPT(nn.Module):
         return total, lm.detach()
 
 
+def cosine_lr(step, total_steps, peak, floor, warmup_fraction=0.01):
+    """Linear warm-up, then cosine decay (--lr-decay-style cosine --lr-warmup-fraction 0.01)."""
+    warm = max(1, int(total_steps * warmup_fraction))
+    if step < warm:
+        return peak * (step + 1) / warm
+    frac = min(1.0, (step - warm) / max(1, total_steps - warm))
+    return floor + 0.5 * (peak - floor) * (1.0 + math.cos(math.pi * frac))
+
+
+class ExposedCommTimer:
+    """Times the all-to-alls the reference issues, as seen from the compute stream.
+
+    ``torch.distributed.all_to_all_single`` is wrapped (the reference itself is untouched): a
+    blocking call is bracketed by two CUDA events, an ``async_op`` call returns a handle whose
+    ``wait()`` is bracketed instead - the part of the exchange the compute stream actually waits for.
+    """
+
+    def __init__(self):
+        self.enabled = False
+        self.pairs = []
+        self._orig = dist.all_to_all_single
+        timer = self
+
+        class Handle:
+            def __init__(self, work):
+                self.work = work
+
+            def wait(self, *args, **kwargs):
+                if not timer.enabled:
+                    return self.work.wait(*args, **kwargs)
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                out = self.work.wait(*args, **kwargs)
+                end.record()
+                timer.pairs.append((start, end))
+                return out
+
+            def __getattr__(self, name):
+                return getattr(self.work, name)
+
+        def wrapped(*args, **kwargs):
+            if not timer.enabled:
+                return timer._orig(*args, **kwargs)
+            if kwargs.get('async_op'):
+                return Handle(timer._orig(*args, **kwargs))
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = timer._orig(*args, **kwargs)
+            end.record()
+            timer.pairs.append((start, end))
+            return out
+
+        dist.all_to_all_single = wrapped
+
+    def reset(self):
+        self.pairs = []
+
+    def total_ms(self):
+        torch.cuda.synchronize()
+        return float(sum(s.elapsed_time(e) for s, e in self.pairs))
+
+
 class RefTrainer:
     """bf16 model parameters, fp32 main parameters, Adam, clip-grad 1.0, local DDP."""
 
-    def __init__(self, model, lr=6e-4, world=1, group=None):
+    def __init__(self, model, lr=6e-4, min_lr=6e-5, total_steps=20000, world=1, group=None):
         self.model, self.world, self.group = model, world, group
+        self.lr, self.min_lr, self.total_steps, self.step_count = lr, min_lr, total_steps, 0
         self.params = [p for p in model.parameters() if p.requires_grad]
         self.dense = [p for p in self.params if not getattr(p, 'expert_model_parallel', False)]
         self.main = [p.detach().clone().float().requires_grad_(True) for p in self.params]
@@ -141,6 +205,9 @@ class RefTrainer:
             dist.all_reduce(sq, group=self.group)
         coeff = torch.clamp(1.0 / (sq.sqrt() + 1e-6), max=1.0)
         torch._foreach_mul_([m.grad for m in self.main], coeff)
+        for group in self.opt.param_groups:
+            group['lr'] = cosine_lr(self.step_count, self.total_steps, self.lr, self.min_lr)
+        self.step_count += 1
         self.opt.step()
         with torch.no_grad():
             torch._foreach_copy_(self.params, self.main)

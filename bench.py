@@ -106,8 +106,8 @@ def _dist_setup(n_gpus: int):
     return rank, world, local
 
 
-def _measure(trainer, world, rank, local, steps, warmup, launch_counter):
-    """Returns (device-timed ms/step, e2e ms/step, clocks, launches, h2d bytes, d2h bytes)."""
+def _measure(trainer, world, rank, local, steps, warmup, launch_counter, comm_timer=None):
+    """Returns (device-timed ms/step, e2e ms/step, clocks, launches, h2d bytes, d2h bytes, loss, exposed comm ms)."""
     import torch
     import torch.distributed as dist
 
@@ -162,7 +162,20 @@ def _measure(trainer, world, rank, local, steps, warmup, launch_counter):
     clocks = sampler.stop()
     e2e_ms = max_over_ranks(start2.elapsed_time(end2) / steps)
     h2d = host_batches[0].numel() * host_batches[0].element_size()
-    return device_ms, e2e_ms, clocks, launches, h2d, 4, last
+    # Exposed exchange time (outside both timed regions): device time of the communication-only
+    # pieces of the expert-parallel exchange on the compute stream, per step, max over ranks.
+    exposed = None
+    if comm_timer is not None and world > 1:
+        comm_timer.reset()
+        comm_timer.enabled = True
+        for i in range(steps):
+            b = dev_batches[i % len(dev_batches)]
+            trainer.step(b[:, :-1], b[:, 1:])
+        _flush(trainer)
+        comm_timer.enabled = False
+        exposed = max_over_ranks(comm_timer.total_ms() / steps)
+        comm_timer.reset()
+    return device_ms, e2e_ms, clocks, launches, h2d, 4, last, exposed
 
 
 def _flush(trainer):
@@ -171,7 +184,8 @@ def _flush(trainer):
         flush()
 
 
-def _emit(impl, n_gpus, steps, warmup, device_ms, e2e_ms, clocks, launches, h2d, d2h, loss, extra_config=None):
+def _emit(impl, n_gpus, steps, warmup, device_ms, e2e_ms, clocks, launches, h2d, d2h, loss, exposed,
+          extra_config=None):
     tokens_per_step = n_gpus * MICRO_BATCH * MODEL['seq']
     value = tokens_per_step / (device_ms / 1e3)
     e2e = tokens_per_step / (e2e_ms / 1e3)
@@ -183,6 +197,7 @@ def _emit(impl, n_gpus, steps, warmup, device_ms, e2e_ms, clocks, launches, h2d,
         'l2': 'no flush needed: one step touches tens of GB, far beyond the 126 MB L2',
         'vs_baseline_denominator': 'reference plot-derived 80k tokens/s per A100 GPU x n_gpus',
         'last_loss': loss,
+        'exposed_comm_ms': exposed,
     }
     config.update(extra_config or {})
     line = {
@@ -215,7 +230,8 @@ def run_ours(args):
                  mlp_impl=args.mlp_impl, memory_optimized_mlp=args.memory_optimized_mlp, ep_fused_comm=fused)
     model = MoETransformer(cfg)
     trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000), dp_group=group)
-    out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count)
+    from megablocks_b200.utils.metrics import comm_timer
+    out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count, comm_timer)
     status.check()
     if rank == 0:
         _emit('megablocks_b200', args.gpus, args.steps, args.warmup, *out,
@@ -229,6 +245,7 @@ def run_ours(args):
 
 
 def run_reference(args):
+    os.environ['MB_REF_GMM'] = args.ref_gmm
     try:
         import torch
         import torch.distributed as dist
@@ -245,14 +262,18 @@ def run_reference(args):
     group = dist.group.WORLD if world > 1 else None
     model = ref_arm.RefGPT(MODEL, torch.device('cuda', local), ep_group=group,
                            memory_optimized_mlp=args.memory_optimized_mlp)
-    trainer = ref_arm.RefTrainer(model, world=world, group=group)
-    out = _measure(trainer, world, rank, local, args.steps, args.warmup, lambda: 0)
+    comm_timer = ref_arm.ExposedCommTimer()
+    trainer = ref_arm.RefTrainer(model, lr=6e-4, min_lr=6e-5, total_steps=20000, world=world, group=group)
+    out = _measure(trainer, world, rank, local, args.steps, args.warmup, lambda: 0, comm_timer)
     if rank == 0:
         _emit('reference', args.gpus, args.steps, args.warmup, *out,
               extra_config={'mlp_impl': 'grouped', 'memory_optimized_mlp': args.memory_optimized_mlp,
                             'ep_comm': 'nccl all_to_all' if world > 1 else 'none',
+                            'ref_gmm': args.ref_gmm,
                             'note': 'unmodified reference library from baseline/_ref; grouped_gemm and stk '
-                                    'are import shims (per-expert cuBLAS loop), backbone/optimizer plain PyTorch'})
+                                    'are import shims (grouped_gemm = per-expert cuBLAS loop, or one '
+                                    'torch._grouped_mm launch with --ref-gmm grouped_mm), backbone/optimizer '
+                                    'plain PyTorch'})
     if world > 1:
         dist.destroy_process_group()
 
@@ -266,6 +287,10 @@ def main():
     ap.add_argument('--mlp-impl', dest='mlp_impl', choices=['grouped', 'sparse'], default='grouped')
     ap.add_argument('--ep-comm', dest='ep_comm', choices=['auto', 'fused', 'nccl'], default='auto',
                     help='expert-parallel exchange: peer-memory kernels (auto/fused) or NCCL all-to-all')
+    ap.add_argument('--ref-gmm', dest='ref_gmm', choices=['loop', 'grouped_mm'], default='loop',
+                    help="reference arm only: its grouped_gemm dependency as the package's default per-expert "
+                         'cuBLAS loop, or as one torch._grouped_mm launch per GEMM (the analogue of the '
+                         "package's CUTLASS build)")
     ap.add_argument('--memory-optimized-mlp', dest='memory_optimized_mlp', action='store_true',
                     help='recompute the expert activation in backward (both arms); off, as in the '
                          "reference's Arguments default and its experiment scripts")

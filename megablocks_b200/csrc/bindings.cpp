@@ -63,30 +63,40 @@ int64_t symm_open(const at::Tensor& handle);
 void symm_close(int64_t ptr);
 void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
                            int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
-                           int64_t off_count_flags, int64_t seq, at::Tensor counts_out, at::Tensor recv_bins,
-                           at::Tensor scratch);
+                           int64_t off_count_flags, int64_t seq, int64_t expert_capacity, at::Tensor counts_out,
+                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch);
 void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
                      const at::Tensor& bins, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
                      int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                      int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
-                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done);
-void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done,
+                     const c10::optional<at::Tensor>& dropped_rows);
+void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& raw_counts,
+                       const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
                        int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done);
 void ep_set_flag_op(at::Tensor flag, int64_t value);
+void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_t world, int64_t rank,
+                     int64_t off_grad, int64_t off_ready, int64_t off_done, int64_t start, int64_t count,
+                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas);
 void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code);
 
 // torch_glue.cpp: fused row-wise ops
 std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at::Tensor& targets);
 void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
                              const c10::optional<at::Tensor>& scale, double scale_mul);
-std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
-                                          double eps, const c10::optional<at::Tensor>& res);
+std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma,
+                                          const c10::optional<at::Tensor>& beta, double eps,
+                                          const c10::optional<at::Tensor>& res);
 std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
                                            const at::Tensor& mean, const at::Tensor& rstd,
-                                           const c10::optional<at::Tensor>& dres);
+                                           const c10::optional<at::Tensor>& dres, bool rms);
 bool layernorm_can_fuse(const at::Tensor& x);
+at::Tensor lbl_forward_op(const std::vector<at::Tensor>& scores, const std::vector<at::Tensor>& counts, double scale);
+std::vector<at::Tensor> lbl_backward_op(const std::vector<at::Tensor>& scores, const std::vector<at::Tensor>& counts,
+                                        double scale, const at::Tensor& gout);
+at::Tensor rope_op(const at::Tensor& x, const at::Tensor& cosv, const at::Tensor& sinv, bool inverse);
 at::Tensor column_sum_op(const at::Tensor& x);
 
 // torch_glue.cpp: optimizer
@@ -128,6 +138,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_forward", &mb::layernorm_forward);
   m.def("layernorm_backward", &mb::layernorm_backward);
   m.def("layernorm_can_fuse", &mb::layernorm_can_fuse);
+  m.def("lbl_forward", &mb::lbl_forward_op, "Load-balancing loss of all layers in one reduction kernel");
+  m.def("lbl_backward", &mb::lbl_backward_op);
+  m.def("rope", &mb::rope_op, "Rotary position embedding of [batch, seq, heads, dim]");
   m.def("column_sum", &mb::column_sum_op, "Sum over rows of x[rows, cols] (bias gradient)");
   m.def("symm_alloc", &mb::symm_alloc);
   m.def("symm_open", &mb::symm_open);
@@ -139,6 +152,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_return_rows", &mb::ep_return_rows_op);
   m.def("ep_wait_flags", &mb::ep_wait_flags_op);
   m.def("ep_set_flag", &mb::ep_set_flag_op);
+  m.def("dp_allreduce", &mb::dp_allreduce_op,
+        "Gradient bucket all-reduce / reduce-scatter over peer memory (one kernel, bounded waits)");
   m.def("adam_record_size", &mb::adam_record_size);
   m.def("adam_step", &mb::adam_step_op);
   m.def("grad_sqnorm", &mb::grad_sqnorm_op);

@@ -75,9 +75,9 @@ __device__ __forceinline__ T* peer_ptr(const uint64_t* peer_base, int rank, int6
 // counts
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
-exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int* __restrict__ counts_out,
-                       int* __restrict__ recv_bins, int* __restrict__ scratch_zero, int scratch_ints,
-                       int* status) {
+exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int expert_capacity,
+                       int* __restrict__ counts_out, int* __restrict__ kept_out, int* __restrict__ recv_bins,
+                       int* __restrict__ scratch_zero, int scratch_ints, int* status) {
   const int parity = seq & 1;
   const int64_t counts_off = L.off_counts + int64_t(parity) * L.world * L.num_experts * 4;
   // (a) my counts -> row `me` of every peer's matrix.
@@ -106,7 +106,7 @@ exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int* __
   if (!ok_s || dead_s) {
     // Fail closed: with an all-zero count matrix every kernel that follows on this stream
     // (push, expert GEMMs, return) finds nothing to move and stores nothing anywhere.
-    for (int i = threadIdx.x; i < L.world * L.num_experts; i += blockDim.x) counts_out[i] = 0;
+    for (int i = threadIdx.x; i < L.world * L.num_experts; i += blockDim.x) counts_out[i] = kept_out[i] = 0;
     for (int j = threadIdx.x; j < L.experts_per_rank; j += blockDim.x) recv_bins[j] = 0;
     return;
   }
@@ -122,11 +122,23 @@ exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int* __
     counts_out[i] = v;
   }
   __syncthreads();
+  // Rows that survive a per-expert capacity: of everything routed to expert e, taken source by
+  // source in rank order, only the first `expert_capacity` rows are kept (0 = no limit), which is
+  // the rule of the reference's binned gather after its second sort.
+  for (int e = threadIdx.x; e < L.num_experts; e += blockDim.x) {
+    int room = expert_capacity > 0 ? expert_capacity : 0x7fffffff;
+    for (int s = 0; s < L.world; ++s) {
+      const int keep = min(counts_out[s * L.num_experts + e], room);
+      kept_out[s * L.num_experts + e] = keep;
+      room -= keep;
+    }
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int j = 0; j < L.experts_per_rank; ++j) {
       const int e = L.rank * L.experts_per_rank + j;
-      for (int s = 0; s < L.world; ++s) acc += counts_out[s * L.num_experts + e];
+      for (int s = 0; s < L.world; ++s) acc += kept_out[s * L.num_experts + e];
       // More rows than the buffer holds: the senders skip them (see push_rows_kernel), the
       // receiver's groups end at the capacity, and the status word reports the overflow.
       recv_bins[j] = min(acc, L.capacity_rows);
@@ -143,7 +155,8 @@ __global__ void __launch_bounds__(kPushWarps * 32)
 push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const T* __restrict__ weights,
                  const int* __restrict__ bins, const int* __restrict__ counts, EpLayout L,
                  const uint64_t* __restrict__ data_base, int64_t off_recv, int64_t off_flags, int64_t off_free,
-                 int seq, int top_k, int n, int cols, int* __restrict__ done, int* status) {
+                 int seq, int top_k, int n, int cols, int* __restrict__ done, int* status,
+                 T* __restrict__ dropped_rows) {
   extern __shared__ int smem[];
   int* dst_start = smem;                    // [E] first row of (me, e) in the owner's buffer
   int* src_start = smem + L.num_experts;    // [E] first sorted position of e here
@@ -186,8 +199,18 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
     const int owner = e / epr;
     const int copy = __ldg(indices + i);
     const T* src = x + int64_t(copy / top_k) * cols;
-    const int dst_row = dst_start[e] + (i - src_start[e]);
-    if (e >= E || dst_row < 0 || dst_row >= L.capacity_rows) continue;   // never store outside the owner's buffer
+    if (e >= E) continue;
+    const int within = i - src_start[e];
+    if (within >= counts[L.rank * E + e]) {
+      // Beyond the expert's capacity: the copy is dropped.  Nobody will return a row for it, so its
+      // slot in this rank's return buffer is cleared here.
+      if (dropped_rows != nullptr)
+        for (int c0 = lane * VEC; c0 < cols; c0 += 32 * VEC)
+          *reinterpret_cast<uint4*>(dropped_rows + int64_t(i) * cols + c0) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const int dst_row = dst_start[e] + within;
+    if (dst_row < 0 || dst_row >= L.capacity_rows) continue;   // never store outside the owner's buffer
     T* dst = peer_ptr<T>(data_base, owner, off_recv) + int64_t(dst_row) * cols;
     const float scale = weights != nullptr ? to_float(weights[copy]) : 1.f;
     // Four 16-byte loads in flight per lane before the first (remote) store.
@@ -234,7 +257,8 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kPushWarps * 32)
-return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLayout L,
+return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, const int* __restrict__ raw_counts,
+                   EpLayout L,
                    const uint64_t* __restrict__ data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
                    int rows_bound, int ret_rows, int* __restrict__ done, const int* status) {
   extern __shared__ int smem[];
@@ -255,7 +279,7 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, EpLa
     const int j = idx / W, s = idx - j * W;
     const int e = L.rank * epr + j;
     int acc = 0;
-    for (int e2 = 0; e2 < e; ++e2) acc += counts[s * E + e2];
+    for (int e2 = 0; e2 < e; ++e2) acc += raw_counts[s * E + e2];   // the source's order holds dropped copies too
     remote_start[idx] = acc;
   }
   for (int s = threadIdx.x; s < W; s += blockDim.x) {
@@ -333,18 +357,19 @@ __global__ void set_flag_kernel(int* flag, int value) { st_release_sys(flag, val
 
 }  // namespace
 
-cudaError_t ep_exchange_counts(const int* tpe, const EpLayout& layout, int seq, int* counts_out, int* recv_bins,
-                               int* scratch_zero, int scratch_ints, int* status, cudaStream_t stream) {
+cudaError_t ep_exchange_counts(const int* tpe, const EpLayout& layout, int seq, int expert_capacity, int* counts_out,
+                               int* kept_out, int* recv_bins, int* scratch_zero, int scratch_ints, int* status,
+                               cudaStream_t stream) {
   if (layout.world > 1024) return cudaErrorInvalidValue;
-  exchange_counts_kernel<<<1, 1024, 0, stream>>>(tpe, layout, seq, counts_out, recv_bins, scratch_zero,
-                                                scratch_ints, status);
+  exchange_counts_kernel<<<1, 1024, 0, stream>>>(tpe, layout, seq, expert_capacity, counts_out, kept_out, recv_bins,
+                                                scratch_zero, scratch_ints, status);
   return cudaGetLastError();
 }
 
 cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const void* weights, const int* bins,
                          const int* counts, const EpLayout& layout, const uint64_t* data_base, int64_t off_recv,
                          int64_t off_flags, int64_t off_free, int seq, int top_k, int n, int cols, int* done,
-                         int* status, int sms, cudaStream_t stream) {
+                         int* status, void* dropped_rows, int sms, cudaStream_t stream) {
   const int elem = type == kF32 ? 4 : 2;
   if ((int64_t(cols) * elem) % 16 != 0) return cudaErrorInvalidValue;
   const int grid = max(1, min(ceil_div(max(n, 1), kPushWarps), sms * 4));
@@ -352,12 +377,13 @@ cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const vo
   MB_SWITCH_FLOAT(type, T, {
     push_rows_kernel<T><<<grid, kPushWarps * 32, smem, stream>>>(
         static_cast<const T*>(x), indices, static_cast<const T*>(weights), bins, counts, layout, data_base, off_recv,
-        off_flags, off_free, seq, top_k, n, cols, done, status);
+        off_flags, off_free, seq, top_k, n, cols, done, status, static_cast<T*>(dropped_rows));
   })
   return cudaGetLastError();
 }
 
-cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const EpLayout& layout,
+cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const int* raw_counts,
+                           const EpLayout& layout,
                            const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
                            int rows_bound, int ret_rows, int* done, const int* status, int sms,
                            cudaStream_t stream) {
@@ -368,7 +394,7 @@ cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const E
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   const int grid = max(1, min(ceil_div(max(rows_bound, 1), kPushWarps), sms * 4));
   MB_SWITCH_FLOAT(type, T, {
-    return_rows_kernel<T><<<grid, kPushWarps * 32, smem, stream>>>(static_cast<const T*>(y), counts, layout,
+    return_rows_kernel<T><<<grid, kPushWarps * 32, smem, stream>>>(static_cast<const T*>(y), counts, raw_counts, layout,
                                                                   data_base, off_ret, off_flags, seq, cols, rows_bound,
                                                                   ret_rows, done, status);
   })

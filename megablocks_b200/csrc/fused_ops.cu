@@ -118,7 +118,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, int64_t rows,
                      int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
-                     float* __restrict__ rstd_out) {
+                     float* __restrict__ rstd_out, int rms) {
   constexpr int VEC = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   const int64_t stride = int64_t(gridDim.x) * kLnWarps;
@@ -132,17 +132,20 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const
     }
     s = warp_sum(s);
     ss = warp_sum(ss);
-    const float mean = s / cols;
+    // RMS norm (`rms`): no centring and no bias; the stored mean is 0 so the backward needs no second form.
+    const float mean = rms ? 0.f : s / cols;
     const float rstd = rsqrtf(fmaxf(ss / cols - mean * mean, 0.f) + eps);
     if (lane == 0) { mean_out[r] = mean; rstd_out[r] = rstd; }
     T* yr = y + r * cols;
     for (int c = lane * VEC; c < cols; c += 32 * VEC) {
       Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
       Pack<T, VEC> g = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
-      Pack<T, VEC> b = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
+      Pack<T, VEC> b;
+      if (beta != nullptr) b = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
 #pragma unroll
       for (int k = 0; k < VEC; ++k)
-        p.v[k] = from_float<T>((to_float(p.v[k]) - mean) * rstd * to_float(g.v[k]) + to_float(b.v[k]));
+        p.v[k] = from_float<T>((to_float(p.v[k]) - mean) * rstd * to_float(g.v[k]) +
+                               (beta != nullptr ? to_float(b.v[k]) : 0.f));
       *reinterpret_cast<Pack<T, VEC>*>(yr + c) = p;
     }
   }
@@ -152,7 +155,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
-                     T* __restrict__ dx, float* __restrict__ partial) {
+                     T* __restrict__ dx, float* __restrict__ partial, int rms) {
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float acc[];          // [2][cols]: dgamma, dbeta of this CTA
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
@@ -180,7 +183,7 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       }
     }
     s1 = warp_sum(s1) / cols;
-    s2 = warp_sum(s2) / cols;
+    s2 = rms ? 0.f : warp_sum(s2) / cols;       // no centring: the mean term of the gradient vanishes
     T* dxr = dx + r * cols;
     for (int c = lane * VEC; c < cols; c += 32 * VEC) {
       Pack<T, VEC> px = *reinterpret_cast<const Pack<T, VEC>*>(xr + c);
@@ -209,7 +212,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32, 2)
 layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                          const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
-                         T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dres) {
+                         T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dres, int rms) {
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float acc[];          // [2][cols]
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) acc[c] = 0.f;
@@ -276,7 +279,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
       }
     }
     s1 = warp_sum(s1) / cols;
-    s2 = warp_sum(s2) / cols;
+    s2 = rms ? 0.f : warp_sum(s2) / cols;
     T* dxr = dx + r * cols;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
@@ -320,7 +323,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                          int64_t rows, int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
-                         float* __restrict__ rstd_out, const T* __restrict__ res, T* __restrict__ sum_out) {
+                         float* __restrict__ rstd_out, const T* __restrict__ res, T* __restrict__ sum_out, int rms) {
   constexpr int VEC = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   Pack<T, VEC> pg[MAXV], pb[MAXV];
@@ -329,7 +332,12 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
     const int c = (j * 32 + lane) * VEC;
     if (c < cols) {
       pg[j] = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
-      pb[j] = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
+      if (beta != nullptr) {
+        pb[j] = *reinterpret_cast<const Pack<T, VEC>*>(beta + c);
+      } else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) pb[j].v[k] = from_float<T>(0.f);
+      }
     }
   }
   const float inv_cols = 1.f / cols;
@@ -380,7 +388,7 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
     }
     s = warp_sum(s);
     ss = warp_sum(ss);
-    const float mean = s * inv_cols;
+    const float mean = rms ? 0.f : s * inv_cols;
     const float rstd = rsqrtf(fmaxf(ss * inv_cols - mean * mean, 0.f) + eps);
     if (lane == 0) { mean_out[r] = mean; rstd_out[r] = rstd; }
     T* yr = y + r * cols;
@@ -482,36 +490,37 @@ __global__ void colsum_reduce_kernel(const float* __restrict__ partial, int slic
 
 template <typename T>
 bool launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
-                          float* mean, float* rstd, const T* res, T* sum_out, int sms, cudaStream_t stream) {
+                          float* mean, float* rstd, const T* res, T* sum_out, int rms, int sms, cudaStream_t stream) {
   constexpr int kVec = 16 / sizeof(T);
   const int grid = max(1, min(ceil_div(rows, kLnWarps), sms * 6));
   const int packs = ceil_div(cols, 32 * kVec);
   switch (packs) {
-    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
-    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
-    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
-    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out); break;
+    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
+    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
+    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
+    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
     default:
       if (res != nullptr) return false;   // the wide-row kernel has no fused add
       layernorm_fwd_kernel<T><<<max(1, min(ceil_div(rows, kLnWarps), sms * 2)), kLnWarps * 32, 0, stream>>>(
-          x, gamma, beta, rows, cols, eps, y, mean, rstd);
+          x, gamma, beta, rows, cols, eps, y, mean, rstd, rms);
   }
   return true;
 }
 
 template <typename T>
 bool launch_layernorm_bwd(const T* dy, const T* x, const T* gamma, const float* mean, const float* rstd, int64_t rows,
-                          int cols, T* dx, float* partial, const T* dres, int grid, size_t smem, cudaStream_t stream) {
+                          int cols, T* dx, float* partial, const T* dres, int rms, int grid, size_t smem,
+                          cudaStream_t stream) {
   constexpr int kVec = 16 / sizeof(T);
   const int packs = ceil_div(cols, 32 * kVec);
   switch (packs) {
-    case 1: layernorm_bwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
-    case 2: layernorm_bwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
-    case 3: layernorm_bwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
-    case 4: layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres); break;
+    case 1: layernorm_bwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres, rms); break;
+    case 2: layernorm_bwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres, rms); break;
+    case 3: layernorm_bwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres, rms); break;
+    case 4: layernorm_bwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, dres, rms); break;
     default:
       if (dres != nullptr) return false;
-      layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial);
+      layernorm_bwd_kernel<T><<<grid, kLnWarps * 32, smem, stream>>>(dy, x, gamma, mean, rstd, rows, cols, dx, partial, rms);
   }
   return true;
 }
@@ -547,14 +556,14 @@ bool layernorm_fusable(DType type, int cols) {
 }
 
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, int sms,
-                          cudaStream_t stream) {
+                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, bool rms,
+                          int sms, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
     if (!launch_layernorm_fwd<T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),
                                  rows, cols, eps, static_cast<T*>(y), mean, rstd, static_cast<const T*>(res),
-                                 static_cast<T*>(sum_out), sms, stream))
+                                 static_cast<T*>(sum_out), rms ? 1 : 0, sms, stream))
       return cudaErrorInvalidValue;
   })
   return cudaGetLastError();
@@ -562,7 +571,7 @@ cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const vo
 
 cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
-                          float* partial, const void* dres, int sms, cudaStream_t stream) {
+                          float* partial, const void* dres, bool rms, int sms, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   const int grid = layernorm_grid(rows, sms);
   const size_t smem = size_t(2) * cols * sizeof(float);
@@ -571,7 +580,7 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
     if (!launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
                                  mean, rstd, rows, cols, static_cast<T*>(dx), partial, static_cast<const T*>(dres),
-                                 grid, smem, stream))
+                                 rms ? 1 : 0, grid, smem, stream))
       return cudaErrorInvalidValue;
     layernorm_bwd_reduce_kernel<T><<<ceil_div(2 * cols, 32), 256, 0, stream>>>(
         partial, grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));

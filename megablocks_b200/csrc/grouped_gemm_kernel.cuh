@@ -664,7 +664,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int j = idx / W, s2 = idx - j * W;
       const int e = p.scatter_rank * epr + j;
       int acc = 0;
-      for (int e2 = 0; e2 < e; ++e2) acc += __ldg(p.scatter_counts + s2 * E + e2);
+      for (int e2 = 0; e2 < e; ++e2) acc += __ldg(p.scatter_raw_counts + s2 * E + e2);
       s_remote_start[idx] = acc;       // first sorted position of (source s2, expert e) at the source
     }
     for (int s2 = threadIdx.x; s2 < W; s2 += kThreads) {

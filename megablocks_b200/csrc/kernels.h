@@ -87,20 +87,42 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
                               cudaStream_t stream);
 int layernorm_grid(int64_t rows, int sms);   // CTAs (= rows of `partial`) the backward uses
 // Optional fusions (rows short enough for the register kernels, see layernorm_fusable): forward
-// normalises x + res and writes the sum to sum_out; backward adds dres to dx.
+// normalises x + res and writes the sum to sum_out; backward adds dres to dx.  `rms`: RMS norm
+// (y = x * rsqrt(mean(x^2) + eps) * gamma; beta may be null, dbeta is then meaningless).
 bool layernorm_fusable(DType type, int cols);
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, int sms,
-                          cudaStream_t stream);
+                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, bool rms,
+                          int sms, cudaStream_t stream);
 cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
-                          float* partial, const void* dres, int sms, cudaStream_t stream);
+                          float* partial, const void* dres, bool rms, int sms, cudaStream_t stream);
 
 // Column sums of x[rows, cols] (cols a multiple of 16 bytes): `partial` holds slices x cols floats,
 // slices = colsum_slices(...).
 int colsum_slices(int64_t rows, int cols, int elem_size, int sms);
 cudaError_t column_sum(DType type, const void* x, int64_t rows, int cols, void* out, float* partial, int slices,
                        cudaStream_t stream);
+
+// ---- model_ops.cu -------------------------------------------------------------
+constexpr int kLblMaxLayers = 64;
+struct LblArgs {
+  const void* scores[kLblMaxLayers];   // [tokens, experts] router scores of every layer
+  const int* counts[kLblMaxLayers];    // [experts] tokens per expert of every layer
+  void* dscores[kLblMaxLayers];        // backward: gradient of every layer's scores
+};
+int lbl_slices(int64_t tokens, int layers, int sms);
+// loss = scale * sum over layers of <counts, column sums of scores>; `partial` holds layers x slices
+// floats, `ticket` is a zeroed int.  Deterministic (fixed partition, fixed summation order).
+cudaError_t lbl_forward(DType type, const LblArgs& args, int layers, int64_t tokens, int experts, float scale,
+                        float* partial, int slices, int* ticket, float* loss, cudaStream_t stream);
+// dscores[l][t, e] = gout[0] * scale * counts[l][e].
+cudaError_t lbl_backward(DType type, const LblArgs& args, int layers, int64_t tokens, int experts, float scale,
+                         const float* gout, int sms, cudaStream_t stream);
+// Rotary embedding of x[batch, seq, heads, dim] (strides in elements, unit stride in dim) with
+// cos / sin tables [seq, dim / 2]; `inverse` rotates the other way (the gradient).  out is contiguous.
+cudaError_t rope(DType type, const void* x, int64_t stride_b, int64_t stride_s, int64_t stride_h, const float* cosv,
+                 const float* sinv, int batch, int seq, int heads, int dim, bool inverse, void* out, int sms,
+                 cudaStream_t stream);
 
 // ---- ep_comm.cu ---------------------------------------------------------------
 // Geometry of one expert-parallel workspace.  `peer_base[r]` is the address at which
@@ -119,20 +141,48 @@ struct EpLayout {
 constexpr int kEpErrCounts = 16, kEpErrOverflow = 17, kEpErrGemmWait = 18, kEpErrReturnWait = 19,
               kEpErrBufferBusy = 20;
 
-cudaError_t ep_exchange_counts(const int* tpe, const EpLayout& layout, int seq, int* counts_out, int* recv_bins,
-                               int* scratch_zero, int scratch_ints, int* status, cudaStream_t stream);
+// `counts_out` receives the [world][experts] matrix of routed copies, `kept_out` the copies that
+// survive `expert_capacity` (rows kept per expert, counted over the sources in rank order; 0 = no
+// limit, kept == counts), `recv_bins` the inclusive prefix sums of the kept rows of the local experts.
+cudaError_t ep_exchange_counts(const int* tpe, const EpLayout& layout, int seq, int expert_capacity, int* counts_out,
+                               int* kept_out, int* recv_bins, int* scratch_zero, int scratch_ints, int* status,
+                               cudaStream_t stream);
 // `data_base[r]` is the mapping of the heap that holds the row buffers (it may differ
-// from the heap of the flags); `off_free < 0` skips the buffer-free handshake.
+// from the heap of the flags); `off_free < 0` skips the buffer-free handshake.  `counts` is the
+// matrix of KEPT copies; a copy beyond its expert's kept count is not sent, and its row of
+// `dropped_rows` (this rank's return buffer, sorted order; may be null) is cleared instead.
 cudaError_t ep_push_rows(DType type, const void* x, const int* indices, const void* weights, const int* bins,
                          const int* counts, const EpLayout& layout, const uint64_t* data_base, int64_t off_recv,
                          int64_t off_flags, int64_t off_free, int seq, int top_k, int n, int cols, int* done,
-                         int* status, int sms, cudaStream_t stream);
-cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const EpLayout& layout,
+                         int* status, void* dropped_rows, int sms, cudaStream_t stream);
+// `counts` = kept copies (segment sizes here), `raw_counts` = routed copies (positions at the sources).
+cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const int* raw_counts,
+                           const EpLayout& layout,
                            const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
                            int rows_bound, int ret_rows, int* done, const int* status, int sms,
                            cudaStream_t stream);
 cudaError_t ep_set_flag(int* flag, int value, cudaStream_t stream);
 cudaError_t ep_wait_flags(const int* flags, int count, int seq, int* status, int code, cudaStream_t stream);
+
+// ---- dp_comm.cu ---------------------------------------------------------------
+// Geometry of the data-parallel gradient heap: `peer_base[r]` is where rank r's symmetric heap is
+// mapped in this process; the gradient buffer and the two flag arrays ([buckets][world] int32
+// each) sit at the same byte offsets on every rank.
+struct DpLayout {
+  const uint64_t* peer_base;
+  int world;
+  int rank;
+  int64_t off_grad;
+  int64_t off_ready;
+  int64_t off_done;
+};
+constexpr int kDpErrReady = 32, kDpErrDone = 33;
+// All-reduce (or, with `scatter_only`, reduce-scatter into this rank's slice) of elements
+// [start, start + count) of the gradient buffer, times `scale`; `start` and `count` must be multiples
+// of 16 bytes (for the reduce-scatter: `count` a multiple of world x 16 bytes, so that the slices are
+// the callers' shards).  `ticket` is a zeroed device int owned by the bucket.
+cudaError_t dp_allreduce(DType type, const DpLayout& layout, int64_t start, int64_t count, int bucket, int seq,
+                         float scale, bool scatter_only, int* ticket, int* status, int ctas, cudaStream_t stream);
 
 // ---- grouped GEMM ---------------------------------------------------------------
 namespace gemm {
@@ -176,7 +226,8 @@ struct GemmParams {
   // last row for a source has been stored its flag is released.  Null scatter_base = off.
   const uint64_t* scatter_base;       // mapping of every rank's heap that holds the return buffer
   const uint64_t* scatter_flag_base;  // mapping of every rank's heap that holds the flags
-  const int* scatter_counts;
+  const int* scatter_counts;          // [world][experts] copies KEPT per (source, expert): segment sizes here
+  const int* scatter_raw_counts;      // [world][experts] copies routed: positions in the sources' sorted order
   int* scatter_done;                  // [world] zeroed completion counters
   int64_t scatter_off;                // byte offset of the return buffer in its heap
   int64_t scatter_flag_off;           // byte offset of the int32 flag array [world] in its heap

@@ -564,11 +564,11 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     p.wait_seq = int(wait_seq);
   }
   if (scatter.has_value()) {
-    // scatter = {data heap bases, flag heap bases, counts, done}; scatter_args = {data offset, flag
+    // scatter = {data heap bases, flag heap bases, kept counts, done[, routed counts]}; scatter_args = {data offset, flag
     // offset, world, rank, experts, seq, rows of the return buffer}.
     TORCH_CHECK(epilogue == kEpiNone || epilogue == kEpiAdd, "the fused combine supports the plain and the add epilogue");
-    TORCH_CHECK(layout == kNN && scatter->size() == 4 && scatter_args.size() == 7,
-                "the fused combine needs the NN layout, four tensors and seven integers");
+    TORCH_CHECK(layout == kNN && (scatter->size() == 4 || scatter->size() == 5) && scatter_args.size() == 7,
+                "the fused combine needs the NN layout, four or five tensors and seven integers");
     const auto& bases = (*scatter)[0];
     const auto& flag_bases = (*scatter)[1];
     const auto& counts = (*scatter)[2];
@@ -583,6 +583,13 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     p.scatter_base = reinterpret_cast<const uint64_t*>(bases.data_ptr<int64_t>());
     p.scatter_flag_base = reinterpret_cast<const uint64_t*>(flag_bases.data_ptr<int64_t>());
     p.scatter_counts = counts.data_ptr<int>();
+    p.scatter_raw_counts = p.scatter_counts;
+    if (scatter->size() == 5) {   // a capacity limit dropped copies: positions at the sources count them too
+      const auto& raw = (*scatter)[4];
+      TORCH_CHECK(raw.is_cuda() && raw.scalar_type() == at::kInt && raw.numel() == counts.numel(),
+                  "bad raw count matrix of the fused combine");
+      p.scatter_raw_counts = raw.data_ptr<int>();
+    }
     p.scatter_done = done.data_ptr<int>();
     p.scatter_off = scatter_args[0];
     p.scatter_flag_off = scatter_args[1];
@@ -840,11 +847,15 @@ bool layernorm_can_fuse(const at::Tensor& x) {
 }
 
 // Returns {y, mean, rstd, s}: s = x + res (or x itself without res) is the tensor that was normalised.
-std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
-                                          double eps, const c10::optional<at::Tensor>& res) {
-  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CONTIG(gamma); MB_CHECK_CONTIG(beta);
-  TORCH_CHECK(x.dim() == 2 && gamma.numel() == x.size(1) && beta.numel() == x.size(1) &&
-                  gamma.scalar_type() == x.scalar_type() && beta.scalar_type() == x.scalar_type(),
+// `beta` absent = RMS norm (no centring, no bias); the returned mean is then all zeros.
+std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma,
+                                          const c10::optional<at::Tensor>& beta, double eps,
+                                          const c10::optional<at::Tensor>& res) {
+  MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CONTIG(gamma);
+  const bool rms = !beta.has_value();
+  TORCH_CHECK(x.dim() == 2 && gamma.numel() == x.size(1) && gamma.scalar_type() == x.scalar_type() &&
+                  (rms || (beta->is_contiguous() && beta->numel() == x.size(1) &&
+                           beta->scalar_type() == x.scalar_type())),
               "layernorm expects x[rows, cols] and weight / bias of length cols in the dtype of x");
   c10::cuda::CUDAGuard guard(x.device());
   at::Tensor y = at::empty_like(x);
@@ -857,17 +868,18 @@ std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor&
   }
   auto fopts = x.options().dtype(at::kFloat);
   at::Tensor mean = at::empty({x.size(0)}, fopts), rstd = at::empty({x.size(0)}, fopts);
-  MB_CUDA_OK(layernorm_fwd(float_code(x.scalar_type()), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), x.size(0),
-                           int(x.size(1)), float(eps), y.data_ptr(), mean.data_ptr<float>(),
-                           rstd.data_ptr<float>(), res.has_value() ? res->data_ptr() : nullptr,
-                           res.has_value() ? sum.data_ptr() : nullptr, sm_count(), stream()));
+  MB_CUDA_OK(layernorm_fwd(float_code(x.scalar_type()), x.data_ptr(), gamma.data_ptr(),
+                           rms ? nullptr : beta->data_ptr(), x.size(0), int(x.size(1)), float(eps), y.data_ptr(),
+                           mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                           res.has_value() ? res->data_ptr() : nullptr, res.has_value() ? sum.data_ptr() : nullptr,
+                           rms, sm_count(), stream()));
   MB_LAUNCHED(1);
   return {y, mean, rstd, sum};
 }
 
 std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
                                            const at::Tensor& mean, const at::Tensor& rstd,
-                                           const c10::optional<at::Tensor>& dres) {
+                                           const c10::optional<at::Tensor>& dres, bool rms) {
   MB_CHECK_CUDA(dy); MB_CHECK_CONTIG(dy); MB_CHECK_CONTIG(x);
   c10::cuda::CUDAGuard guard(x.device());
   if (dres.has_value())
@@ -880,9 +892,83 @@ std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tenso
   MB_CUDA_OK(layernorm_bwd(float_code(x.scalar_type()), dy.data_ptr(), x.data_ptr(), gamma.data_ptr(),
                            mean.data_ptr<float>(), rstd.data_ptr<float>(), x.size(0), int(x.size(1)), dx.data_ptr(),
                            dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr<float>(),
-                           dres.has_value() ? dres->data_ptr() : nullptr, sm_count(), stream()));
+                           dres.has_value() ? dres->data_ptr() : nullptr, rms, sm_count(), stream()));
   MB_LAUNCHED(2);
   return {dx, dgamma, dbeta};
+}
+
+// ---------------------------------------------------------------------------
+// load-balancing loss, rotary embedding
+// ---------------------------------------------------------------------------
+namespace {
+LblArgs lbl_args(const std::vector<at::Tensor>& scores, const std::vector<at::Tensor>& counts) {
+  TORCH_CHECK(!scores.empty() && scores.size() == counts.size() && scores.size() <= size_t(kLblMaxLayers),
+              "load_balancing_loss: between 1 and ", kLblMaxLayers, " layers per call");
+  LblArgs args{};
+  const auto& first = scores[0];
+  for (size_t l = 0; l < scores.size(); ++l) {
+    const auto& s = scores[l];
+    const auto& c = counts[l];
+    TORCH_CHECK(s.is_cuda() && s.is_contiguous() && s.dim() == 2 && s.sizes() == first.sizes() &&
+                    s.scalar_type() == first.scalar_type(),
+                "load_balancing_loss: scores must be contiguous CUDA [tokens, experts] tensors of one shape and dtype");
+    TORCH_CHECK(c.is_cuda() && c.is_contiguous() && c.scalar_type() == at::kInt && c.numel() == s.size(1),
+                "load_balancing_loss: counts must be contiguous CUDA int32 [experts] tensors");
+    args.scores[l] = s.data_ptr();
+    args.counts[l] = c.data_ptr<int>();
+  }
+  return args;
+}
+}  // namespace
+
+at::Tensor lbl_forward_op(const std::vector<at::Tensor>& scores, const std::vector<at::Tensor>& counts, double scale) {
+  LblArgs args = lbl_args(scores, counts);
+  const auto& first = scores[0];
+  c10::cuda::CUDAGuard guard(first.device());
+  const int layers = int(scores.size());
+  const int slices = lbl_slices(first.size(0), layers, sm_count());
+  auto fopts = first.options().dtype(at::kFloat);
+  at::Tensor partial = at::empty({layers * slices}, fopts), loss = at::empty({}, fopts);
+  at::Tensor ticket = at::zeros({1}, first.options().dtype(at::kInt));
+  MB_CUDA_OK(lbl_forward(float_code(first.scalar_type()), args, layers, first.size(0), int(first.size(1)), float(scale),
+                         partial.data_ptr<float>(), slices, ticket.data_ptr<int>(), loss.data_ptr<float>(), stream()));
+  MB_LAUNCHED(1);
+  return loss;
+}
+
+std::vector<at::Tensor> lbl_backward_op(const std::vector<at::Tensor>& scores, const std::vector<at::Tensor>& counts,
+                                        double scale, const at::Tensor& gout) {
+  LblArgs args = lbl_args(scores, counts);
+  const auto& first = scores[0];
+  TORCH_CHECK(gout.is_cuda() && gout.scalar_type() == at::kFloat && gout.numel() == 1, "gout must be a CUDA fp32 scalar");
+  c10::cuda::CUDAGuard guard(first.device());
+  std::vector<at::Tensor> out;
+  for (size_t l = 0; l < scores.size(); ++l) {
+    out.push_back(at::empty_like(scores[l]));
+    args.dscores[l] = out.back().data_ptr();
+  }
+  MB_CUDA_OK(lbl_backward(float_code(first.scalar_type()), args, int(scores.size()), first.size(0), int(first.size(1)),
+                          float(scale), gout.data_ptr<float>(), sm_count(), stream()));
+  MB_LAUNCHED(1);
+  return out;
+}
+
+// x: [batch, seq, heads, dim] view with unit stride in dim; returns a contiguous tensor of that shape.
+at::Tensor rope_op(const at::Tensor& x, const at::Tensor& cosv, const at::Tensor& sinv, bool inverse) {
+  MB_CHECK_CUDA(x);
+  TORCH_CHECK(x.dim() == 4 && x.stride(3) == 1, "rope expects [batch, seq, heads, dim] with unit stride in dim");
+  TORCH_CHECK(cosv.is_cuda() && sinv.is_cuda() && cosv.is_contiguous() && sinv.is_contiguous() &&
+                  cosv.scalar_type() == at::kFloat && sinv.scalar_type() == at::kFloat && cosv.dim() == 2 &&
+                  cosv.size(0) >= x.size(1) && cosv.size(1) == x.size(3) / 2 && sinv.sizes() == cosv.sizes(),
+              "rope expects fp32 cos / sin tables [>= seq, dim / 2]");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "rope: input must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty(x.sizes(), x.options());
+  MB_CUDA_OK(rope(float_code(x.scalar_type()), x.data_ptr(), x.stride(0), x.stride(1), x.stride(2),
+                  cosv.data_ptr<float>(), sinv.data_ptr<float>(), int(x.size(0)), int(x.size(1)), int(x.size(2)),
+                  int(x.size(3)), inverse, out.data_ptr(), sm_count(), stream()));
+  MB_LAUNCHED(1);
+  return out;
 }
 
 // Sum over the rows of x[rows, cols]: the bias gradient of a linear layer.
@@ -962,19 +1048,20 @@ int* status_ptr(const at::Tensor& t) { return status_word(t.device()).data_ptr<i
 
 void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
                            int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
-                           int64_t off_count_flags, int64_t seq, at::Tensor counts_out, at::Tensor recv_bins,
-                           at::Tensor scratch) {
+                           int64_t off_count_flags, int64_t seq, int64_t expert_capacity, at::Tensor counts_out,
+                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch) {
   check_index(tpe, "tokens_per_expert");
   c10::cuda::CUDAGuard guard(tpe.device());
-  TORCH_CHECK(counts_out.numel() == world * num_experts && recv_bins.numel() == experts_per_rank &&
-                  counts_out.scalar_type() == at::kInt && recv_bins.scalar_type() == at::kInt &&
-                  scratch.scalar_type() == at::kInt,
-              "bad ep_exchange_counts outputs");
+  TORCH_CHECK(tpe.numel() == num_experts && counts_out.numel() == world * num_experts &&
+                  kept_out.numel() == world * num_experts && recv_bins.numel() == experts_per_rank &&
+                  counts_out.scalar_type() == at::kInt && kept_out.scalar_type() == at::kInt &&
+                  recv_bins.scalar_type() == at::kInt && scratch.scalar_type() == at::kInt && expert_capacity >= 0,
+              "bad ep_exchange_counts arguments");
   const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
                                  off_count_flags);
-  MB_CUDA_OK(ep_exchange_counts(tpe.data_ptr<int>(), L, int(seq), counts_out.data_ptr<int>(),
-                                recv_bins.data_ptr<int>(), scratch.data_ptr<int>(), int(scratch.numel()),
-                                status_ptr(tpe), stream()));
+  MB_CUDA_OK(ep_exchange_counts(tpe.data_ptr<int>(), L, int(seq), int(expert_capacity), counts_out.data_ptr<int>(),
+                                kept_out.data_ptr<int>(), recv_bins.data_ptr<int>(), scratch.data_ptr<int>(),
+                                int(scratch.numel()), status_ptr(tpe), stream()));
   MB_LAUNCHED(1);
 }
 
@@ -982,8 +1069,17 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
                      const at::Tensor& bins, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
                      int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                      int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
-                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done) {
+                     int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done,
+                     const c10::optional<at::Tensor>& dropped_rows) {
   MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
+  void* dropped = nullptr;
+  if (dropped_rows.has_value()) {
+    TORCH_CHECK(dropped_rows->is_cuda() && dropped_rows->is_contiguous() && dropped_rows->scalar_type() == x.scalar_type() &&
+                    dropped_rows->dim() == 2 && dropped_rows->size(1) == x.size(1) &&
+                    dropped_rows->size(0) >= indices.numel(),
+                "dropped_rows must be a [>= copies, hidden] buffer of the activation dtype");
+    dropped = dropped_rows->data_ptr();
+  }
   check_index(indices, "indices"); check_index(bins, "bins");
   check_weights(weights, x, indices.numel());
   c10::cuda::CUDAGuard guard(x.device());
@@ -995,11 +1091,12 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
                           bins.data_ptr<int>(), counts.data_ptr<int>(), L,
                           reinterpret_cast<const uint64_t*>(data_base.data_ptr<int64_t>()), off_recv, off_flags,
                           off_free, int(seq), int(top_k), int(indices.numel()), int(x.size(1)),
-                          done.data_ptr<int>(), status_ptr(x), sm_count(), stream()));
+                          done.data_ptr<int>(), status_ptr(x), dropped, sm_count(), stream()));
   MB_LAUNCHED(1);
 }
 
-void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
+void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& raw_counts,
+                       const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
                        int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done) {
@@ -1009,7 +1106,10 @@ void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::
                                  off_count_flags);
   TORCH_CHECK(data_base.is_cuda() && data_base.scalar_type() == at::kLong && data_base.numel() == world,
               "data_base must be a CUDA int64 tensor with one address per rank");
-  MB_CUDA_OK(ep_return_rows(float_code(y.scalar_type()), y.data_ptr(), counts.data_ptr<int>(), L,
+  TORCH_CHECK(raw_counts.is_cuda() && raw_counts.scalar_type() == at::kInt && raw_counts.numel() == counts.numel(),
+              "raw_counts must match counts");
+  MB_CUDA_OK(ep_return_rows(float_code(y.scalar_type()), y.data_ptr(), counts.data_ptr<int>(),
+                            raw_counts.data_ptr<int>(), L,
                             reinterpret_cast<const uint64_t*>(data_base.data_ptr<int64_t>()), off_ret, off_flags,
                             int(seq), int(y.size(1)), int(y.size(0)), int(ret_rows), done.data_ptr<int>(),
                             status_ptr(y), sm_count(), stream()));
@@ -1027,6 +1127,28 @@ void ep_set_flag_op(at::Tensor flag, int64_t value) {
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && flag.numel() >= 1, "bad flag tensor");
   c10::cuda::CUDAGuard guard(flag.device());
   MB_CUDA_OK(ep_set_flag(flag.data_ptr<int>(), int(value), stream()));
+  MB_LAUNCHED(1);
+}
+
+// Gradient all-reduce / reduce-scatter over peer memory: see dp_comm.cu.  `like` names the device and
+// the element type of the gradient buffer that lives at `off_grad` in the symmetric heap.
+void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_t world, int64_t rank,
+                     int64_t off_grad, int64_t off_ready, int64_t off_done, int64_t start, int64_t count,
+                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas) {
+  MB_CHECK_CUDA(like);
+  TORCH_CHECK(peer_base.is_cuda() && peer_base.scalar_type() == at::kLong && peer_base.numel() == world,
+              "peer_base must be a CUDA int64 tensor with one address per rank");
+  TORCH_CHECK(ticket.is_cuda() && ticket.scalar_type() == at::kInt && ticket.numel() >= 1, "bad ticket tensor");
+  c10::cuda::CUDAGuard guard(like.device());
+  DpLayout L{};
+  L.peer_base = reinterpret_cast<const uint64_t*>(peer_base.data_ptr<int64_t>());
+  L.world = int(world);
+  L.rank = int(rank);
+  L.off_grad = off_grad;
+  L.off_ready = off_ready;
+  L.off_done = off_done;
+  MB_CUDA_OK(dp_allreduce(float_code(like.scalar_type()), L, start, count, int(bucket), int(seq), float(scale),
+                          scatter_only, ticket.data_ptr<int>(), status_ptr(like), int(ctas), stream()));
   MB_LAUNCHED(1);
 }
 

@@ -35,8 +35,6 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         self.ffn_hidden_size = mpu.features_per_rank(args)
         max_column_index = (self.ffn_hidden_size * self.num_experts) // self.blocking
         self.transpose_sort_end_bit = max(int(max_column_index - 1).bit_length(), 1)
-        self._ep_workspaces = {}      # activation dtype -> ring of workspaces
-        self._ep_calls = 0
         if args.moe_expert_model_parallelism:
             self.forward_fn = self.parallel_forward_once
 
@@ -134,57 +132,18 @@ class ParallelDroplessMLP(moe.ParallelMLP):
         return ops.scatter(x, indices, bin_ids, expert_weights, bins, top_k)
 
     # -- expert parallel over peer memory ----------------------------------------
-    def _use_fused_ep(self, x: torch.Tensor) -> bool:
-        want = self.args.ep_fused_comm
-        if want is False:
-            return False
-        from megablocks_b200.parallel import ep
-        ok = ep.fused_path_available(self.args, x)
-        if want is True and not ok:
-            raise RuntimeError('ep_fused_comm=True but the peer-memory route cannot serve this layer '
-                               '(needs CUDA 16-bit activations, a kernel-known activation, world <= experts, '
-                               'hidden and ffn multiples of 64)')
-        return ok
-
     def parallel_forward_once(self, x, expert_weights, top_experts):
         if not self._use_fused_ep(x):
             return super().parallel_forward_once(x, expert_weights, top_experts)
-        from megablocks_b200.ops import gg
-        from megablocks_b200.parallel import ep
-        args = self.args
-        x2d = x.reshape(-1, x.shape[-1])
-        expert_weights = expert_weights.flatten()
-        with torch.no_grad():
-            indices, bin_ids, bins, tokens_per_expert = self.indices_and_bins(top_experts.flatten())
-        copies = indices.numel()
-        ring = self._ep_workspaces.get(x2d.dtype)
-        if ring is None:
-            # Created once per activation dtype (a collective: every rank of the group gets here on
-            # its first call) and sized for the largest copy count over the group.
-            ring = [ep.EpWorkspace(args.expert_parallel_group, self.num_experts,
-                                   max(copies, int(args.ep_max_copies or 0)), args.hidden_size, x2d.dtype,
-                                   x2d.device, capacity_rows=args.ep_capacity_rows)
-                    for _ in range(max(1, int(args.ep_inflight_microbatches)))]
-            self._ep_workspaces[x2d.dtype] = ring
-        workspace = ring[self._ep_calls % len(ring)]
-        self._ep_calls += 1
-        if copies > workspace.copies:
-            raise RuntimeError(
-                f'fused expert parallelism: this call routes {copies} copies but the symmetric buffers were sized '
-                f'for {workspace.copies}.  Set Arguments.ep_max_copies to the largest tokens x top_k of any rank '
-                '(the buffers cannot be regrown inside forward without a collective).')
         mlp = self.mlp
         # Unscaled weights: the 1 / world factor of their gradients is applied inside the wgrad GEMMs.
         w1, w2 = mlp._raw_weights()
         v1 = None
-        if args.mlp_type == 'glu':
+        if self.args.mlp_type == 'glu':
             w1, v1, w2 = mlp._raw_glu_weights()
             v1 = mlp._grouped_view(v1)
-        out = ep.fused_expert_parallel(x2d, expert_weights.to(x2d.dtype), mlp._grouped_view(w1),
-                                       mlp._grouped_view(w2), v1, workspace, indices, bin_ids, bins,
-                                       tokens_per_expert, self.top_k, gg.activation_id(args.activation_fn),
-                                       args.memory_optimized_mlp, wgrad_scale=mlp.wgrad_scale())
-        return out, tokens_per_expert
+        return self.fused_parallel_forward_once(x, expert_weights, top_experts, mlp._grouped_view(w1),
+                                                mlp._grouped_view(w2), v1, w1_kn=False, expert_capacity=0)
 
     # -- dispatch --------------------------------------------------------------
     def forward_once(self, x, expert_weights, top_experts):

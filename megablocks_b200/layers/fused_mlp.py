@@ -28,14 +28,18 @@ from megablocks_b200.ops import gg as G
 
 
 def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tail: bool = True,
-                rows_hint: int = 0, scatter=None):
-    """Forward GEMMs.  Returns ``(y, saved)`` where ``saved = (z1, z2, h or None)``."""
+                rows_hint: int = 0, scatter=None, w1_kn: bool = False):
+    """Forward GEMMs.  Returns ``(y, saved)`` where ``saved = (z1, z2, h or None)``.
+
+    ``w1`` (and ``v1``) are ``[E, f, h]``, or ``[E, h, f]`` with ``w1_kn`` (the layout of the
+    token-dropping layer's experts); ``w2`` is ``[E, f, h]``.
+    """
     kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
     if v1 is not None:
-        z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=True, wait=wait, **kw)
-        z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=z1, **kw)
+        z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=not w1_kn, wait=wait, **kw)
+        z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=not w1_kn, epilogue=G.EPI_GLU, act=act, aux1=z1, **kw)
     else:
-        z1, h, _ = G.grouped_gemm(x, w1, bins, trans_b=True, epilogue=G.EPI_ACT, act=act, wait=wait, **kw)
+        z1, h, _ = G.grouped_gemm(x, w1, bins, trans_b=not w1_kn, epilogue=G.EPI_ACT, act=act, wait=wait, **kw)
         z2 = None
     # `scatter`: the last GEMM stores its rows straight into the peers' return buffers.
     y, _, _ = G.grouped_gemm(h, w2, bins, scatter=scatter, **kw)
@@ -43,7 +47,7 @@ def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tai
 
 
 def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zero_tail: bool = True,
-                 rows_hint: int = 0, scatter=None, wgrad_scale: float = 1.0):
+                 rows_hint: int = 0, scatter=None, wgrad_scale: float = 1.0, w1_kn: bool = False):
     """Backward GEMMs.  ``needs = (dx, dw1, dw2, dv1)`` flags; returns those four (``None`` where unneeded).
 
     ``wgrad_scale`` multiplies the weight gradients inside their GEMMs (the expert-parallel
@@ -64,18 +68,24 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
     dx = dw1 = dw2 = dv1 = None
     if needs[2]:
         dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
+    def wgrad(dz):      # [E, f, h] = dz^T x, or [E, h, f] = x^T dz for the [E, h, f] layout
+        a, b = (x, dz) if w1_kn else (dz, x)
+        return G.grouped_gemm(a, b, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)[0]
+
     if needs[1]:
-        dw1, _, _ = G.grouped_gemm(dz1, x, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
+        dw1 = wgrad(dz1)
     if v1 is not None and needs[3]:
-        dv1, _, _ = G.grouped_gemm(dz2, x, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
+        dv1 = wgrad(dz2)
     if needs[0]:
         # The GEMM that produces the final dx is the last reader of the receive buffers and, with
-        # `scatter`, also the one that returns the rows to their sources.
+        # `scatter`, also the one that returns the rows to their sources (the epilogue that does so
+        # exists for the NN layout; callers pass no `scatter` with `w1_kn`).
         if v1 is None:
-            dx, _, _ = G.grouped_gemm(dz1, w1, bins, scatter=scatter, **kw)
+            dx, _, _ = G.grouped_gemm(dz1, w1, bins, trans_b=w1_kn, scatter=scatter, **kw)
         else:
-            dx, _, _ = G.grouped_gemm(dz1, w1, bins, **kw)
-            dx, _, _ = G.grouped_gemm(dz2, v1, bins, epilogue=G.EPI_ADD, aux1=dx, scatter=scatter, **kw)
+            dx, _, _ = G.grouped_gemm(dz1, w1, bins, trans_b=w1_kn, **kw)
+            dx, _, _ = G.grouped_gemm(dz2, v1, bins, trans_b=w1_kn, epilogue=G.EPI_ADD, aux1=dx, scatter=scatter,
+                                      **kw)
     return dx, dw1, dw2, dv1
 
 

@@ -63,6 +63,12 @@ def batched_load_balancing_loss(args: Arguments) -> torch.Tensor:
     for scores, counts in zip(expert_scores, tokens_per_expert):
         assert scores.dim() == 2 and scores.shape == (tokens, args.moe_num_experts)
         assert counts.dim() == 1 and counts.shape[0] == args.moe_num_experts
+    scale = (args.moe_num_experts * args.moe_loss_weight) / (args.num_layers * tokens * args.moe_top_k)
+    from megablocks_b200.ops import fused
+    if tokens != 0 and fused.load_balancing_loss_supported(expert_scores, tokens_per_expert):
+        # CUDA: all layers in one reduction kernel (fp32 accumulation whatever `moe_lbl_in_fp32` says),
+        # nothing concatenated; the gradient is one broadcast kernel.
+        return fused.load_balancing_loss(list(expert_scores), list(tokens_per_expert), scale / tokens)
     # Column means layer by layer, then one concatenation of the [E] vectors: the same numbers as
     # reducing the concatenated [T, L * E] matrix, without materialising it.
     reduced = []
@@ -72,7 +78,6 @@ def batched_load_balancing_loss(args: Arguments) -> torch.Tensor:
         reduced.append(layer_scores.mean(dim=0) if tokens != 0 else layer_scores.sum(dim=0))
     scores = torch.cat(reduced)
     counts = torch.cat(tokens_per_expert).to(scores.dtype)
-    scale = (args.moe_num_experts * args.moe_loss_weight) / (args.num_layers * tokens * args.moe_top_k)
     return scale * torch.dot(counts, scores)
 
 
@@ -100,7 +105,8 @@ class ParallelMLP(torch.nn.Module):
             self.register_parameter('bias', None)
 
         self.forward_fn = self.parallel_forward_once if args.moe_expert_model_parallelism else self.forward_once
-        self._fused_ep = None
+        self._ep_workspaces = {}      # activation dtype -> ring of symmetric workspaces of the fused route
+        self._ep_calls = 0
 
     def _build_experts(self, args: Arguments) -> torch.nn.Module:
         return mlp.MLP(args)
@@ -156,8 +162,14 @@ class ParallelMLP(torch.nn.Module):
         rank ``r`` owns experts ``(r % esd) * epr ..`` and ffn rows
         ``(r // esd) * f/hsd ..``.
         """
-        if self._fused_ep is not None:
-            return self._fused_ep(self, x, expert_weights, top_experts)
+        if type(self).permute_and_compute is ParallelMLP.permute_and_compute and self._use_fused_ep(x):
+            # Token-dropping experts ([E, h, f] / [E, f, h] weights) over peer memory: the capacity rule
+            # of the binned gather is applied by the senders, which know every rank's counts.
+            from megablocks_b200.layers.mlp import resolve_dtensor
+            copies = top_experts.numel() * mpu.hidden_sharding_degree(self.args)
+            return self.fused_parallel_forward_once(x, expert_weights, top_experts, resolve_dtensor(self.mlp.w1),
+                                                    resolve_dtensor(self.mlp.w2), None, w1_kn=True,
+                                                    expert_capacity=self.expert_capacity(copies))
 
         args = self.args
         group = args.expert_parallel_group
@@ -213,6 +225,72 @@ class ParallelMLP(torch.nn.Module):
         x = ops.sum(x.view(hsd, -1, args.hidden_size), dim=0)
         x = ops.scatter(x, indices, bin_ids, expert_weights, bins, self.top_k)
         return x, tokens_per_expert.flatten()
+
+    # -- expert parallel over peer memory ----------------------------------------
+    def _use_fused_ep(self, x: torch.Tensor) -> bool:
+        want = self.args.ep_fused_comm
+        if want is False:
+            return False
+        from megablocks_b200.parallel import ep
+        ok = ep.fused_path_available(self.args, x)
+        if want is True and not ok:
+            raise RuntimeError('ep_fused_comm=True but the peer-memory route cannot serve this layer '
+                               '(needs CUDA 16-bit activations, a kernel-known activation, hidden and per-rank ffn '
+                               'multiples of 64)')
+        return ok
+
+    def fused_parallel_forward_once(self, x, expert_weights, top_experts, w1, w2, v1, w1_kn: bool,
+                                    expert_capacity: int):
+        """Expert-parallel forward over peer memory (``megablocks_b200.parallel.ep``).
+
+        ``w1`` is ``[E_local, f, h]`` (``w1_kn=False``, dropless layers) or ``[E_local, h, f]``
+        (``w1_kn=True``, the token-dropping layer); ``w2`` is ``[E_local, f, h]``.
+        ``expert_capacity`` > 0 keeps only the first that many rows every local expert receives,
+        counted over the sources in rank order - the rows the reference's binned gather keeps
+        (megablocks/layers/moe.py:374-401); the others contribute zeros.
+
+        More ranks than experts: every expert's ffn rows are split over ``hsd`` ranks (hidden
+        sharding, megablocks/layers/mpu.py:74-85).  Slice ``h`` of expert ``e`` is treated as the
+        virtual expert ``h * E + e``, which rank ``h * esd + e / epr`` owns; every routed copy goes
+        to all ``hsd`` slices of its expert, and the weighted combine, which sums all copies of a
+        token, adds the slices' partial outputs up.
+        """
+        from megablocks_b200.ops import gg
+        from megablocks_b200.parallel import ep
+        args = self.args
+        x2d = x.reshape(-1, x.shape[-1])
+        expert_weights = expert_weights.flatten()
+        hsd = mpu.hidden_sharding_degree(args)
+        top_k, num_virtual = self.top_k * hsd, self.num_experts * hsd
+        top_experts = top_experts.flatten()
+        if hsd > 1:
+            shift = torch.arange(hsd, device=top_experts.device, dtype=top_experts.dtype) * self.num_experts
+            top_experts = (top_experts.view(-1, 1) + shift).flatten()
+            expert_weights = expert_weights.view(-1, 1).expand(-1, hsd).flatten()
+        with torch.no_grad():
+            indices, bin_ids, bins, _, tokens_per_expert = ops.route_plan(top_experts, num_virtual)
+        copies = indices.numel()
+        ring = self._ep_workspaces.get(x2d.dtype)
+        if ring is None:
+            # Created once per activation dtype (a collective: every rank of the group gets here on
+            # its first call) and sized for the largest copy count over the group.
+            ring = [ep.EpWorkspace(args.expert_parallel_group, num_virtual,
+                                   max(copies, int(args.ep_max_copies or 0)), args.hidden_size, x2d.dtype,
+                                   x2d.device, capacity_rows=args.ep_capacity_rows)
+                    for _ in range(max(1, int(args.ep_inflight_microbatches)))]
+            self._ep_workspaces[x2d.dtype] = ring
+        workspace = ring[self._ep_calls % len(ring)]
+        self._ep_calls += 1
+        if copies > workspace.copies:
+            raise RuntimeError(
+                f'fused expert parallelism: this call routes {copies} copies but the symmetric buffers were sized '
+                f'for {workspace.copies}.  Set Arguments.ep_max_copies to the largest tokens x top_k of any rank '
+                '(the buffers cannot be regrown inside forward without a collective).')
+        out = ep.fused_expert_parallel(x2d, expert_weights.to(x2d.dtype), w1, w2, v1, workspace, indices, bin_ids,
+                                       bins, tokens_per_expert, top_k, gg.activation_id(args.activation_fn),
+                                       args.memory_optimized_mlp, wgrad_scale=self.mlp.wgrad_scale(), w1_kn=w1_kn,
+                                       expert_capacity=int(expert_capacity))
+        return out, tokens_per_expert[:self.num_experts]
 
     def forward(self, x: torch.Tensor, scores: torch.Tensor, expert_weights: torch.Tensor,
                 top_experts: torch.Tensor):

@@ -123,28 +123,13 @@ def preset(name: str, **overrides) -> TransformerConfig:
     return TransformerConfig(**cfg)
 
 
-class RMSNorm(nn.Module):
-
-    def __init__(self, dim: int, eps: float = 1e-5, device=None, dtype=None):
-        super().__init__()
-        self.eps = eps
-        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
-
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+RMSNorm = fused.RMSNorm
 
 
 def _rope_tables(seq_len: int, head_dim: int, theta: float, device):
     inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
     ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
-    return ang.cos(), ang.sin()
-
-
-def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    # x: [batch, heads, seq, head_dim]; rotate pairs (i, i + d/2).
-    d = x.shape[-1] // 2
-    x1, x2 = x[..., :d].float(), x[..., d:].float()
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+    return ang.cos().contiguous(), ang.sin().contiguous()
 
 
 class Attention(nn.Module):
@@ -170,11 +155,12 @@ class Attention(nn.Module):
         qkv = self.qkv(x)
         q_dim, kv_dim = cfg.num_heads * self.head_dim, cfg.kv_heads * self.head_dim
         q, k, v = qkv.split([q_dim, kv_dim, kv_dim], dim=-1)
-        q = q.view(b, s, cfg.num_heads, self.head_dim).transpose(1, 2)
-        k = k.view(b, s, cfg.kv_heads, self.head_dim).transpose(1, 2)
+        q = q.view(b, s, cfg.num_heads, self.head_dim)
+        k = k.view(b, s, cfg.kv_heads, self.head_dim)
+        if rope is not None:     # rotate the [batch, seq, heads, dim] views of the fused projection in one pass each
+            q, k = fused.rope(q, *rope), fused.rope(k, *rope)
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
         v = v.view(b, s, cfg.kv_heads, self.head_dim).transpose(1, 2)
-        if rope is not None:
-            q, k = _apply_rope(q, *rope), _apply_rope(k, *rope)
         out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=cfg.kv_heads != cfg.num_heads)
         return self.proj(out.transpose(1, 2).reshape(b, s, -1))
 

@@ -9,6 +9,13 @@
 * :func:`layer_norm` - LayerNorm whose backward reduces the weight and bias
   gradients through shared memory in the same pass that produces ``dx``.
 
+* :func:`rms_norm` / :class:`RMSNorm` - the same kernels without centring and bias (Mixtral-style
+  models), including the fused residual add.
+* :func:`rope` - rotary position embedding of ``[batch, heads, seq, head_dim]`` queries / keys in
+  one pass (rotation of the pairs ``(i, i + d/2)`` in fp32, no fp32 copies of the tensor).
+* :func:`load_balancing_loss` - the auxiliary loss of all layers in one reduction kernel and its
+  gradient in one broadcast kernel.
+
 * :func:`linear` / :class:`Linear` - ``nn.Linear`` whose bias gradient is one column-sum kernel
   at memory bandwidth (the library route reduces the same tensor at a third of that).
 
@@ -60,7 +67,7 @@ class _LayerNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx: Any, dy: torch.Tensor):
         x2, weight, mean, rstd = ctx.saved_tensors
-        dx, dw, db = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd, None)
+        dx, dw, db = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd, None, False)
         return dx.view(ctx.shape), dw, db, None
 
 
@@ -83,7 +90,7 @@ class _AddLayerNorm(torch.autograd.Function):
         if dy is None:
             return ds, ds, None, None, None
         dres = ds.reshape(s.shape).contiguous() if ds is not None else None
-        dx, dw, db = ext().layernorm_backward(dy.reshape(s.shape).contiguous(), s, weight, mean, rstd, dres)
+        dx, dw, db = ext().layernorm_backward(dy.reshape(s.shape).contiguous(), s, weight, mean, rstd, dres, False)
         dx = dx.view(ctx.shape)
         return dx, dx, dw, db, None
 
@@ -120,6 +127,155 @@ class LayerNorm(torch.nn.LayerNorm):
     def add_forward(self, a: torch.Tensor, b):
         """``(a + b, self(a + b))`` with the add fused into the kernels; ``b`` may be ``None``."""
         return add_layer_norm(a, b, self.weight, self.bias, self.eps)
+
+
+class _RMSNorm(torch.autograd.Function):
+    """``y = x * rsqrt(mean(x^2) + eps) * weight`` on the LayerNorm kernels (no centring, no bias)."""
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, eps: float):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, None, eps, None)
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.shape = shape
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor):
+        x2, weight, mean, rstd = ctx.saved_tensors
+        dx, dw, _ = ext().layernorm_backward(dy.reshape(x2.shape).contiguous(), x2, weight, mean, rstd, None, True)
+        return dx.view(ctx.shape), dw, None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """``s = a + b; y = RMSNorm(s)`` in one pass; the backward adds ``ds`` while it writes ``dx``."""
+
+    @staticmethod
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, weight: torch.Tensor, eps: float):
+        shape = a.shape
+        a2 = a.reshape(-1, shape[-1]).contiguous()
+        b2 = b.reshape(-1, shape[-1]).contiguous()
+        y, mean, rstd, s = ext().layernorm_forward(a2, weight, None, eps, b2)
+        ctx.save_for_backward(s, weight, mean, rstd)
+        ctx.shape = shape
+        return s.view(shape), y.view(shape)
+
+    @staticmethod
+    def backward(ctx: Any, ds, dy):
+        s, weight, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return ds, ds, None, None
+        dres = ds.reshape(s.shape).contiguous() if ds is not None else None
+        dx, dw, _ = ext().layernorm_backward(dy.reshape(s.shape).contiguous(), s, weight, mean, rstd, dres, True)
+        dx = dx.view(ctx.shape)
+        return dx, dx, dw, None
+
+
+def _norm_kernel_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    cols = x.shape[-1]
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and weight.dtype == x.dtype
+            and (cols * x.element_size()) % 16 == 0 and cols <= 6144)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    if _norm_kernel_ok(x, weight):
+        return _RMSNorm.apply(x, weight, eps)
+    return F.rms_norm(x, (x.shape[-1],), weight, eps)
+
+
+def add_rms_norm(a: torch.Tensor, b, weight: torch.Tensor, eps: float = 1e-5):
+    """``(a + b, RMSNorm(a + b))``; ``b`` may be ``None``.  On CUDA the add rides in the norm's kernels."""
+    if b is None:
+        return a, rms_norm(a, weight, eps)
+    cols = a.shape[-1]
+    fused = (a.is_cuda and b.is_cuda and a.dtype == b.dtype == weight.dtype and a.shape == b.shape
+             and a.dtype in (torch.bfloat16, torch.float16, torch.float32)
+             and ext().layernorm_can_fuse(a.reshape(-1, cols)))
+    if fused:
+        return _AddRMSNorm.apply(a, b, weight, eps)
+    s = a + b
+    return s, rms_norm(s, weight, eps)
+
+
+class RMSNorm(torch.nn.Module):
+    """Root-mean-square norm (weight only) running the fused kernels on CUDA."""
+
+    def __init__(self, dim: int, eps: float = 1e-5, device=None, dtype=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = torch.nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return rms_norm(x, self.weight, self.eps)
+
+    def add_forward(self, a: torch.Tensor, b):
+        return add_rms_norm(a, b, self.weight, self.eps)
+
+
+class _Rope(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        ctx.save_for_backward(cos, sin)
+        return ext().rope(x, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx: Any, dy: torch.Tensor):
+        cos, sin = ctx.saved_tensors
+        if dy.stride(-1) != 1:
+            dy = dy.contiguous()
+        return ext().rope(dy, cos, sin, True), None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x[batch, seq, heads, dim]`` (any strides with a unit one in ``dim``) with
+    fp32 tables ``cos`` / ``sin`` of shape ``[seq, dim / 2]``; pairs are ``(i, i + dim / 2)``.
+    Returns a contiguous tensor."""
+    d = x.shape[-1]
+    elem = x.element_size()
+    ok = (x.is_cuda and x.dim() == 4 and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
+          and x.stride(-1) == 1 and d % (2 * (16 // elem)) == 0 and x.data_ptr() % 16 == 0
+          and all((st * elem) % 16 == 0 for st in x.stride()[:3]) and cos.dtype == torch.float32)
+    if ok:
+        return _Rope.apply(x, cos.contiguous(), sin.contiguous())
+    half = d // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    c, s = cos[:x.shape[1]].unsqueeze(1), sin[:x.shape[1]].unsqueeze(1)     # [seq, 1, dim / 2]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+class _LoadBalancingLoss(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, scale: float, layers: int, *tensors):
+        scores, counts = list(tensors[:layers]), list(tensors[layers:])
+        ctx.scale, ctx.layers = scale, layers
+        ctx.save_for_backward(*tensors)
+        return ext().lbl_forward(scores, counts, scale)
+
+    @staticmethod
+    def backward(ctx: Any, gout: torch.Tensor):
+        tensors = ctx.saved_tensors
+        scores, counts = list(tensors[:ctx.layers]), list(tensors[ctx.layers:])
+        grads = ext().lbl_backward(scores, counts, ctx.scale, gout.detach().float().reshape(1).contiguous())
+        return (None, None) + tuple(grads) + (None,) * ctx.layers
+
+
+def load_balancing_loss_supported(scores, counts) -> bool:
+    first = scores[0]
+    return (len(scores) <= 64 and all(s.is_cuda and s.is_contiguous() and s.dim() == 2 and s.shape == first.shape
+                                      and s.dtype == first.dtype for s in scores)
+            and first.dtype in (torch.bfloat16, torch.float16, torch.float32) and first.shape[0] > 0
+            and all(c.is_cuda and c.dtype == torch.int32 and c.is_contiguous() for c in counts))
+
+
+def load_balancing_loss(scores, counts, scale: float) -> torch.Tensor:
+    """``scale * sum_l <counts[l], column sums of scores[l]>`` over the layers, as one fp32 scalar.
+
+    One reduction kernel forward (fp32 accumulation, deterministic), one broadcast kernel backward.
+    """
+    return _LoadBalancingLoss.apply(float(scale), len(scores), *scores, *counts)
 
 
 class _Linear(torch.autograd.Function):

@@ -17,9 +17,18 @@ weights with ``expert_model_parallel`` so that trainer can skip them
 
 Buckets are sized for launch latency and overlap (NVSwitch gives every pair of
 GPUs full bandwidth, so there is no per-link reason to make them large).
+
+Two backends move the bytes.  ``'peer'`` (the default on CUDA when every rank of the
+group can map its peers' memory): the gradient buffer lives in a symmetric heap and one
+kernel of this library per bucket (``csrc/dp_comm.cu``) reduces it with peer loads and
+stores over NVLink - ready flags, a reduce of the rank's own slice, stores into every
+rank's slice, done flags - without any NCCL call.  ``'nccl'``: ``all_reduce`` /
+``reduce_scatter_tensor``, kept as the baseline and for CPU (gloo) ranks.
 """
 
 from typing import List, Optional, Sequence
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -61,7 +70,7 @@ class GradReducer:
     """Bucketed gradient collective launched from backward hooks on a side stream."""
 
     def __init__(self, flat: FlatBuffer, group: Optional[dist.ProcessGroup], bucket_bytes: int = 32 << 20,
-                 shard: bool = False):
+                 shard: bool = False, backend: str = 'auto', ctas: int = 16):
         self.flat, self.group, self.shard = flat, group, shard
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -94,8 +103,49 @@ class GradReducer:
         # With gradient accumulation only the last micro-batch's backward may start the collectives:
         # the trainer clears `active` for the earlier ones.
         self.active = True
+        self.backend = self._pick_backend(backend)
+        self.ctas = int(ctas)
+        self.seq = 0
+        if self.backend == 'peer':
+            self._init_peer()
         for i, p in enumerate(flat.params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
+
+    # -- peer-memory backend -------------------------------------------------------
+    def _pick_backend(self, backend: str) -> str:
+        if backend not in ('auto', 'peer', 'nccl'):
+            raise ValueError(f"backend must be 'auto', 'peer' or 'nccl', got {backend!r}")
+        backend = os.environ.get('MB200_DP_BACKEND', backend)
+        usable = self.flat.grad.is_cuda and self.flat.grad.dtype in (torch.bfloat16, torch.float16, torch.float32)
+        if backend == 'peer' and not usable:
+            raise RuntimeError("the 'peer' gradient reducer needs CUDA gradients")
+        if backend == 'auto':
+            backend = 'peer' if usable else 'nccl'
+        return backend
+
+    def _init_peer(self) -> None:
+        """Re-home the gradient buffer in a symmetric heap that every rank of the group maps."""
+        from megablocks_b200.parallel.ep import SymmetricHeap
+        flat = self.flat
+        grad_bytes = _align(flat.numel * flat.grad.element_size(), 256)
+        flag_bytes = _align(len(self.buckets) * self.world * 4, 256)
+        self._off_grad, self._off_ready, self._off_done = 0, grad_bytes, grad_bytes + flag_bytes
+        self._heap = SymmetricHeap(self.group, grad_bytes + 2 * flag_bytes, flat.grad.device)
+        self._heap.local.zero_()
+        new_grad = self._heap.view(0, (flat.numel,), flat.grad.dtype)
+        new_grad.copy_(flat.grad)
+        flat.grad = new_grad
+        flat.zero_grad()                       # re-attaches every p.grad view to the new storage
+        self._tickets = torch.zeros(len(self.buckets), dtype=torch.int32, device=flat.grad.device)
+        torch.cuda.synchronize(flat.grad.device)
+        dist.barrier(self.group)               # nobody launches before every heap is zeroed
+
+    def _launch_peer(self, bi: int) -> None:
+        from megablocks_b200._ext import ext
+        s, e = self.buckets[bi][:2]
+        ext().dp_allreduce(self.flat.grad, self._heap.peer_base, self.world, self.rank, self._off_grad,
+                           self._off_ready, self._off_done, s, e - s, bi, self.seq, 1.0 / self.world, self.shard,
+                           self._tickets[bi:bi + 1], self.ctas)
 
     # -- shard geometry (ZeRO-1) --------------------------------------------------
     def shard_range(self, bucket: int):
@@ -116,6 +166,8 @@ class GradReducer:
     def _launch(self, bi: int) -> None:
         if self._launched[bi]:
             return
+        if self.backend == 'peer' and not any(self._launched):
+            self.seq += 1        # first bucket of this step
         self._launched[bi] = True
         s, e = self.buckets[bi][:2]
         grad = self.flat.grad[s:e]
@@ -125,7 +177,9 @@ class GradReducer:
         else:
             ctx = _NullContext()
         with ctx:
-            if self.shard and grad.is_cuda:
+            if self.backend == 'peer':
+                self._launch_peer(bi)
+            elif self.shard and grad.is_cuda:
                 lo, hi = self.shard_range(bi)
                 out = self.flat.grad[lo:hi]
                 work = dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG, group=self.group, async_op=True)

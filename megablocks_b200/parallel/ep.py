@@ -142,43 +142,54 @@ class EpWorkspace:
         return self.seq
 
     # -- steps ----------------------------------------------------------------------------
-    def exchange_counts(self, tpe: torch.Tensor, seq: int):
+    def exchange_counts(self, tpe: torch.Tensor, seq: int, expert_capacity: int = 0):
         """All-gather of the per-expert copy counts by remote stores.
 
-        Returns ``(counts[world * experts], recv_bins[experts_per_rank], done)`` where
-        ``done`` holds the zeroed completion counters of this call's four push / return kernels.
+        Returns ``(counts, recv_bins[experts_per_rank], done)``: ``counts = (kept, routed)``, two
+        ``[world * experts]`` matrices - the copies every (rank, expert) pair routed and those that
+        survive ``expert_capacity`` rows per expert (0 = no limit: the same numbers) - and ``done``,
+        the zeroed completion counters of this call's four push / return kernels.
         """
         E, W = self.num_experts, self.world
-        counts = torch.empty(W * E, dtype=torch.int32, device=self.device)
+        routed = torch.empty(W * E, dtype=torch.int32, device=self.device)
+        kept = torch.empty(W * E, dtype=torch.int32, device=self.device)
         recv_bins = torch.empty(self.epr, dtype=torch.int32, device=self.device)
         scratch = torch.empty(2 * E + 2 * W, dtype=torch.int32, device=self.device)
-        ext().ep_exchange_counts(tpe, *self._layout(), seq, counts, recv_bins, scratch)
+        ext().ep_exchange_counts(tpe, *self._layout(), seq, int(expert_capacity), routed, kept, recv_bins, scratch)
         done = (scratch[:E], scratch[2 * E:2 * E + W], scratch[E:2 * E], scratch[2 * E + W:])
-        return counts, recv_bins, done
+        return (kept, routed), recv_bins, done
 
-    def push(self, x, indices, weights, bins, counts, direction: int, seq: int, top_k: int, done):
-        """Store my routed copies of ``x`` into the owners' receive buffers (0 = forward, 1 = backward)."""
+    def push(self, x, indices, weights, bins, counts, direction: int, seq: int, top_k: int, done,
+             drops: bool = False):
+        """Store my routed copies of ``x`` into the owners' receive buffers (0 = forward, 1 = backward).
+
+        With ``drops`` (a capacity limit is on) the return-buffer rows of the copies that are not
+        sent are cleared, since no owner will write them.
+        """
+        kept = counts[0]
         if direction == 0:
-            ext().ep_push_rows(x, indices, weights, bins, counts, *self._layout(), self.heap.peer_base,
-                               self.off_recv_x, self.off_disp_flags[0], self.off_free, seq, top_k, done)
+            ext().ep_push_rows(x, indices, weights, bins, kept, *self._layout(), self.heap.peer_base,
+                               self.off_recv_x, self.off_disp_flags[0], self.off_free, seq, top_k, done,
+                               self.ret_y if drops else None)
         else:
-            ext().ep_push_rows(x, indices, weights, bins, counts, *self._layout(), self.bwd_heap.peer_base,
-                               self.off_recv_dy, self.off_disp_flags[1], -1, seq, top_k, done)
+            ext().ep_push_rows(x, indices, weights, bins, kept, *self._layout(), self.bwd_heap.peer_base,
+                               self.off_recv_dy, self.off_disp_flags[1], -1, seq, top_k, done,
+                               self.ret_dx if drops else None)
 
     def return_rows(self, y, counts, direction: int, seq: int, done):
         """Store my expert-ordered rows ``y`` back into the sources' sorted order."""
         if direction == 0:
-            ext().ep_return_rows(y, counts, *self._layout(), self.heap.peer_base, self.off_ret_y,
+            ext().ep_return_rows(y, counts[0], counts[1], *self._layout(), self.heap.peer_base, self.off_ret_y,
                                  self.off_ret_flags[0], seq, self.copies, done)
         else:
-            ext().ep_return_rows(y, counts, *self._layout(), self.bwd_heap.peer_base, self.off_ret_dx,
+            ext().ep_return_rows(y, counts[0], counts[1], *self._layout(), self.bwd_heap.peer_base, self.off_ret_dx,
                                  self.off_ret_flags[1], seq, self.copies, done)
 
     def scatter_args(self, counts, direction: int, seq: int, done):
         """``scatter`` argument of the grouped GEMM: return the output rows to their sources from the epilogue."""
         heap = self.heap if direction == 0 else self.bwd_heap
         off = self.off_ret_y if direction == 0 else self.off_ret_dx
-        return ([heap.peer_base, self.heap.peer_base, counts, done],
+        return ([heap.peer_base, self.heap.peer_base, counts[0], done, counts[1]],
                 [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq, self.copies])
 
     def fuse_combine(self) -> bool:
@@ -220,18 +231,19 @@ class _FusedExpertParallel(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, x, expert_weights, w1, w2, v1, ws: EpWorkspace, indices, bin_ids, bins, tpe, top_k: int,
-                act: int, keep_h: bool, wgrad_scale: float = 1.0):
+                act: int, keep_h: bool, wgrad_scale: float = 1.0, w1_kn: bool = False, expert_capacity: int = 0):
         seq = ws.next_seq()
         ws.begin_use(seq)
         x = x.contiguous()
         tokens = x.shape[0]
+        drops = expert_capacity > 0
         with comm_timer.region(), nvtx_range('ep.dispatch'):
-            counts, recv_bins, done = ws.exchange_counts(tpe, seq)
-            ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0])
+            counts, recv_bins, done = ws.exchange_counts(tpe, seq, expert_capacity)
+            ws.push(x, indices, None, bins, counts, 0, seq, top_k, done[0], drops)
         fuse = ws.fuse_combine()
         y, saved = mlp_forward(ws.recv_x, w1, w2, v1, recv_bins, act, keep_h, wait=ws.arrival(0, seq),
                                zero_tail=False, rows_hint=ws.copies,
-                               scatter=ws.scatter_args(counts, 0, seq, done[1]) if fuse else None)
+                               scatter=ws.scatter_args(counts, 0, seq, done[1]) if fuse else None, w1_kn=w1_kn)
         with comm_timer.region(), nvtx_range('ep.combine_wait'):
             if not fuse:
                 ws.return_rows(y, counts, 0, seq, done[1])
@@ -242,7 +254,8 @@ class _FusedExpertParallel(torch.autograd.Function):
         if not will_backward:
             ws.release_receive_buffer(seq)
         z1, z2, h = saved
-        tensors = [expert_weights, w1, w2, indices, bin_ids, bins, counts, recv_bins, z1, done[2], done[3]]
+        tensors = [expert_weights, w1, w2, indices, bin_ids, bins, counts[0], counts[1], recv_bins, z1, done[2],
+                   done[3]]
         ctx.glu = v1 is not None
         ctx.keep_h = h is not None
         if ctx.glu:
@@ -251,7 +264,7 @@ class _FusedExpertParallel(torch.autograd.Function):
             tensors.append(h)
         ctx.save_for_backward(*tensors)
         ctx.ws, ctx.seq, ctx.top_k, ctx.act, ctx.tokens = ws, seq, top_k, act, tokens
-        ctx.wgrad_scale = wgrad_scale
+        ctx.wgrad_scale, ctx.w1_kn, ctx.drops = wgrad_scale, w1_kn, drops
         ctx.mark_non_differentiable()
         return out
 
@@ -267,16 +280,17 @@ class _FusedExpertParallel(torch.autograd.Function):
                 'forward-forward-backward-backward accumulation, retain_graph): raise '
                 'Arguments.ep_inflight_microbatches to their number or set ep_fused_comm=False.')
         saved = list(ctx.saved_tensors)
-        expert_weights, w1, w2, indices, bin_ids, bins, counts, recv_bins, z1, done_push, done_ret = saved[:11]
+        expert_weights, w1, w2, indices, bin_ids, bins, kept, routed, recv_bins, z1, done_push, done_ret = saved[:12]
+        counts = (kept, routed)
         v1 = z2 = None
         if ctx.glu:
-            v1, z2 = saved[11:13]
+            v1, z2 = saved[12:14]
         h = saved[-1] if ctx.keep_h else None
         dout = dout.contiguous()
-        fuse = ws.fuse_combine()
+        fuse = ws.fuse_combine() and not ctx.w1_kn      # the dx GEMM of the [E, h, f] layout is NT: no fused return
         # d(out)/d(expert rows): each copy's gradient is its token's gradient times its router weight.
         with comm_timer.region(), nvtx_range('ep.dispatch_grad'):
-            ws.push(dout, indices, expert_weights, bins, counts, 1, seq, top_k, done_push)
+            ws.push(dout, indices, expert_weights, bins, counts, 1, seq, top_k, done_push, ctx.drops)
         dweights = None
         if ctx.needs_input_grad[1]:
             dweights = ext().scatter_wgrad(ws.ret_y, dout, indices, bin_ids, bins, bins, top_k)
@@ -286,7 +300,7 @@ class _FusedExpertParallel(torch.autograd.Function):
                                           (True,) + needs[1:], wait=ws.arrival(1, seq), zero_tail=False,
                                           rows_hint=ws.copies,
                                           scatter=ws.scatter_args(counts, 1, seq, done_ret) if fuse else None,
-                                          wgrad_scale=ctx.wgrad_scale)
+                                          wgrad_scale=ctx.wgrad_scale, w1_kn=ctx.w1_kn)
         # Every read of both receive buffers is enqueued above; only now may peers learn
         # (through the return flags / the free flag) that they can be overwritten.
         with comm_timer.region(), nvtx_range('ep.combine_grad_wait'):
@@ -297,17 +311,21 @@ class _FusedExpertParallel(torch.autograd.Function):
         dx = None
         if needs[0]:
             dx = ext().scatter_rows(ws.ret_dx, indices, bin_ids, None, bins, bins, top_k, ctx.tokens)
-        return dx, dweights, dw1, dw2, dv1, None, None, None, None, None, None, None, None, None
+        return (dx, dweights, dw1, dw2, dv1) + (None,) * 11
 
 
 def fused_expert_parallel(x, expert_weights, w1, w2, v1, workspace: EpWorkspace, indices, bin_ids, bins, tpe,
-                          top_k: int, act: int, memory_optimized: bool, wgrad_scale: float = 1.0) -> torch.Tensor:
+                          top_k: int, act: int, memory_optimized: bool, wgrad_scale: float = 1.0,
+                          w1_kn: bool = False, expert_capacity: int = 0) -> torch.Tensor:
     """``x[tokens, hidden]`` -> ``out[tokens, hidden]`` through the expert-parallel group of ``workspace``.
 
-    The gradients of ``w1`` / ``w2`` / ``v1`` come out multiplied by ``wgrad_scale``.
+    The gradients of ``w1`` / ``w2`` / ``v1`` come out multiplied by ``wgrad_scale``.  ``w1_kn``:
+    ``w1`` is ``[E, h, f]`` instead of ``[E, f, h]``.  ``expert_capacity`` > 0 drops every copy past
+    that many rows per expert (counted over the sources in rank order); dropped copies contribute
+    zeros, forward and backward.
     """
     return _FusedExpertParallel.apply(x, expert_weights, w1, w2, v1, workspace, indices, bin_ids, bins, tpe, top_k,
-                                      act, not memory_optimized, wgrad_scale)
+                                      act, not memory_optimized, wgrad_scale, w1_kn, expert_capacity)
 
 
 def fused_path_available(args, x: torch.Tensor) -> bool:
@@ -319,7 +337,10 @@ def fused_path_available(args, x: torch.Tensor) -> bool:
     if gg.activation_id(args.activation_fn) is None:
         return False
     world = mpu.get_expert_parallel_world_size(args)
-    if world < 2 or world > args.moe_num_experts or args.moe_num_experts % world:
+    experts = args.moe_num_experts
+    if world < 2 or (world <= experts and experts % world) or (world > experts and world % experts):
+        return False
+    if world > experts and args.ffn_hidden_size % (world // experts):
         return False
     if args.hidden_size % 64 or mpu.features_per_rank(args) % 64:
         return False

@@ -39,6 +39,9 @@ class TrainerConfig:
     warmup_fraction: float = 0.01
     zero1: bool = False              # shard optimizer state of the replicated parameters
     bucket_mb: int = 32
+    # Data-parallel gradient reduction: 'peer' = this library's kernel over NVLink peer memory,
+    # 'nccl' = library collectives, 'auto' = peer on CUDA, nccl otherwise.
+    dp_backend: str = 'auto'
     schedule: bool = True
     # Run the (bandwidth-bound) Adam update of the expert weights on a side stream, layer by layer,
     # while the next step's forward already runs; every MoE layer waits for its own weights only.
@@ -97,7 +100,8 @@ class Trainer:
             else None
         if self.world > 1:
             self.flat = FlatBuffer(self.dense_params, granule=self.world * 8)
-            self.reducer = GradReducer(self.flat, dp_group, cfg.bucket_mb << 20, shard=cfg.zero1)
+            self.reducer = GradReducer(self.flat, dp_group, cfg.bucket_mb << 20, shard=cfg.zero1,
+                                       backend=cfg.dp_backend)
         if self.world > 1 and cfg.zero1:
             # One optimizer "tensor" per owned bucket slice; disjoint across ranks.
             self._shard_params, self._shard_grads = [], []
@@ -366,6 +370,8 @@ def main(argv=None):
     ap.add_argument('--defer-expert-update', action='store_true',
                     help='run the expert Adam update on a side stream, layer by layer, under the next forward')
     ap.add_argument('--ep-comm', choices=['auto', 'fused', 'nccl'], default='auto')
+    ap.add_argument('--dp-comm', choices=['auto', 'peer', 'nccl'], default='auto',
+                    help='gradient reduction of the replicated parameters: own peer-memory kernel or NCCL')
     ap.add_argument('--log', type=str, default=None, help='JSONL metrics file')
     ap.add_argument('--log-interval', type=int, default=10)
     ap.add_argument('--save', type=str, default=None, help='checkpoint directory')
@@ -430,7 +436,7 @@ def main(argv=None):
     if pp > 1:
         stage = PipelineStage(pp_group, (args.micro_batch, cfg.max_seq_len, cfg.hidden_size), cfg.dtype, device)
     trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1,
-                                           overlap_expert_update=args.defer_expert_update,
+                                           overlap_expert_update=args.defer_expert_update, dp_backend=args.dp_comm,
                                            grad_accum_steps=accum, optimizer=args.optimizer),
                       dp_group=group, pipeline=stage)
     if args.load:

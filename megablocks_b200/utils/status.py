@@ -20,6 +20,8 @@ _MESSAGES = {
     18: 'grouped GEMM: rows of an expert never arrived from a peer (dispatch flag not released)',
     19: 'expert-parallel combine: a peer never returned its rows',
     20: 'expert-parallel dispatch: a peer never released its receive buffer',
+    32: 'data-parallel gradient reduction: a peer never announced its bucket',
+    33: 'data-parallel gradient reduction: a peer never finished reading or writing a bucket',
 }
 
 

@@ -104,3 +104,101 @@ def test_linear_bias_gradient(device, rows, cin, cout):
     torch.testing.assert_close(lin.bias.grad.float().cpu(), br.grad, **scale)
     wscale = dict(rtol=2e-2, atol=2e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
     torch.testing.assert_close(lin.weight.grad.float().cpu(), wr.grad, **wscale)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,cols', [(1000, 768), (77, 1024), (300, 4096), (64, 128)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_rms_norm_and_fused_add(device, rows, cols, dtype):
+    """RMS norm (and the residual-add form) forward and backward against the fp32 formula."""
+    norm = fused.RMSNorm(cols, eps=1e-5).to(device=device, dtype=dtype)
+    with torch.no_grad():
+        norm.weight.copy_(torch.randn(cols) * 0.5 + 1)
+    a = (torch.randn(rows, cols) * 2 + 0.3).to(dtype).to(device).requires_grad_(True)
+    b = torch.randn(rows, cols).to(dtype).to(device).requires_grad_(True)
+    p1 = torch.randn(rows, cols).to(dtype).to(device)
+    p2 = torch.randn(rows, cols).to(dtype).to(device)
+
+    def ref_norm(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * w
+
+    tol = dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    y = norm(a)
+    (y.float() * p1.float()).sum().backward()
+    ar = a.detach().float().cpu().requires_grad_(True)
+    wr = norm.weight.detach().float().cpu().requires_grad_(True)
+    (ref_norm(ar, wr) * p1.float().cpu()).sum().backward()
+    torch.testing.assert_close(y.detach().float().cpu(), ref_norm(ar, wr).detach(), **tol)
+    torch.testing.assert_close(a.grad.float().cpu(), ar.grad, **tol)
+    wtol = dict(rtol=3e-2, atol=3e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(norm.weight.grad.float().cpu(), wr.grad, **wtol)
+
+    # (a + b, norm(a + b)) with gradients arriving on both outputs.
+    a.grad = None
+    norm.weight.grad = None
+    s, y = norm.add_forward(a, b)
+    ((y.float() * p1.float()).sum() + (s.float() * p2.float()).sum()).backward()
+    ar = a.detach().float().cpu().requires_grad_(True)
+    br = b.detach().float().cpu().requires_grad_(True)
+    sr = (ar + br).to(dtype).float() if dtype == torch.bfloat16 else ar + br
+    sr_live = ar + br
+    ((ref_norm(sr_live, wr.detach()) * p1.float().cpu()).sum() + (sr_live * p2.float().cpu()).sum()).backward()
+    torch.testing.assert_close(s.detach().float().cpu(), sr.detach(), **tol)
+    torch.testing.assert_close(a.grad.float().cpu(), ar.grad, **tol)
+    torch.testing.assert_close(b.grad.float().cpu(), br.grad, **tol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('batch,seq,heads,dim', [(2, 64, 4, 32), (1, 300, 8, 128), (3, 17, 2, 64)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_rope(device, batch, seq, heads, dim, dtype):
+    """Rotary embedding of a strided [batch, seq, heads, dim] view (a slice of a fused projection)."""
+    qkv = torch.randn(batch, seq, 3 * heads * dim).to(dtype).to(device).requires_grad_(True)
+    inv = 1.0 / (10000.0**(torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    ang = torch.outer(torch.arange(seq, dtype=torch.float32), inv)
+    cos, sin = ang.cos().to(device), ang.sin().to(device)
+    k = qkv[..., heads * dim:2 * heads * dim].view(batch, seq, heads, dim)      # non-contiguous view
+    out = fused.rope(k, cos, sin)
+    probe = torch.randn(batch, seq, heads, dim).to(dtype).to(device)
+    (out.float() * probe.float()).sum().backward()
+
+    ref_in = qkv.detach().float().cpu().requires_grad_(True)
+    kr = ref_in[..., heads * dim:2 * heads * dim].view(batch, seq, heads, dim)
+    half = dim // 2
+    c, s = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    ref = torch.cat([kr[..., :half] * c - kr[..., half:] * s, kr[..., half:] * c + kr[..., :half] * s], dim=-1)
+    (ref * probe.float().cpu()).sum().backward()
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(out.detach().float().cpu(), ref.detach(), **tol)
+    torch.testing.assert_close(qkv.grad.float().cpu(), ref_in.grad, **tol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('layers,tokens,experts,top_k', [(1, 64, 8, 1), (12, 4096, 64, 1), (3, 1000, 48, 2),
+                                                         (2, 300, 512, 4)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_batched_load_balancing_loss(device, layers, tokens, experts, top_k, dtype):
+    """All layers' auxiliary loss (one reduction kernel on CUDA) against the concatenated fp32 formula."""
+    import megablocks_b200 as mb
+    from megablocks_b200.layers import moe
+    args = mb.Arguments(hidden_size=64, ffn_hidden_size=64, num_layers=layers, moe_num_experts=experts, moe_top_k=top_k,
+                        moe_loss_weight=0.1, moe_lbl_in_fp32=True, device=torch.device(device))
+    scores = [torch.softmax(torch.randn(tokens, experts), -1).to(dtype).to(device).requires_grad_(True)
+              for _ in range(layers)]
+    counts = [torch.bincount(torch.randint(0, experts, (tokens * top_k,)), minlength=experts).int().to(device)
+              for _ in range(layers)]
+    moe.clear_load_balancing_loss()
+    for c, s in zip(counts, scores):
+        moe.save_load_balancing_loss((c, s))
+    loss = moe.batched_load_balancing_loss(args)
+    (loss * 3.0).backward()
+    moe.clear_load_balancing_loss()
+
+    ref_scores = [s.detach().float().cpu().requires_grad_(True) for s in scores]
+    cat_scores = torch.cat(ref_scores, dim=1).mean(dim=0)
+    cat_counts = torch.cat([c.cpu() for c in counts]).float()
+    ref = experts * 0.1 / (layers * tokens * top_k) * torch.dot(cat_counts, cat_scores)
+    (ref * 3.0).backward()
+    torch.testing.assert_close(loss.detach().float().cpu(), ref.detach(), rtol=1e-3, atol=1e-6)
+    for s, r in zip(scores, ref_scores):
+        torch.testing.assert_close(s.grad.float().cpu(), r.grad, rtol=1e-2, atol=1e-9)
