@@ -41,23 +41,37 @@ def import_reference():
     return Arguments, dmoe, moe
 
 
-class RefAttention(nn.Module):
+def _rope(x, cos, sin):
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d].float(), x[..., d:].float()
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
-    def __init__(self, hidden, heads, layers, device, dtype):
+
+class RefAttention(nn.Module):
+    """Multi-head (GPT-2) or grouped-query attention with rotary positions (Mixtral flavour)."""
+
+    def __init__(self, hidden, heads, layers, device, dtype, kv_heads=None, bias=True):
         super().__init__()
-        self.heads = heads
-        self.qkv = nn.Linear(hidden, 3 * hidden, device=device, dtype=dtype)
-        self.proj = nn.Linear(hidden, hidden, device=device, dtype=dtype)
+        self.heads, self.kv_heads = heads, kv_heads or heads
+        self.head_dim = hidden // heads
+        self.qkv = nn.Linear(hidden, (heads + 2 * self.kv_heads) * self.head_dim, bias=bias, device=device, dtype=dtype)
+        self.proj = nn.Linear(hidden, hidden, bias=bias, device=device, dtype=dtype)
         nn.init.normal_(self.qkv.weight, std=0.02)
         nn.init.normal_(self.proj.weight, std=0.02 / math.sqrt(2.0 * layers))
-        nn.init.zeros_(self.qkv.bias)
-        nn.init.zeros_(self.proj.bias)
+        if bias:
+            nn.init.zeros_(self.qkv.bias)
+            nn.init.zeros_(self.proj.bias)
 
-    def forward(self, x):
+    def forward(self, x, rope=None):
         b, s, h = x.shape
-        q, k, v = self.qkv(x).split(h, dim=-1)
-        q, k, v = (t.view(b, s, self.heads, h // self.heads).transpose(1, 2) for t in (q, k, v))
-        out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        q_dim, kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        q, k, v = self.qkv(x).split([q_dim, kv_dim, kv_dim], dim=-1)
+        q = q.view(b, s, self.heads, self.head_dim).transpose(1, 2)
+        k = k.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        v = v.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        if rope is not None:
+            q, k = _rope(q, *rope), _rope(k, *rope)
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv_heads != self.heads)
         return self.proj(out.transpose(1, 2).reshape(b, s, h))
 
 
@@ -65,44 +79,79 @@ class RefBlock(nn.Module):
 
     def __init__(self, cfg, moe_args, dmoe_mod, device, dtype):
         super().__init__()
-        self.ln1 = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
-        self.attn = RefAttention(cfg['hidden'], cfg['heads'], cfg['layers'], device, dtype)
-        self.ln2 = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+        mixtral = cfg.get('flavour', 'gpt2') == 'mixtral'
+        norm = (lambda n: nn.RMSNorm(n, eps=1e-5, device=device, dtype=dtype)) if mixtral else \
+            (lambda n: nn.LayerNorm(n, device=device, dtype=dtype))
+        self.ln1 = norm(cfg['hidden'])
+        self.attn = RefAttention(cfg['hidden'], cfg['heads'], cfg['layers'], device, dtype,
+                                 kv_heads=cfg.get('kv_heads'), bias=not mixtral)
+        self.ln2 = norm(cfg['hidden'])
         self.moe = dmoe_mod.dMoE(moe_args)
 
-    def forward(self, x):
-        x = x + self.attn(self.ln1(x))
+    def forward(self, x, rope=None):
+        x = x + self.attn(self.ln1(x), rope)
         return x + self.moe(self.ln2(x))
 
 
 class RefGPT(nn.Module):
 
-    def __init__(self, cfg, device, ep_group=None, memory_optimized_mlp=False):
+    def __init__(self, cfg, device, ep_group=None, memory_optimized_mlp=False, recompute=False):
+        """``cfg``: hidden, ffn, layers, heads, seq, vocab, experts, top_k and optionally ``flavour``
+        ('gpt2' | 'mixtral': RMSNorm, rotary positions, ``kv_heads`` grouped-query attention, SwiGLU
+        experts, untied LM head) and ``rope_theta``."""
         super().__init__()
         Arguments, dmoe_mod, self.moe_mod = import_reference()
         dtype = torch.bfloat16
+        self.cfg, self.recompute = cfg, recompute
+        self.mixtral = cfg.get('flavour', 'gpt2') == 'mixtral'
         self.moe_args = Arguments(
-            hidden_size=cfg['hidden'], ffn_hidden_size=cfg['ffn'], num_layers=cfg['layers'], bias=True,
-            return_bias=False, activation_fn=partial(F.gelu, approximate='tanh'),
+            hidden_size=cfg['hidden'], ffn_hidden_size=cfg['ffn'], num_layers=cfg['layers'], bias=not self.mixtral,
+            return_bias=False, activation_fn=F.silu if self.mixtral else partial(F.gelu, approximate='tanh'),
             moe_num_experts=cfg['experts'], moe_top_k=cfg['top_k'], moe_loss_weight=0.1, moe_lbl_in_fp32=True,
+            moe_normalize_expert_weights=1 if self.mixtral else None,
             moe_expert_model_parallelism=ep_group is not None, expert_parallel_group=ep_group,
-            memory_optimized_mlp=memory_optimized_mlp, mlp_type='mlp', mlp_impl='grouped', fp16=False, bf16=True, device=device,
+            memory_optimized_mlp=memory_optimized_mlp, mlp_type='glu' if self.mixtral else 'mlp', mlp_impl='grouped',
+            fp16=False, bf16=True, device=device,
             init_method=partial(nn.init.normal_, mean=0.0, std=0.02),
             output_layer_init_method=partial(nn.init.normal_, mean=0.0, std=0.02 / math.sqrt(2.0 * cfg['layers'])))
         self.wte = nn.Embedding(cfg['vocab'], cfg['hidden'], device=device, dtype=dtype)
-        self.wpe = nn.Embedding(cfg['seq'], cfg['hidden'], device=device, dtype=dtype)
         nn.init.normal_(self.wte.weight, std=0.02)
-        nn.init.normal_(self.wpe.weight, std=0.02)
+        self.wpe = self.lm_head = None
+        if self.mixtral:
+            self.lm_head = nn.Linear(cfg['hidden'], cfg['vocab'], bias=False, device=device, dtype=dtype)
+            nn.init.normal_(self.lm_head.weight, std=0.02)
+        else:
+            self.wpe = nn.Embedding(cfg['seq'], cfg['hidden'], device=device, dtype=dtype)
+            nn.init.normal_(self.wpe.weight, std=0.02)
         self.blocks = nn.ModuleList(
             [RefBlock(cfg, self.moe_args, dmoe_mod, device, dtype) for _ in range(cfg['layers'])])
-        self.ln_f = nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+        self.ln_f = nn.RMSNorm(cfg['hidden'], eps=1e-5, device=device, dtype=dtype) if self.mixtral else \
+            nn.LayerNorm(cfg['hidden'], device=device, dtype=dtype)
+        self._rope = None
+
+    def _rope_tables(self, seq, device):
+        if self._rope is None or self._rope[0].shape[0] < seq:
+            head_dim = self.cfg['hidden'] // self.cfg['heads']
+            inv = 1.0 / (self.cfg.get('rope_theta', 1e6)**(torch.arange(0, head_dim, 2, device=device).float() / head_dim))
+            ang = torch.outer(torch.arange(seq, device=device).float(), inv)
+            self._rope = (ang.cos(), ang.sin())
+        return self._rope[0][:seq], self._rope[1][:seq]
 
     def loss(self, tokens, targets):
         b, s = tokens.shape
-        x = self.wte(tokens) + self.wpe(torch.arange(s, device=tokens.device))
+        x = self.wte(tokens)
+        rope = None
+        if self.mixtral:
+            rope = self._rope_tables(s, tokens.device)
+        else:
+            x = x + self.wpe(torch.arange(s, device=tokens.device))
         for block in self.blocks:
-            x = block(x)
-        logits = F.linear(self.ln_f(x), self.wte.weight)
+            if self.recompute and self.training:
+                from torch.utils.checkpoint import checkpoint
+                x = checkpoint(block, x, rope, use_reentrant=False)
+            else:
+                x = block(x, rope)
+        logits = F.linear(self.ln_f(x), self.lm_head.weight if self.mixtral else self.wte.weight)
         lm = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1))
         total = lm + self.moe_mod.batched_load_balancing_loss(self.moe_args)
         self.moe_mod.clear_load_balancing_loss()

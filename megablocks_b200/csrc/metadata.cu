@@ -7,6 +7,8 @@
 // observation: every key space here is tiny (expert ids, <= 1024 values, or one
 // 8-bit digit), so a sort is a histogram, a scan and one stable placement pass,
 // and the histogram / prefix sums the caller wants next fall out of the same passes.
+#include <atomic>
+
 #include "common.cuh"
 #include "route_plan_noalloc.h"
 
@@ -413,20 +415,24 @@ static __device__ __align__(256) int g_noalloc_scratch[kNoAllocScratchInts];
 
 // Device address of the scratch array per device.  The array's name is only a
 // host-side handle; kernels need the address cudaGetSymbolAddress reports.
-int* g_noalloc_scratch_addr[64] = {nullptr};
+// (Filled on first use; two host threads that race here store the same value, and the atomic makes
+// that exchange well defined.)
+std::atomic<int*> g_noalloc_scratch_addr[64];
 
 cudaError_t noalloc_scratch(int** out) {
   int dev = 0;
   cudaError_t rc = cudaGetDevice(&dev);
   if (rc != cudaSuccess) return rc;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (g_noalloc_scratch_addr[dev] == nullptr) {
+  int* addr = g_noalloc_scratch_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* ptr = nullptr;
     rc = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
     if (rc != cudaSuccess) return rc;
-    g_noalloc_scratch_addr[dev] = static_cast<int*>(ptr);
+    addr = static_cast<int*>(ptr);
+    g_noalloc_scratch_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_noalloc_scratch_addr[dev];
+  *out = addr;
   return cudaSuccess;
 }
 

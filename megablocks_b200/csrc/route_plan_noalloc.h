@@ -29,6 +29,8 @@
 //   tokens_per_expert[e], bins[e] (inclusive prefix sum), padded_bins[e] (prefix sum of
 //   counts rounded up to `block`).
 // All pointers are device pointers to int32; outputs need n, n, E, E and E elements.
+// `stream` must be a stream of the device that is current when the call is made: the
+// scratch address is looked up for the current device and the kernels are launched there.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -48,16 +48,24 @@ def _layer_args(kw, device, group=None, fused=None, dtype=torch.bfloat16):
 
 
 def _skew_router(layer, kw):
-    """Zipf-like bias folded into the router weight: the first experts get most tokens, the last none."""
-    if not kw.get('zipf'):
-        return
+    """Router whose decisions cannot flip between bf16 and fp32.
+
+    Expert e reads input feature e only (weight 1), and the inputs carry, per token, a random
+    permutation of multiples of 0.5 in their first `experts` features: any two logits of a token
+    are at least 0.5 apart, far more than a bf16 rounding, so the parallel bf16 run and the fp32
+    single-process oracle route every token identically.  `zipf` adds a per-expert bias (multiples of
+    1/8, through a constant input feature) that skews the load; the last two experts get nothing.
+    """
     with torch.no_grad():
         w = layer.router.layer.weight
         experts = w.shape[0]
-        ranks = torch.arange(1, experts + 1, dtype=torch.float32, device=w.device)
-        bias = torch.log(1.0 / ranks**float(kw['zipf']))
-        bias[experts - 2:] = -1e4                       # nobody routes to the last two experts
-        w[:, 0] = bias.to(w.dtype)                      # the inputs set x[:, 0] = 1: logits = bias + noise
+        w.zero_()
+        w[:, :experts] = torch.eye(experts, device=w.device, dtype=w.dtype)
+        if kw.get('zipf'):
+            ranks = torch.arange(1, experts + 1, dtype=torch.float32, device=w.device)
+            bias = -torch.round(float(kw['zipf']) * torch.log(ranks) * 3.0 * 8.0) / 8.0
+            bias[experts - 2:] = -64.0                  # nobody routes to the last two experts
+            w[:, experts] = bias.to(w.dtype)            # the inputs set feature `experts` to 1
 
 
 def _tokens_of(rank, kw):
@@ -67,9 +75,11 @@ def _tokens_of(rank, kw):
 def _inputs(rank, kw, device, dtype):
     gen = torch.Generator().manual_seed(100 + rank)
     n = _tokens_of(rank, kw)
+    experts = kw.get('experts', 8)
     x = torch.randn(n, 1, HIDDEN, generator=gen)
-    if kw.get('zipf'):
-        x[:, :, 0] = 1.0
+    perm = torch.argsort(torch.rand(n, experts, generator=gen), dim=1).float() * 0.5
+    x[:, 0, :experts] = perm
+    x[:, 0, experts] = 1.0
     probe = torch.randn(n, 1, HIDDEN, generator=gen)
     return x.to(dtype).to(device), probe.to(dtype).to(device)
 
@@ -138,16 +148,6 @@ def _close(got, want, what, rtol=3e-2, scale=2e-2):
     torch.testing.assert_close(got, want, rtol=rtol, atol=scale * float(want.abs().max()) + 1e-3, msg=lambda m: f'{what}: {m}')
 
 
-def _close_rows(got, want, what, max_bad=0.02):
-    """Row-wise comparison that tolerates a few rows: a token whose two best router logits are a
-    rounding error apart may pick another expert in bf16 than in the fp32 oracle, and its whole row
-    then differs.  Every other row must match."""
-    got, want = got.reshape(-1, got.shape[-1]), want.reshape(-1, want.shape[-1])
-    tol = 3e-2 * want.abs() + 2e-2 * float(want.abs().max()) + 1e-3
-    bad_rows = ((got - want).abs() > tol).any(dim=1).float().mean().item()
-    assert bad_rows <= max_bad, f'{what}: {bad_rows:.2%} of the rows differ from the fp32 oracle'
-
-
 CASES = [
     dict(top_k=1, mem_opt=True, tokens=512),
     dict(top_k=2, tokens=300),
@@ -189,11 +189,10 @@ def test_fused_route(kw, tmp_path):
     esd = min(world, experts)
     hsd, epr = world // esd, experts // esd
     for r, res in enumerate(results):
-        _close_rows(res[True]['out'][-1], outs[r], f'rank {r} output')
-        _close_rows(res[True]['dx'], dxs[r], f'rank {r} dx')
-    # Sums over tokens: a handful of re-routed tokens moves them a little.
+        _close(res[True]['out'][-1], outs[r], f'rank {r} output')
+        _close(res[True]['dx'], dxs[r], f'rank {r} dx')
     total = sum(res[True]['grads']['router.layer.weight'] for res in results)
-    _close(total, layer.router.layer.weight.grad.cpu(), 'router gradient', rtol=1e-1, scale=1e-1)
+    _close(total, layer.router.layer.weight.grad.cpu(), 'router gradient', rtol=5e-2, scale=3e-2)
     names = ('w1', 'w2') + (('v1',) if kw.get('mlp_type') == 'glu' else ())
     for name in names:
         full = getattr(layer.experts.mlp, name).grad.cpu().view(experts, -1, HIDDEN)
@@ -202,4 +201,4 @@ def test_fused_route(kw, tmp_path):
             e0, r0 = (r % esd) * epr, (r // esd) * f_local
             want = full[e0:e0 + epr, r0:r0 + f_local] / world
             _close(res[True]['grads'][f'experts.mlp.{name}'].reshape(want.shape), want, f'rank {r} {name}',
-                   rtol=1e-1, scale=6e-2)
+                   rtol=5e-2, scale=3e-2)

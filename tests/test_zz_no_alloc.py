@@ -5,7 +5,8 @@ living inside another runtime's arena, engines with a frozen memory map, sandbox
 that deny cudaMalloc): they bring every buffer and the library's own fixed scratch
 array does the rest.  The test calls the symbol with ctypes exactly as such a caller
 would, twice in a row with different inputs (the scratch keeps the first call's
-contents), and requires bit-equal results with the regular ``route_plan`` op.  It
+contents), and requires bit-equal results with the regular ``route_plan`` op and with a
+plain CPU oracle (stable sort, bincount, cumsum), which shares no kernel with either.  It
 also checks that oversize requests are refused before anything is launched.
 
 This file sorts last on purpose: if it ever fails, a run that stops at the first
@@ -52,6 +53,15 @@ def test_route_plan_noalloc_matches_route_plan_twice_in_a_row():
         torch.cuda.synchronize()
         for got, ref in zip((indices, bin_ids, bins, padded, tpe), want):
             assert torch.equal(got, ref)
+        # Independent oracle on the host.
+        host = top.cpu().long()
+        sorted_ids, order = torch.sort(host, stable=True)
+        counts = torch.bincount(host, minlength=experts)
+        assert torch.equal(indices.cpu().long(), order)
+        assert torch.equal(bin_ids.cpu().long(), sorted_ids)
+        assert torch.equal(tpe.cpu().long(), counts)
+        assert torch.equal(bins.cpu().long(), torch.cumsum(counts, 0))
+        assert torch.equal(padded.cpu().long(), torch.cumsum((counts + block - 1) // block * block, 0))
 
 
 @pytest.mark.gpu
