@@ -759,6 +759,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           MB_T_END(w0, t_empty);
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[stage]);
+          if (p.diag & 1) {   // diagnostic: no operand loads, the MMAs chew on whatever the stage holds
+            mbar_arrive(bar);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_arrive_expect_tx(bar, kABytes + Cfg::kBBytes);
           const uint32_t a_dst = smem_u32(smem_a + stage * kABytes);
           const uint32_t b_dst = smem_u32(smem_b + stage * Cfg::kBBytes);
@@ -840,13 +845,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0) {
           const uint32_t a_base = smem_u32(a_tile);
           const uint32_t b_base = smem_u32(b_tile);
+          if (!(p.diag & 2)) {   // (diagnostic bit 2: operand loads and epilogue without any MMA)
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint64_t a_desc = kAMn ? smem_desc_sw128(a_base + k * (kUmmaK * 128), kBoxBytes, 1024)
-                                         : smem_desc_sw128(a_base + k * (kUmmaK * 2), 16, 1024);
-            const uint64_t b_desc = kBMn ? smem_desc_sw128(b_base + k * (kUmmaK * 128), kBoxBytes, 1024)
-                                         : smem_desc_sw128(b_base + k * (kUmmaK * 2), 16, 1024);
-            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              const uint64_t a_desc = kAMn ? smem_desc_sw128(a_base + k * (kUmmaK * 128), kBoxBytes, 1024)
+                                           : smem_desc_sw128(a_base + k * (kUmmaK * 2), 16, 1024);
+              const uint64_t b_desc = kBMn ? smem_desc_sw128(b_base + k * (kUmmaK * 128), kBoxBytes, 1024)
+                                           : smem_desc_sw128(b_base + k * (kUmmaK * 2), 16, 1024);
+              umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(&empty_bar[stage]));   // stage is reusable once these MMAs retire
         }

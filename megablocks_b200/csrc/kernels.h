@@ -241,6 +241,9 @@ struct GemmParams {
   // their staged chunk to the TMA unit instead of storing it with the LSU.  0 = off.
   int store_tma;
   CUtensorMap out_map[3];
+  // Diagnostics for roofline experiments (results are meaningless): bit 0 = the producer issues no
+  // operand loads, bit 1 = the MMA warp issues no MMAs.  Set from MB200_GEMM_DIAG; 0 in normal use.
+  int diag;
   // Role timers (builds with -DMB_GEMM_TIMING only): [grid][16] cycle counters, see the kernel.
   long long* timing;
 };

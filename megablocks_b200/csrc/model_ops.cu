@@ -67,6 +67,29 @@ lbl_bwd_kernel(LblArgs a, int64_t tokens, int experts, float scale, const float*
   T* __restrict__ out = static_cast<T*>(a.dscores[layer]);
   const int* __restrict__ counts = a.counts[layer];
   const float g = *gout * scale;
+  constexpr int VEC = 16 / sizeof(T);
+  if (experts % VEC == 0) {
+    // Every row is the same vector g * counts: each thread builds its 16-byte piece once and
+    // stores it down its column strip.
+    const int vecs_per_row = experts / VEC;
+    const int64_t total = tokens * vecs_per_row;
+    const int64_t stride = int64_t(gridDim.x) * kLblThreads;
+    int64_t i = int64_t(blockIdx.x) * kLblThreads + threadIdx.x;
+    // A stride that is a multiple of the row length keeps a thread in one column strip.
+    const bool fixed = stride % vecs_per_row == 0;
+    struct alignas(16) Raw { T v[VEC]; } piece;
+    int have = -1;
+    for (; i < total; i += stride) {
+      const int v = int(i % vecs_per_row);
+      if (!fixed || have != v) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) piece.v[k] = from_float<T>(g * float(__ldg(counts + v * VEC + k)));
+        have = v;
+      }
+      *reinterpret_cast<uint4*>(out + i * VEC) = *reinterpret_cast<const uint4*>(&piece);
+    }
+    return;
+  }
   const int64_t total = tokens * experts;
   for (int64_t i = int64_t(blockIdx.x) * kLblThreads + threadIdx.x; i < total; i += int64_t(gridDim.x) * kLblThreads)
     out[i] = from_float<T>(g * float(__ldg(counts + int(i % experts))));

@@ -555,6 +555,13 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   p.timing = reinterpret_cast<long long*>(timing_words(a.device()).data_ptr<int64_t>());
 #endif
   p.zero_tail = zero_tail ? 1 : 0;
+  {
+    static const int diag = [] {
+      const char* v = std::getenv("MB200_GEMM_DIAG");
+      return v != nullptr ? std::atoi(v) : 0;
+    }();
+    p.diag = diag;
+  }
   if (wait_flags.has_value()) {
     TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == at::kInt && layout != kTN,
                 "wait_flags must be a CUDA int32 tensor (NT / NN layouts only)");
