@@ -30,6 +30,7 @@ import torch
 import torch.nn.functional as F
 
 from megablocks_b200._ext import ext
+from megablocks_b200.utils import debug
 
 # Epilogue kinds understood by the kernel.
 EPI_NONE = 0      # c = acc
@@ -204,6 +205,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     """
     if num_groups is None:
         num_groups = bins.numel()
+    debug.check_groups(bins, a.shape[0])
     if a.is_cuda and ext().grouped_gemm_supported(a, b, bool(trans_a), bool(trans_b), int(num_groups)):
         flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
         return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,

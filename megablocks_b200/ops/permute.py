@@ -27,6 +27,7 @@ from typing import Any, Optional
 import torch
 
 from megablocks_b200._ext import ext
+from megablocks_b200.utils import debug
 
 
 # ----------------------------------------------------------------------------
@@ -60,6 +61,7 @@ def _sum_top_k(tmp: torch.Tensor, tokens: int, top_k: int) -> torch.Tensor:
 # Kernels behind the padded / unpadded ops.
 # ----------------------------------------------------------------------------
 def _gather_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k, out_rows):
+    debug.check_routing(indices, bin_ids, bins, padded_bins, top_k, x.shape[0], out_rows)
     if x.is_cuda:
         return ext().gather_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k, out_rows)
     copy_ids = indices.to(torch.int64)
@@ -71,6 +73,7 @@ def _gather_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k, out_row
 
 def _scatter_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k):
     tokens = indices.numel() // top_k
+    debug.check_routing(indices, bin_ids, bins, padded_bins, top_k, tokens, x.shape[0])
     if x.is_cuda:
         return ext().scatter_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k, tokens)
     copy_ids = indices.to(torch.int64)
@@ -82,6 +85,7 @@ def _scatter_rows(x, indices, bin_ids, weights, bins, padded_bins, top_k):
 
 def _scatter_wgrad(x, grad, indices, bin_ids, bins, padded_bins, top_k):
     """d(loss)/d(weights): one dot product of an expert row with its token's grad."""
+    debug.check_routing(indices, bin_ids, bins, padded_bins, top_k, grad.shape[0], x.shape[0])
     if x.is_cuda:
         return ext().scatter_wgrad(x, grad, indices, bin_ids, bins, padded_bins, top_k)
     copy_ids = indices.to(torch.int64)

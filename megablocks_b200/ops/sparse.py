@@ -29,6 +29,7 @@ from typing import Any, Optional, Tuple
 import torch
 
 from megablocks_b200._ext import ext
+from megablocks_b200.utils import debug
 
 _KERNEL_BLOCK = 128
 _MODE_SDD, _MODE_DSD, _MODE_DDS = 0, 1, 2
@@ -201,6 +202,7 @@ def _segments(s: Matrix, transposed_list: bool):
 
 
 def _sdd_kernel(a: torch.Tensor, b: torch.Tensor, topo: Matrix) -> torch.Tensor:
+    debug.check_topology(topo.row_indices, topo.column_indices, topo.offsets, topo._size, topo.blocking)
     sa, a_t = _stored(a)
     sb, b_t = _stored(b)
     # a is [M, K]: stored transposed = MN-major.  b is [K, N]: stored as given = MN-major.
@@ -208,6 +210,7 @@ def _sdd_kernel(a: torch.Tensor, b: torch.Tensor, topo: Matrix) -> torch.Tensor:
 
 
 def _dsd_kernel(s: Matrix, data: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    debug.check_topology(s.row_indices, s.column_indices, s.offsets, s._size, s.blocking)
     sb, b_t = _stored(b)
     offsets, block, kblock = _segments(s, s.is_transposed)
     return ext().bsmm(_MODE_DSD, data.contiguous(), s.is_transposed, sb, not b_t, offsets, block, kblock, s.size(0),
@@ -215,6 +218,7 @@ def _dsd_kernel(s: Matrix, data: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def _dds_kernel(a: torch.Tensor, s: Matrix, data: torch.Tensor) -> torch.Tensor:
+    debug.check_topology(s.row_indices, s.column_indices, s.offsets, s._size, s.blocking)
     sa, a_t = _stored(a)
     # Columns of s are the rows of its transpose: a plain topology needs the transposed list.
     offsets, block, kblock = _segments(s, not s.is_transposed)
