@@ -49,7 +49,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
                                      int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
-                                     const std::vector<int64_t>& scatter_args, double alpha);
+                                     const std::vector<int64_t>& scatter_args, double alpha,
+                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2);
 int64_t read_status(bool clear);
 int64_t launch_count();
 at::Tensor gemm_role_timers(const at::Tensor& like);

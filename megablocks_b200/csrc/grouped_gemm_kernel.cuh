@@ -42,6 +42,7 @@ namespace gemm {
 using namespace ptx;
 
 constexpr int kUmmaK = 16;
+constexpr int kBandN = 8;                    // column tiles per band of the tile walk (NT / NN)
 constexpr int kSmallGroups = 224;            // groups whose tables fit beside two sets of staging buffers
 constexpr int kMaxScatterSegments = 512;     // experts per rank x world of the fused combine
 constexpr int kEpilogueWarps = 8;            // two warps per TMEM lane quarter
@@ -683,7 +684,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t tmem_base = *tmem_base_slot;
 
   // ---- tile schedule (every role decodes the same sequence) ---------------------
-  const int num_nb = (p.N + BLOCK_N - 1) / BLOCK_N;
+  // With two B operands a tile covers half as many output columns (each operand fills half of the
+  // accumulator).
+  const bool dual = LAYOUT == kNT && BLOCK_N == 256 && p.dual_b != 0;
+  const bool concat = LAYOUT == kNN && p.k_concat != 0;
+  const int tile_n = dual ? BLOCK_N / 2 : BLOCK_N;
+  const int num_nb = (p.N + tile_n - 1) / tile_n;
   const int num_mb_tn = (p.M + kBlockM - 1) / kBlockM;
   const int total_tiles =
       dead ? 0 : ((LAYOUT == kTN) ? G * num_mb_tn * num_nb : (G > 0 ? s_mblk_end[G - 1] : 0) * num_nb);
@@ -695,22 +701,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tile.group = t / per_group;
       const int r = t - tile.group * per_group;
       const int mb_i = r / num_nb;
-      tile.n0 = (r - mb_i * num_nb) * BLOCK_N;
+      tile.n0 = (r - mb_i * num_nb) * tile_n;
       tile.row0 = mb_i * kBlockM;
       tile.rows_valid = min(kBlockM, p.M - tile.row0);
       tile.k_begin = tile.group ? s_row_end[tile.group - 1] : 0;
       tile.k_len = s_row_end[tile.group] - tile.k_begin;
     } else {
-      const int mblk = t / num_nb;
-      tile.n0 = (t - mblk * num_nb) * BLOCK_N;
+      // Tiles of a group are walked in bands of kBandN column tiles, row blocks fastest inside a
+      // band: the CTAs that run at the same time then share a few B tiles and a few dozen A tiles
+      // (tens of MB) instead of sweeping the group's whole weight matrix once per row block, which
+      // for large experts (hundreds of MB of weights) would stream them from HBM again and again.
       int lo = 0, hi = G - 1;
+      const int key = t / num_nb;              // group boundaries are multiples of num_nb tiles
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
-        if (s_mblk_end[mid] <= mblk) lo = mid + 1; else hi = mid;
+        if (s_mblk_end[mid] <= key) lo = mid + 1; else hi = mid;
       }
       tile.group = lo;
+      const int mblk_begin = lo ? s_mblk_end[lo - 1] : 0;
+      const int mblks = s_mblk_end[lo] - mblk_begin;
+      const int u = t - mblk_begin * num_nb;   // index of the tile inside its group
+      const int band_n = p.band_n > 0 ? p.band_n : kBandN;
+      const int band = u / (mblks * band_n);
+      const int r = u - band * mblks * band_n;
+      const int width = min(band_n, num_nb - band * band_n);
+      const int local = r / width;
+      tile.n0 = (band * band_n + (r - local * width)) * tile_n;
       const int row_start = lo ? s_row_end[lo - 1] : 0;
-      const int local = mblk - (lo ? s_mblk_end[lo - 1] : 0);
       tile.row0 = row_start + local * kBlockM;
       tile.rows_valid = min(kBlockM, s_row_end[lo] - tile.row0);
       tile.k_begin = 0;
@@ -729,7 +746,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       MB_T_DECL(t_empty);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const Tile tile = decode(t);
-        const int num_kb = (tile.k_len + kBlockK - 1) / kBlockK;
+        const int num_kb1 = (tile.k_len + kBlockK - 1) / kBlockK;
+        const int num_kb = concat ? 2 * num_kb1 : num_kb1;
         if (LAYOUT != kTN && p.wait_flags != nullptr && tile.group != arrived_group) {
           // Rows of this group are stored by peer GPUs; each source releases one flag
           // per group when its last row has landed.
@@ -769,12 +787,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t b_dst = smem_u32(smem_b + stage * Cfg::kBBytes);
           if constexpr (LAYOUT == kNT) {
             tma_load_2d(a_dst, &tmap_a, bar, kb * kBlockK, tile.row0);
-            tma_load_2d(b_dst, &tmap_b, bar, kb * kBlockK, tile.group * p.N + tile.n0);
+            if (dual) {   // 128 rows of each weight matrix, one after the other in the stage
+              tma_load_2d(b_dst, &tmap_b, bar, kb * kBlockK, tile.group * p.N + tile.n0);
+              tma_load_2d(b_dst + Cfg::kBBytes / 2, &p.b2_map, bar, kb * kBlockK, tile.group * p.N + tile.n0);
+            } else {
+              tma_load_2d(b_dst, &tmap_b, bar, kb * kBlockK, tile.group * p.N + tile.n0);
+            }
           } else if constexpr (LAYOUT == kNN) {
-            tma_load_2d(a_dst, &tmap_a, bar, kb * kBlockK, tile.row0);
+            // Second operand pair of a concatenated contraction: same coordinates, other tensors.
+            const bool second = concat && kb >= num_kb1;
+            const int kk = second ? kb - num_kb1 : kb;
+            const CUtensorMap* ma = second ? &p.a2_map : &tmap_a;
+            const CUtensorMap* mbp = second ? &p.b2_map : &tmap_b;
+            tma_load_2d(a_dst, ma, bar, kk * kBlockK, tile.row0);
 #pragma unroll
             for (int j = 0; j < BLOCK_N / 64; ++j)
-              tma_load_2d(b_dst + j * kBoxBytes, &tmap_b, bar, tile.n0 + 64 * j, tile.group * p.K + kb * kBlockK);
+              tma_load_2d(b_dst + j * kBoxBytes, mbp, bar, tile.n0 + 64 * j, tile.group * p.K + kk * kBlockK);
           } else {
             const int krow = tile.k_begin + kb * kBlockK;
 #pragma unroll
@@ -803,7 +831,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     MB_T_BEGIN(role0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Tile tile = decode(t);
-      const int num_kb = (tile.k_len + kBlockK - 1) / kBlockK;
+      const int num_kb = ((tile.k_len + kBlockK - 1) / kBlockK) * (concat ? 2 : 1);
       MB_T_BEGIN(w1);
       ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_stage]), acc_phase ^ 1u, abort_flag, p.status, kErrMmaTmem,
                      kWaitLimitNs);
@@ -950,10 +978,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       // The two warps of a quarter interleave 32-column chunks.
       MB_T_BEGIN(wloop);
 #pragma unroll 1
-      for (int ci = half; ci < kChunks; ci += 2) {
+      const int chunks = dual ? kChunks / 2 : kChunks;
+      for (int ci = half; ci < chunks; ci += 2) {
         const int c0 = ci * 32;
         const int col = tile.n0 + c0;
         if (col >= p.N) break;                   // uniform across the warp
+        if (dual) {
+          // a b^T first: written out (out3) and kept packed; then a b2^T with the GLU product.
+          uint32_t raw[32];
+          PackedRow z1, unused;
+          tmem_ld_32x32(taddr + c0, raw);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            z1.q[v].x = pack2<T>(__uint_as_float(raw[v * 8 + 0]), __uint_as_float(raw[v * 8 + 1]));
+            z1.q[v].y = pack2<T>(__uint_as_float(raw[v * 8 + 2]), __uint_as_float(raw[v * 8 + 3]));
+            z1.q[v].z = pack2<T>(__uint_as_float(raw[v * 8 + 4]), __uint_as_float(raw[v * 8 + 5]));
+            z1.q[v].w = pack2<T>(__uint_as_float(raw[v * 8 + 6]), __uint_as_float(raw[v * 8 + 7]));
+          }
+          if (rows_ok > 0) {
+            const int cols = min(32, p.N - col);
+            const CUtensorMap* maps = p.store_tma ? p.out_map : nullptr;
+            epilogue_emit<T, kEpiNone, kActIdentity, 0>(raw, z1, unused, stage, static_cast<T*>(p.out3) + row_off + col,
+                                                        p.N, rows_ok, cols, lane, nullptr, col,
+                                                        maps ? maps + 2 : nullptr, tma);
+            tmem_ld_32x32(taddr + BLOCK_N / 2 + c0, raw);
+            tmem_ld_wait();
+            epilogue_by_act<T, kEpiGlu>(raw, z1, unused, stage, row_off + col, p.N, rows_ok, cols, lane, p, nullptr, col,
+                                        tma);
+          }
+          continue;
+        }
         // Ask for the next chunk's auxiliary operands, then bring this chunk's through the
         // staging buffer (coalesced read, each thread picks up its own row).
         if (ci + 2 < kChunks && rows_ok > 0 && col + 64 < p.N) {

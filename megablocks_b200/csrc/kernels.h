@@ -192,7 +192,7 @@ constexpr int kBlockK = 64;
 constexpr int kMaxGroups = 1024;
 
 enum Layout : int { kNT = 0, kNN = 1, kTN = 2 };
-enum Epilogue : int { kEpiNone = 0, kEpiAct = 1, kEpiDAct = 2, kEpiGlu = 3, kEpiDGlu = 4, kEpiAdd = 5 };
+enum Epilogue : int { kEpiNone = 0, kEpiAct = 1, kEpiDAct = 2, kEpiGlu = 3, kEpiDGlu = 4, kEpiAdd = 5, kEpiGluDual = 6 };
 enum Act : int { kActIdentity = 0, kActGeluTanh = 1, kActSilu = 2, kActRelu = 3, kActGeluErf = 4 };
 
 struct GemmParams {
@@ -241,6 +241,18 @@ struct GemmParams {
   // their staged chunk to the TMA unit instead of storing it with the LSU.  0 = off.
   int store_tma;
   CUtensorMap out_map[3];
+  // Second operand pair.
+  //   dual_b (NT, block_n 256, epilogue kEpiGluDual): a tile covers 128 output columns and multiplies
+  //   the same A tile with the matching 128 rows of b AND of b2 (one MMA with N = 256: accumulator
+  //   columns [0, 128) = a b^T, [128, 256) = a b2^T).  Outputs: c = a b2^T, out2 = act(a b^T) * c,
+  //   out3 = a b^T - the GLU forward in one launch.  Both B tensor maps then have 128-row boxes.
+  //   k_concat (NN): the contraction runs over a x b and then over a2 x b2 into the same accumulator
+  //   (c = a b + a2 b2: the GLU input gradient in one launch).
+  int dual_b;
+  int k_concat;
+  int band_n;      // NT / NN: column tiles per band of the tile walk (0 = the kernel's default)
+  CUtensorMap a2_map;
+  CUtensorMap b2_map;
   // Diagnostics for roofline experiments (results are meaningless): bit 0 = the producer issues no
   // operand loads, bit 1 = the MMA warp issues no MMAs.  Set from MB200_GEMM_DIAG; 0 in normal use.
   int diag;

@@ -493,7 +493,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<at::Tensor>& wait_flags, int64_t wait_count,
                                      int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
-                                     const std::vector<int64_t>& scatter_args, double alpha) {
+                                     const std::vector<int64_t>& scatter_args, double alpha,
+                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -545,9 +546,24 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
     out2 = at::empty_like(c);
     p.out2 = out2.data_ptr();
   }
-  if (epilogue == kEpiDGlu && want_out3) {
+  if ((epilogue == kEpiDGlu && want_out3) || epilogue == kEpiGluDual) {
     out3 = at::empty_like(c);
     p.out3 = out3.data_ptr();
+  }
+  const bool dual = epilogue == kEpiGluDual;
+  const bool concat = a2.has_value();
+  if (dual) {
+    TORCH_CHECK(layout == kNT && b2.has_value() && !a2.has_value() && !scatter.has_value() && p.N >= 128 && pair_mode != 1,
+                "the dual-B GLU epilogue needs the NT layout, a second weight tensor and at least 128 output columns");
+    TORCH_CHECK(b2->is_cuda() && b2->is_contiguous() && b2->sizes() == b.sizes() && b2->scalar_type() == b.scalar_type(),
+                "b2 must match b");
+  }
+  if (concat) {
+    TORCH_CHECK(layout == kNN && b2.has_value() && (epilogue == kEpiNone || epilogue == kEpiAdd),
+                "a concatenated contraction needs the NN layout, a2 and b2, and a plain or add epilogue");
+    TORCH_CHECK(a2->is_cuda() && a2->is_contiguous() && a2->sizes() == a.sizes() && a2->scalar_type() == a.scalar_type() &&
+                    b2->is_cuda() && b2->is_contiguous() && b2->sizes() == b.sizes() && b2->scalar_type() == b.scalar_type(),
+                "a2 / b2 must match a / b");
   }
   p.c = c.data_ptr();
   p.status = status_word(a.device()).data_ptr<int>();
@@ -561,6 +577,11 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
       return v != nullptr ? std::atoi(v) : 0;
     }();
     p.diag = diag;
+    static const int band = [] {
+      const char* v = std::getenv("MB200_GEMM_BAND");
+      return v != nullptr ? std::atoi(v) : 0;
+    }();
+    p.band_n = band;
   }
   if (wait_flags.has_value()) {
     TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == at::kInt && layout != kTN,
@@ -609,7 +630,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   if (out_numel == 0) return {c, out2, out3};
 
-  const int block_n = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
+  const int block_n = (p.N >= 256 || dual) ? 256 : (p.N >= 128 ? 128 : 64);
   // CTA pairs (cta_group::2, 256-row tiles, six 32 KB stages per CTA) pull a third less operand
   // traffic through L2, but measured back to back against the single-CTA kernel (alternating
   // launches, L2 flushed, medians) they are 0-8 % slower on every shape tried, from 64 ragged groups
@@ -617,7 +638,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   // are therefore only taken on request.  pair_mode: 1 = whenever the kernel supports the problem,
   // anything else = never.
   (void)rows_hint;
-  const bool pair = pair_mode == 1 && block_n == 256 && sm_count() >= 2 && !scatter.has_value();
+  const bool pair = pair_mode == 1 && block_n == 256 && sm_count() >= 2 && !scatter.has_value() && !dual && !concat;
   if (!scatter.has_value() && store_tma_enabled()) {
     // Full 32-row quarters of a tile leave through the TMA unit (one instruction per chunk).
     const int64_t out_rows = out_numel / p.N;
@@ -647,11 +668,23 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   }
   if (layout == kNT) {
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
-    tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n);
-    tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * num_nb;
+    if (dual) {
+      tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n / 2);
+      p.b2_map = make_tensor_map(b2->data_ptr(), bf16, num_groups * p.N, p.K, block_n / 2);
+      p.dual_b = 1;
+      tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * ceil_div(p.N, block_n / 2);
+    } else {
+      tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.N, p.K, block_n);
+      tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * num_nb;
+    }
   } else if (layout == kNN) {
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.K, kBlockM);
     tb = make_tensor_map(b.data_ptr(), bf16, num_groups * p.K, p.N, 64);
+    if (concat) {
+      p.a2_map = make_tensor_map(a2->data_ptr(), bf16, a2->size(0), p.K, kBlockM);
+      p.b2_map = make_tensor_map(b2->data_ptr(), bf16, num_groups * p.K, p.N, 64);
+      p.k_concat = 1;
+    }
     tiles_bound = (ceil_div(a.size(0), kBlockM) + num_groups) * num_nb;
   } else {
     ta = make_tensor_map(a.data_ptr(), bf16, a.size(0), p.M, 64);

@@ -7,6 +7,8 @@ prefix sum for the block-sparse layout, where every group is a multiple of 128
 rows and pad rows are zero).
 
 Forward (MLP):  ``z = x w1^T``, ``h = act(z)`` (GEMM epilogue), ``y = h w2``.
+GLU: ``z1 = x w1^T`` and ``z2 = x v1^T`` come out of ONE launch whose epilogue also forms
+``h = act(z1) * z2``; in backward ``dx = dz1 w1 + dz2 v1`` is one contraction over both pairs.
 Backward:       ``dz = (dy w2^T) * act'(z)`` (epilogue; it also regenerates
 ``h`` when it was not kept), ``dw2 = h^T dy``, ``dw1 = dz^T x``, ``dx = dz w1``.
 GLU adds ``z2 = x v1^T`` with ``h = act(z1) * z2`` and the matching backward.
@@ -35,7 +37,11 @@ def mlp_forward(x, w1, w2, v1, bins, act: int, keep_h: bool, wait=None, zero_tai
     token-dropping layer's experts); ``w2`` is ``[E, f, h]``.
     """
     kw = dict(zero_tail=zero_tail, rows_hint=rows_hint)
-    if v1 is not None:
+    if v1 is not None and not w1_kn and w1.shape[1] >= 128:
+        # Both weight matrices in one launch: each tile multiplies its rows of x with 128 rows of w1
+        # and of v1, and the epilogue forms act(z1) * z2 from the two halves of the accumulator.
+        z2, h, z1 = G.grouped_gemm(x, w1, bins, trans_b=True, epilogue=G.EPI_GLU_DUAL, act=act, b2=v1, wait=wait, **kw)
+    elif v1 is not None:
         z1, _, _ = G.grouped_gemm(x, w1, bins, trans_b=not w1_kn, wait=wait, **kw)
         z2, h, _ = G.grouped_gemm(x, v1, bins, trans_b=not w1_kn, epilogue=G.EPI_GLU, act=act, aux1=z1, **kw)
     else:
@@ -82,6 +88,9 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
         # exists for the NN layout; callers pass no `scatter` with `w1_kn`).
         if v1 is None:
             dx, _, _ = G.grouped_gemm(dz1, w1, bins, trans_b=w1_kn, scatter=scatter, **kw)
+        elif not w1_kn:
+            # dx = dz1 w1 + dz2 v1 as ONE contraction over both pairs: no partial result in memory.
+            dx, _, _ = G.grouped_gemm(dz1, w1, bins, a2=dz2, b2=v1, scatter=scatter, **kw)
         else:
             dx, _, _ = G.grouped_gemm(dz1, w1, bins, trans_b=w1_kn, **kw)
             dx, _, _ = G.grouped_gemm(dz2, v1, bins, trans_b=w1_kn, epilogue=G.EPI_ADD, aux1=dx, scatter=scatter,

@@ -39,6 +39,7 @@ EPI_DACT = 2      # c = acc * act'(aux1), out2 = act(aux1)
 EPI_GLU = 3       # c = acc, out2 = act(aux1) * acc
 EPI_DGLU = 4      # c = acc * aux2 * act'(aux1), out2 = acc * act(aux1), out3 = act(aux1) * aux2
 EPI_ADD = 5       # c = acc + aux1
+EPI_GLU_DUAL = 6  # two weight operands: c = a b2^T, out2 = act(a b^T) * c, out3 = a b^T
 
 ACT_IDENTITY = 0
 ACT_GELU_TANH = 1
@@ -182,7 +183,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
                  c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
-                 rows_hint: int = 0, scatter=None, alpha: float = 1.0, pair: Optional[int] = None):
+                 rows_hint: int = 0, scatter=None, alpha: float = 1.0, pair: Optional[int] = None,
+                 a2: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -200,6 +202,11 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     fused into the GEMM epilogue.  The returned ``c`` is then empty.
     ``alpha`` multiplies every accumulator before the epilogue (e.g. the 1 / expert-parallel-world
     factor of expert weight gradients, applied for free instead of by a separate pass).
+    ``b2`` with ``epilogue=EPI_GLU_DUAL`` (``trans_b`` layout): the GLU forward in one launch - every
+    tile multiplies its rows of ``a`` with the matching rows of ``b`` and of ``b2``; returns
+    ``(a b2^T, act(a b^T) * (a b2^T), a b^T)``.  ``a2`` and ``b2`` without ``trans_b``: the contraction
+    runs over ``a x b`` and then ``a2 x b2`` into one accumulator, ``c = a b + a2 b2`` (the GLU input
+    gradient in one launch).
     ``pair`` overrides the kernel choice for this call: 1 = CTA pairs (``cta_group::2``, 256-row
     tiles) whenever the problem allows, 0 = single-CTA kernel, ``None`` = the module default.
     """
@@ -213,7 +220,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                                   int(count), int(stride), int(seq), int(rows_hint),
                                   _PAIR_MODE if pair is None else int(pair),
                                   scatter[0] if scatter is not None else None,
-                                  scatter[1] if scatter is not None else [], float(alpha))
+                                  scatter[1] if scatter is not None else [], float(alpha), a2, b2)
     if scatter is not None:
         raise RuntimeError('grouped_gemm: the fused combine needs the CUDA kernel (unsupported shape or dtype)')
     if wait is not None:
@@ -222,8 +229,19 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     # are not a multiple of 8 elements, more than 1024 groups) and every CPU tensor:
     # per-group matmuls in fp32.  On CUDA this reads the group sizes back to the host.
     acc = _cpu_grouped_gemm(a, b, bins, trans_a, trans_b, num_groups)
+    if a2 is not None:
+        acc = acc + _cpu_grouped_gemm(a2, b2, bins, trans_a, trans_b, num_groups)
     if alpha != 1.0:
         acc = acc * alpha
+    if epilogue == EPI_GLU_DUAL:
+        z1 = acc.to(a.dtype)
+        z2 = (_cpu_grouped_gemm(a, b2, bins, trans_a, trans_b, num_groups) * alpha).to(a.dtype)
+        out = (z2, (act_forward(z1.float(), act) * z2.float()).to(a.dtype), z1)
+        last = int(bins[-1])
+        for t in out:
+            if last < t.shape[0]:
+                t[last:] = 0
+        return out
     out, out2, out3 = _cpu_epilogue(acc, epilogue, act, aux1, aux2, a.dtype)
     if not trans_a:
         # Rows past the last bin belong to no group: defined as zero.

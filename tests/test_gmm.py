@@ -270,3 +270,42 @@ def test_alpha_scales_the_accumulators(device):
         ref.append(g[start:start + c].float().cpu().t() @ a[start:start + c].float().cpu())
         start += c
     _close(dw, torch.stack(ref) * 0.125, dtype)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('z,m,k,n', [(4, 600, 128, 256), (3, 1000, 192, 384), (8, 4096, 256, 1024), (2, 130, 64, 200)])
+@pytest.mark.parametrize('act', [G.ACT_SILU, G.ACT_GELU_TANH])
+def test_glu_forward_in_one_launch(device, z, m, k, n, act):
+    """Two weight operands per tile: (x v^T, act(x w^T) * (x v^T), x w^T) against per-group fp32 products."""
+    dtype = _dtype_for(device)
+    counts, bins = _sizes(z, m, device)
+    a = torch.randn(m, k).mul(0.5).to(dtype).to(device)
+    w = torch.randn(z, n, k).mul(0.2).to(dtype).to(device)
+    v = torch.randn(z, n, k).mul(0.2).to(dtype).to(device)
+    z2, h, z1 = G.grouped_gemm(a, w, bins, trans_b=True, epilogue=G.EPI_GLU_DUAL, act=act, b2=v)
+    r1 = _ref_gmm(a.cpu(), w.cpu(), counts, True)
+    r2 = _ref_gmm(a.cpu(), v.cpu(), counts, True)
+    _close(z1, r1, dtype)
+    _close(z2, r2, dtype)
+    want_h = G.act_forward(z1.detach().cpu().float(), act) * z2.detach().cpu().float()   # from the rounded outputs
+    _close(h, want_h, dtype)
+    if device == 'cuda':
+        # Same numbers as the two-launch form.
+        s1, _, _ = G.grouped_gemm(a, w, bins, trans_b=True)
+        s2, sh, _ = G.grouped_gemm(a, v, bins, trans_b=True, epilogue=G.EPI_GLU, act=act, aux1=s1)
+        assert torch.equal(s1, z1) and torch.equal(s2, z2) and torch.equal(sh, h)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('z,m,k,n', [(4, 600, 256, 128), (3, 1000, 320, 192), (8, 4096, 1024, 256), (2, 130, 72, 64)])
+def test_two_operand_pairs_in_one_contraction(device, z, m, k, n):
+    """c = a b + a2 b2 (the GLU input gradient) against per-group fp32 products."""
+    dtype = _dtype_for(device)
+    counts, bins = _sizes(z, m, device)
+    a = torch.randn(m, k).mul(0.5).to(dtype).to(device)
+    a2 = torch.randn(m, k).mul(0.5).to(dtype).to(device)
+    b = torch.randn(z, k, n).mul(0.1).to(dtype).to(device)
+    b2 = torch.randn(z, k, n).mul(0.1).to(dtype).to(device)
+    out, _, _ = G.grouped_gemm(a, b, bins, a2=a2, b2=b2)
+    ref = _ref_gmm(a.cpu(), b.cpu(), counts, False) + _ref_gmm(a2.cpu(), b2.cpu(), counts, False)
+    _close(out, ref, dtype)
