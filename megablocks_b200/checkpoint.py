@@ -13,7 +13,8 @@ world of ``W`` owns experts ``(r % esd) * E/esd ..`` and ffn rows
 * converts between expert-parallel degrees (``reshard``), relying only on that
   slicing rule, so a model trained at EP=8 can be loaded at EP=1, 2, 4 ... and
   back, for both the dropless (2-D) and the token-dropping (3-D) weight layouts,
-* round-trips the optimizer state of :class:`megablocks_b200.train.Trainer`.
+* round-trips the optimizer state of :class:`megablocks_b200.train.Trainer`, also across
+  expert-parallel degrees (fused Adam: per-parameter state resharded like the weights).
 """
 
 import json
@@ -84,6 +85,22 @@ def reshard(shards: List[Dict[str, torch.Tensor]], new_world: int, num_experts: 
     return out
 
 
+_ADAM_PARTS = ('master', 'exp_avg', 'exp_avg_sq')
+
+
+def _named_opt_state(shard: Dict) -> Dict[str, Dict[str, torch.Tensor]]:
+    """Cut one rank's flat Adam buffers into per-parameter tensors with the layout the trainer saved."""
+    named = {}
+    for opt_key, entries in shard['opt_layout'].items():
+        flat = shard[opt_key]
+        for name, off, shape in entries:
+            n = 1
+            for d in shape:
+                n *= d
+            named[name] = {part: flat[part][off:off + n].view(shape) for part in _ADAM_PARTS}
+    return named
+
+
 def save(directory: str, state: Dict, rank: int, world: int, num_experts: int, step: int = 0) -> None:
     """Write this rank's shard; rank 0 also writes ``manifest.json``."""
     os.makedirs(directory, exist_ok=True)
@@ -101,8 +118,12 @@ def manifest(directory: str) -> Dict:
 def load(directory: str, rank: int, world: int, map_location='cpu') -> Dict:
     """Load the model shard for ``rank`` of ``world``, resharding if the checkpoint was saved at another degree.
 
-    Returns ``{'model': state_dict, ...}``; optimizer state is returned only when the
-    degrees match (moments are tied to the weight layout they were accumulated in).
+    At the saved degree the shard is returned as written.  At another degree the result holds the
+    resharded ``'model'`` and, when the trainer's fused Adam wrote the checkpoint, ``'opt_named'``:
+    fp32 master weights and both moments per parameter name, the expert weights' state resharded by
+    the same slicing rule as the weights and the replicated parameters' state taken from rank 0.
+    ``Trainer.load_state_dict`` accepts either form.  ZeRO-sharded or Adafactor state is not
+    converted (those moments restart).
     """
     meta = manifest(directory)
     saved_world = int(meta['world'])
@@ -110,5 +131,20 @@ def load(directory: str, rank: int, world: int, map_location='cpu') -> Dict:
         return torch.load(os.path.join(directory, f'shard_{rank:05d}_of_{world:05d}.pt'), map_location=map_location)
     shards = [torch.load(os.path.join(directory, f'shard_{r:05d}_of_{saved_world:05d}.pt'), map_location=map_location)
               for r in range(saved_world)]
-    models = reshard([s['model'] for s in shards], world, int(meta['num_experts']))
-    return {'model': models[rank], 'step': shards[0].get('step', meta.get('step', 0))}
+    num_experts = int(meta['num_experts'])
+    models = reshard([s['model'] for s in shards], world, num_experts)
+    out = {'model': models[rank], 'step': shards[0].get('step', meta.get('step', 0))}
+    if all('opt_layout' in s for s in shards):
+        named = [_named_opt_state(s) for s in shards]
+        out['opt_named'] = {}
+        for key, entry in named[0].items():
+            if is_expert_key(key):
+                out['opt_named'][key] = {
+                    part: _from_full(_to_full([n[key][part] for n in named], num_experts, key), world, rank,
+                                     entry[part], key) for part in _ADAM_PARTS}
+            else:
+                out['opt_named'][key] = entry
+        out['opt_step'] = shards[0]['expert_opt']['step']
+        if 'loss_scaler' in shards[0]:
+            out['loss_scaler'] = shards[0]['loss_scaler']
+    return out

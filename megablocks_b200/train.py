@@ -310,15 +310,54 @@ class Trainer:
         self.flush()
         state = {'model': self.model.state_dict(), 'dense_opt': self.dense_opt.state_dict(),
                  'expert_opt': self.expert_opt.state_dict(), 'step': self.step_count}
+        state['opt_layout'] = self._opt_layout()
         if self.scaler is not None:
             state['loss_scaler'] = self.scaler.state_dict()
         return state
 
+    def _opt_groups(self):
+        """(optimizer, its tensors) for the optimizers whose flat state is laid out per parameter."""
+        groups = []
+        if isinstance(self.expert_opt, FusedAdam):
+            groups.append(('expert_opt', self.expert_opt, self.expert_params))
+        if isinstance(self.dense_opt, FusedAdam) and not (self.world > 1 and self.cfg.zero1):
+            groups.append(('dense_opt', self.dense_opt, self.dense_params))
+        return groups
+
+    def _opt_layout(self):
+        """Where every named parameter's Adam state sits in the flat buffers: ``{optimizer: [(name,
+        offset, shape)]}``.  With it a checkpoint can be converted to another expert-parallel degree
+        (:func:`megablocks_b200.checkpoint.load`): the state is cut out per parameter and resharded
+        by the same rule as the weights.  ZeRO-sharded and Adafactor state has no such layout and is
+        left out (it restarts after a change of degree)."""
+        names = {id(p): n for n, p in self.model.named_parameters()}
+        return {key: [(names[id(p)], off, list(p.shape)) for p, off in zip(opt.params, opt.offsets)]
+                for key, opt, _ in self._opt_groups()}
+
+    def _load_named_opt_state(self, named, step):
+        names = {id(p): n for n, p in self.model.named_parameters()}
+        for _, opt, _ in self._opt_groups():
+            for p, off in zip(opt.params, opt.offsets):
+                n, entry = p.numel(), named.get(names[id(p)])
+                if entry is None:      # no state for this tensor: keep the loaded weights, restart the moments
+                    opt.master[off:off + n].copy_(p.detach().reshape(-1))
+                    opt.exp_avg[off:off + n].zero_()
+                    opt.exp_avg_sq[off:off + n].zero_()
+                    continue
+                for part in ('master', 'exp_avg', 'exp_avg_sq'):
+                    getattr(opt, part)[off:off + n].copy_(entry[part].reshape(-1))
+                p.data.copy_(opt.master[off:off + n].view_as(p))
+            opt.step_count = int(step)
+
     def load_state_dict(self, state):
         self.flush()
         self.model.load_state_dict(state['model'])
-        self.dense_opt.load_state_dict(state['dense_opt'])
-        self.expert_opt.load_state_dict(state['expert_opt'])
+        if 'opt_named' in state:
+            # Written at another expert-parallel degree and converted by checkpoint.load.
+            self._load_named_opt_state(state['opt_named'], state.get('opt_step', state['step']))
+        else:
+            self.dense_opt.load_state_dict(state['dense_opt'])
+            self.expert_opt.load_state_dict(state['expert_opt'])
         self.step_count = int(state['step'])
         if self.scaler is not None and 'loss_scaler' in state:
             self.scaler.load_state_dict(state['loss_scaler'])

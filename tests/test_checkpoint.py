@@ -69,3 +69,92 @@ def test_slicing_rule_matches_layer_construction():
     args = mb.Arguments(hidden_size=16, ffn_hidden_size=32, moe_num_experts=4, fp16=False, device=torch.device('cpu'))
     assert mlp_mod._rank_slice(args, 4, 32) == (slice(0, 4), slice(0, 32))
     assert checkpoint.is_expert_key('blocks.3.moe.experts.mlp.v1') and not checkpoint.is_expert_key('experts.bias')
+
+
+# ---------------------------------------------------------------------------------------------
+# Optimizer state across expert-parallel degrees: EP=2 -> EP=1 -> EP=2 must give back every
+# rank's fp32 master weights and Adam moments bit for bit, and the merged single-process
+# trainer must hold the two ranks' expert state side by side.
+
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+def _named_state(trainer):
+    out = {}
+    for key, entries in trainer._opt_layout().items():
+        opt = getattr(trainer, key)
+        for name, off, shape in entries:
+            n = int(torch.tensor(shape).prod())
+            out[name] = {part: getattr(opt, part)[off:off + n].clone() for part in ('master', 'exp_avg', 'exp_avg_sq')}
+    return out
+
+
+def _tiny_trainer(group):
+    from megablocks_b200.models.transformer import MoETransformer, preset
+    from megablocks_b200.train import Trainer, TrainerConfig
+    torch.manual_seed(0)
+    cfg = preset('tiny', dtype=torch.float32, expert_parallel_group=group)
+    model = MoETransformer(cfg)
+    return cfg, Trainer(model, TrainerConfig(lr=1e-2, schedule=False, bucket_mb=1), dp_group=group)
+
+
+def _ep2_worker(rank, world, port, root, phase):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        cfg, trainer = _tiny_trainer(dist.group.WORLD)
+        if phase == 'train':
+            gen = torch.Generator().manual_seed(20 + rank)
+            for _ in range(2):
+                batch = torch.randint(0, cfg.vocab_size, (2, 33), generator=gen)
+                trainer.step(batch[:, :-1], batch[:, 1:])
+            checkpoint.save(os.path.join(root, 'ep2'), trainer.state_dict(), rank, world, cfg.moe_num_experts, step=2)
+            torch.save(_named_state(trainer), os.path.join(root, f'want{rank}.pt'))
+        else:
+            state = checkpoint.load(os.path.join(root, 'ep1'), rank, world)
+            assert 'opt_named' in state
+            trainer.load_state_dict(state)
+            torch.save(_named_state(trainer), os.path.join(root, f'got{rank}.pt'))
+            assert trainer.step_count == 2 and trainer.expert_opt.step_count == 2
+            batch = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(5 + rank))
+            assert torch.isfinite(trainer.step(batch[:, :-1], batch[:, 1:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_optimizer_state_survives_a_change_of_expert_parallel_degree(tmp_path):
+    import os
+    import torch.multiprocessing as mp
+    root = str(tmp_path)
+    mp.spawn(_ep2_worker, args=(2, _free_port(), root, 'train'), nprocs=2, join=True)
+    # EP=2 -> one process.
+    cfg, single = _tiny_trainer(None)
+    state = checkpoint.load(os.path.join(root, 'ep2'), 0, 1)
+    single.load_state_dict(state)
+    merged = _named_state(single)
+    want = [torch.load(os.path.join(root, f'want{r}.pt')) for r in range(2)]
+    for name, entry in merged.items():
+        for part, value in entry.items():
+            if checkpoint.is_expert_key(name):
+                both = torch.cat([want[0][name][part], want[1][name][part]])
+                assert torch.equal(value, both), (name, part)           # dropless layout: ranks stack along rows
+            else:
+                assert torch.equal(value, want[0][name][part]), (name, part)
+    for name, p in single.model.named_parameters():                     # weights follow the master copies
+        assert torch.equal(p.detach().reshape(-1), merged[name]['master'])
+    assert single.expert_opt.step_count == 2 and single.dense_opt.step_count == 2
+    checkpoint.save(os.path.join(root, 'ep1'), single.state_dict(), 0, 1, cfg.moe_num_experts, step=2)
+    # ... and back to EP=2: every rank gets exactly what it saved.
+    mp.spawn(_ep2_worker, args=(2, _free_port(), root, 'restore'), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(os.path.join(root, f'got{r}.pt'))
+        assert got.keys() == want[r].keys()
+        for name in got:
+            for part in got[name]:
+                assert torch.equal(got[name][part], want[r][name][part]), (r, name, part)
