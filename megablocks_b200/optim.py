@@ -170,6 +170,12 @@ class FusedAdam:
             w.sub_(self.lr * ((m / bias1) / denom + self.weight_decay * w))
             p.data.copy_(w.view_as(p))
 
+    def resync_master(self):
+        """Take the fp32 master weights from the parameters again (after the model was loaded from a
+        checkpoint that carries no optimizer state)."""
+        for p, off in zip(self.params, self.offsets):
+            self.master[off:off + p.numel()].copy_(p.detach().reshape(-1))
+
     def state_dict(self):
         return {'step': self.step_count, 'master': self.master, 'exp_avg': self.exp_avg,
                 'exp_avg_sq': self.exp_avg_sq, 'lr': self.lr}
@@ -268,6 +274,11 @@ class Adafactor:
                 w.mul_(1.0 - self.lr * self.weight_decay)
             w.add_(update, alpha=-self.lr)
             p.data.copy_(w.view_as(p))
+
+    def resync_master(self):
+        """Take the fp32 master weights from the parameters again."""
+        for p, w in zip(self.params, self.master):
+            w.copy_(p.detach().reshape(w.shape))
 
     def state_dict(self):
         return {'step': self.step_count, 'lr': self.lr, 'master': self.master, 'row': self.row, 'col': self.col,

@@ -352,13 +352,18 @@ class Trainer:
     def load_state_dict(self, state):
         self.flush()
         self.model.load_state_dict(state['model'])
-        if 'opt_named' in state:
-            # Written at another expert-parallel degree and converted by checkpoint.load.
-            self._load_named_opt_state(state['opt_named'], state.get('opt_step', state['step']))
-        else:
+        if 'dense_opt' in state and 'expert_opt' in state:
             self.dense_opt.load_state_dict(state['dense_opt'])
             self.expert_opt.load_state_dict(state['expert_opt'])
-        self.step_count = int(state['step'])
+        else:
+            # Weights only, or written at another expert-parallel degree and converted by
+            # checkpoint.load: the master copies follow the loaded weights, then whatever
+            # per-parameter state the checkpoint carries is put in place.
+            self.dense_opt.resync_master()
+            self.expert_opt.resync_master()
+            if 'opt_named' in state:
+                self._load_named_opt_state(state['opt_named'], state.get('opt_step', state.get('step', 0)))
+        self.step_count = int(state.get('step', 0))
         if self.scaler is not None and 'loss_scaler' in state:
             self.scaler.load_state_dict(state['loss_scaler'])
 
@@ -480,9 +485,7 @@ def main(argv=None):
                       dp_group=group, pipeline=stage)
     if args.load:
         state = checkpoint.load(args.load, rank, world, map_location=device)
-        model.load_state_dict(state['model'])
-        if 'dense_opt' in state:
-            trainer.load_state_dict(state)
+        trainer.load_state_dict(state)
     # The loss lives on the last pipeline stage: its first rank reports.
     reporter = stage_index == pp - 1 and stage_rank == 0
     logger = JsonlLogger(args.log, 0 if reporter else 1)

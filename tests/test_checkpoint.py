@@ -158,3 +158,21 @@ def test_optimizer_state_survives_a_change_of_expert_parallel_degree(tmp_path):
         for name in got:
             for part in got[name]:
                 assert torch.equal(got[name][part], want[r][name][part]), (r, name, part)
+
+
+def test_weights_only_checkpoint_refreshes_the_master_copies():
+    """A checkpoint without optimizer state must not let the first update start from stale fp32 masters."""
+    _, donor = _tiny_trainer(None)
+    _, trainer = _tiny_trainer(None)
+    with torch.no_grad():
+        for p in donor.model.parameters():
+            p.add_(0.25)
+    trainer.load_state_dict({'model': donor.model.state_dict()})
+    for opt in (trainer.dense_opt, trainer.expert_opt):
+        for p, off in zip(opt.params, opt.offsets):
+            assert torch.equal(opt.master[off:off + p.numel()], p.detach().reshape(-1))
+    want = {n: p.detach().clone() for n, p in donor.model.named_parameters()}
+    batch = torch.randint(0, 512, (2, 33), generator=torch.Generator().manual_seed(1))
+    trainer.step(batch[:, :-1], batch[:, 1:])
+    for n, p in trainer.model.named_parameters():       # one lr=1e-2 Adam step away from the loaded weights
+        assert (p.detach() - want[n]).abs().max() <= 1.5e-2
