@@ -229,13 +229,18 @@ def run_ours(args):
     cfg = preset('dmoe-125m', device=torch.device('cuda', local), expert_parallel_group=group,
                  mlp_impl=args.mlp_impl, memory_optimized_mlp=args.memory_optimized_mlp, ep_fused_comm=fused)
     model = MoETransformer(cfg)
-    trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000), dp_group=group)
+    # One process: the whole step is recorded in a CUDA graph during the warm-up steps (two plain
+    # steps, then the recording) and the timed steps replay it.
+    use_graph = args.cuda_graph == 'on' or (args.cuda_graph == 'auto' and world == 1 and args.warmup >= 3)
+    trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000, cuda_graph=use_graph, graph_warmup_steps=2),
+                      dp_group=group)
     from megablocks_b200.utils.metrics import comm_timer
     out = _measure(trainer, world, rank, local, args.steps, args.warmup, ext().launch_count, comm_timer)
     status.check()
     if rank == 0:
         _emit('megablocks_b200', args.gpus, args.steps, args.warmup, *out,
               extra_config={'mlp_impl': args.mlp_impl, 'memory_optimized_mlp': args.memory_optimized_mlp,
+                            'cuda_graph_step': trainer._graph is not None,
                             'ep_comm': ('none' if world == 1 else
                                         'fused peer-memory kernels (remote stores + flags, no NCCL all-to-all)'
                                         if model.blocks[0].moe.experts._ep_workspaces else
@@ -287,6 +292,8 @@ def main():
     ap.add_argument('--mlp-impl', dest='mlp_impl', choices=['grouped', 'sparse'], default='grouped')
     ap.add_argument('--ep-comm', dest='ep_comm', choices=['auto', 'fused', 'nccl'], default='auto',
                     help='expert-parallel exchange: peer-memory kernels (auto/fused) or NCCL all-to-all')
+    ap.add_argument('--cuda-graph', dest='cuda_graph', choices=['auto', 'on', 'off'], default='auto',
+                    help='replay the training step from one CUDA graph (auto: on for a single process)')
     ap.add_argument('--ref-gmm', dest='ref_gmm', choices=['loop', 'grouped_mm'], default='loop',
                     help="reference arm only: its grouped_gemm dependency as the package's default per-expert "
                          'cuBLAS loop, or as one torch._grouped_mm launch per GEMM (the analogue of the '

@@ -53,6 +53,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2);
 int64_t read_status(bool clear);
 int64_t launch_count();
+void count_launches(int64_t n);
 at::Tensor gemm_role_timers(const at::Tensor& like);
 at::Tensor bsmm_op(int64_t mode, const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn,
                    const at::Tensor& idx0, const c10::optional<at::Tensor>& idx1,
@@ -104,7 +105,8 @@ at::Tensor column_sum_op(const at::Tensor& x);
 int64_t adam_record_size();
 void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t param_code,
                   int64_t grad_code, double lr, double beta1, double beta2, double eps, double weight_decay,
-                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale);
+                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale,
+                  const c10::optional<at::Tensor>& hyper);
 void grad_sqnorm_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t grad_code,
                     at::Tensor out_accum);
 void clip_coeff_op(const at::Tensor& sqnorm, double max_norm, double extra_scale, at::Tensor out);
@@ -132,6 +134,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &mb::grouped_gemm);
   m.def("read_status", &mb::read_status);
   m.def("launch_count", &mb::launch_count);
+  m.def("count_launches", &mb::count_launches);
   m.def("gemm_role_timers", &mb::gemm_role_timers,
         "Per-CTA cycle counters of the grouped GEMM roles (builds with -DMB_GEMM_TIMING)");
   m.def("cross_entropy_forward", &mb::cross_entropy_forward);

@@ -70,10 +70,11 @@ struct AdamTensor {
   float norm_weight;  // weight of this tensor in the squared gradient norm
   int pad_;
 };
-// `blocks[i] = {tensor index, chunk index}`; every CTA updates `chunk` elements.
+// `blocks[i] = {tensor index, chunk index}`; every CTA updates `chunk` elements.  `hyper` (nullable,
+// device memory) = {lr, bias1, bias2}, read by the kernel in place of the arguments of those names.
 cudaError_t adam_step(DType param_type, DType grad_type, const AdamTensor* tensors, const int2* blocks,
                       int num_blocks, int chunk, float lr, float beta1, float beta2, float eps, float weight_decay,
-                      float bias1, float bias2, const float* grad_scale, cudaStream_t stream);
+                      float bias1, float bias2, const float* grad_scale, const float* hyper, cudaStream_t stream);
 cudaError_t grad_sqnorm(DType grad_type, const AdamTensor* tensors, const int2* blocks, int num_blocks, int chunk,
                         float* out_accum, cudaStream_t stream);
 cudaError_t clip_coeff(const float* sqnorm, float max_norm, float extra_scale, float* out, cudaStream_t stream);

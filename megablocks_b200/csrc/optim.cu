@@ -45,12 +45,19 @@ __device__ __forceinline__ void store8f<float>(float* p, const float (&in)[8]) {
   __stcs(reinterpret_cast<float4*>(p + 4), make_float4(in[4], in[5], in[6], in[7]));
 }
 
-// grad_scale_ptr[0] multiplies every gradient (clip coefficient x 1/accumulation).
+// grad_scale_ptr[0] multiplies every gradient (clip coefficient x 1/accumulation).  `hyper`, when
+// given, holds {lr, bias1, bias2} in device memory and replaces the arguments of those names: a
+// launch recorded in a CUDA graph then follows the schedule without being re-recorded.
 template <typename P, typename G>
 __global__ void __launch_bounds__(kOptThreads)
 adam_kernel(const AdamTensor* __restrict__ tensors, const int2* __restrict__ blocks, int chunk, float lr,
             float beta1, float beta2, float eps, float weight_decay, float bias1, float bias2,
-            const float* __restrict__ grad_scale_ptr) {
+            const float* __restrict__ grad_scale_ptr, const float* __restrict__ hyper) {
+  if (hyper != nullptr) {
+    lr = hyper[0];
+    bias1 = hyper[1];
+    bias2 = hyper[2];
+  }
   const int2 job = blocks[blockIdx.x];
   const AdamTensor t = tensors[job.x];
   const int64_t begin = int64_t(job.y) * chunk;
@@ -169,11 +176,11 @@ __global__ void clip_coeff_kernel(const float* __restrict__ sqnorm, float max_no
 
 cudaError_t adam_step(DType param_type, DType grad_type, const AdamTensor* tensors, const int2* blocks,
                       int num_blocks, int chunk, float lr, float beta1, float beta2, float eps, float weight_decay,
-                      float bias1, float bias2, const float* grad_scale, cudaStream_t stream) {
+                      float bias1, float bias2, const float* grad_scale, const float* hyper, cudaStream_t stream) {
   if (num_blocks == 0) return cudaSuccess;
 #define MB_ADAM(P, G)                                                                                        \
   adam_kernel<P, G><<<num_blocks, kOptThreads, 0, stream>>>(tensors, blocks, chunk, lr, beta1, beta2, eps,   \
-                                                            weight_decay, bias1, bias2, grad_scale)
+                                                            weight_decay, bias1, bias2, grad_scale, hyper)
   if (param_type == kBF16 && grad_type == kBF16) MB_ADAM(__nv_bfloat16, __nv_bfloat16);
   else if (param_type == kF16 && grad_type == kF16) MB_ADAM(__half, __half);
   else if (param_type == kF32 && grad_type == kF32) MB_ADAM(float, float);

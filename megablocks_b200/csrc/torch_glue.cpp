@@ -815,8 +815,15 @@ int64_t adam_record_size() { return sizeof(AdamTensor); }
 
 void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chunk, int64_t param_code,
                   int64_t grad_code, double lr, double beta1, double beta2, double eps, double weight_decay,
-                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale) {
+                  double bias1, double bias2, const c10::optional<at::Tensor>& grad_scale,
+                  const c10::optional<at::Tensor>& hyper) {
   c10::cuda::CUDAGuard guard(table.device());
+  const float* hyper_ptr = nullptr;
+  if (hyper.has_value()) {
+    TORCH_CHECK(hyper->is_cuda() && hyper->scalar_type() == at::kFloat && hyper->numel() >= 3 && hyper->is_contiguous(),
+                "hyper must be three contiguous CUDA float32 values {lr, bias1, bias2}");
+    hyper_ptr = hyper->data_ptr<float>();
+  }
   const float* scale = nullptr;
   if (grad_scale.has_value()) {
     TORCH_CHECK(grad_scale->is_cuda() && grad_scale->scalar_type() == at::kFloat, "grad_scale must be CUDA float32");
@@ -824,7 +831,7 @@ void adam_step_op(const at::Tensor& table, const at::Tensor& blocks, int64_t chu
   }
   MB_CUDA_OK(adam_step(code_of(param_code), code_of(grad_code), table_ptr(table), blocks_ptr(blocks),
                        int(blocks.size(0)), int(chunk), float(lr), float(beta1), float(beta2), float(eps),
-                       float(weight_decay), float(bias1), float(bias2), scale, stream()));
+                       float(weight_decay), float(bias1), float(bias2), scale, hyper_ptr, stream()));
   MB_LAUNCHED(1);
 }
 
@@ -1193,6 +1200,10 @@ void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_
 }
 
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+// A replayed CUDA graph launches kernels that never pass through the ops above: the owner of the
+// graph adds the number it recorded, once per replay.
+void count_launches(int64_t n) { MB_LAUNCHED(n); }
 
 // Reads (and optionally clears) the status word of the current device; nonzero means
 // a kernel abandoned a wait.  Synchronises the device.

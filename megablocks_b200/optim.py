@@ -45,6 +45,10 @@ class FusedAdam:
         self.params: List[torch.Tensor] = [p for p in params]
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.step_count = 0
+        # Optional CUDA float32 tensor {lr, bias1, bias2}: when set, the kernel reads the three values
+        # from it instead of taking them as launch arguments (used by the trainer's CUDA-graph step,
+        # whose recorded launches must follow the schedule).
+        self.hyper: Optional[torch.Tensor] = None
         self.norm_weights = list(norm_weights) if norm_weights is not None else [1.0] * len(self.params)
         if not self.params:
             self.device = torch.device('cpu')
@@ -157,7 +161,7 @@ class FusedAdam:
         if self.device.type == 'cuda':
             blocks = self._blocks[self._block_start[lo]:self._block_start[hi]]
             ext().adam_step(self._table, blocks, _CHUNK, _CODES[self.dtype], _CODES[grads[0].dtype], self.lr, b1,
-                            b2, self.eps, self.weight_decay, bias1, bias2, grad_scale)
+                            b2, self.eps, self.weight_decay, bias1, bias2, grad_scale, self.hyper)
             return
         scale = float(grad_scale[0]) if grad_scale is not None else 1.0
         for p, g, off in list(zip(self.params, grads, self.offsets))[lo:hi]:

@@ -58,6 +58,13 @@ class TrainerConfig:
     loss_scaling: Optional[bool] = None
     init_loss_scale: float = 2.0**16
     loss_scale_window: int = 1000
+    # Record the whole step (forward, backward, norm, clip, both Adam updates) in ONE CUDA graph
+    # after `graph_warmup_steps` ordinary steps and replay it from then on.  Possible because no
+    # kernel of the step needs a size from the host: group sizes, the clip coefficient, the learning
+    # rate and Adam's bias corrections are all read from device memory.  Single process, bf16/fp32,
+    # fused Adam, fixed batch shape; anything else keeps running step by step.
+    cuda_graph: bool = False
+    graph_warmup_steps: int = 3
 
 
 class Trainer:
@@ -119,6 +126,8 @@ class Trainer:
         self.step_count = 0
         self.last_grad_norm = None
         self._h2d = None
+        self._graph = None           # (CUDAGraph, tokens, targets, loss, kernel launches per replay)
+        self._eager_steps = 0
 
     # -- deferred expert update ------------------------------------------------------
     def _plan_expert_update_groups(self, deferred: bool) -> None:
@@ -246,16 +255,108 @@ class Trainer:
             return torch.stack(lm_values).mean()
         return torch.zeros((), device=self.device)
 
+    # -- whole-step CUDA graph ---------------------------------------------------------
+    def _graph_eligible(self) -> bool:
+        return (self.cfg.cuda_graph and self.device.type == 'cuda' and self.world == 1 and self.pipeline is None
+                and self.scaler is None and self._update_stream is None
+                and isinstance(self.dense_opt, FusedAdam) and isinstance(self.expert_opt, FusedAdam)
+                and self.step_count <= max(int(self.cfg.total_steps), 1))     # rows of the schedule table
+
+    def _hyper_table(self) -> torch.Tensor:
+        """Row ``s`` = {learning rate, bias1, bias2} of the step taken when ``step_count == s``."""
+        cfg = self.cfg
+        rows = max(int(cfg.total_steps), 1) + 1
+        b1, b2 = cfg.betas
+        steps = torch.arange(rows, dtype=torch.float64)
+        lr = torch.tensor([cosine_lr(s, cfg.total_steps, cfg.lr, cfg.min_lr, cfg.warmup_fraction) if cfg.schedule
+                           else cfg.lr for s in range(rows)], dtype=torch.float64)
+        table = torch.stack([lr, 1.0 - b1**(steps + 1), 1.0 - b2**(steps + 1)], dim=1)
+        return table.float().to(self.device)
+
+    def _capture(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        from megablocks_b200._ext import ext
+        assert self.dense_opt.step_count == self.step_count and self.expert_opt.step_count == self.step_count
+        self._table = self._hyper_table()
+        self._graph_step = torch.tensor([self.step_count], dtype=torch.int64, device=self.device)
+        self._hyper = torch.zeros(3, dtype=torch.float32, device=self.device)
+        self.dense_opt.hyper = self.expert_opt.hyper = self._hyper
+        static_tokens, static_targets = tokens.clone(), targets.clone()
+        self._zero_grad()
+        torch.cuda.synchronize(self.device)
+        torch.cuda.empty_cache()     # the graph gets a pool of its own: hand back what the warm-up steps cached
+        graph = torch.cuda.CUDAGraph()
+        before = ext().launch_count()
+        counters = (self.step_count, self.dense_opt.step_count, self.expert_opt.step_count)
+        try:
+            with torch.cuda.graph(graph):
+                torch.index_select(self._table, 0, self._graph_step, out=self._hyper.view(1, 3))
+                self._graph_step.add_(1)
+                loss = self._step_eager(static_tokens, static_targets, zero_grad=False)
+        finally:
+            # Recording advanced the host-side counters without running anything: take that back.
+            self.step_count, self.dense_opt.step_count, self.expert_opt.step_count = counters
+        launches = ext().launch_count() - before
+        self._graph = (graph, static_tokens, static_targets, loss, launches)
+
+    def _graph_replay(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        from megablocks_b200._ext import ext
+        graph, static_tokens, static_targets, loss, launches = self._graph
+        static_tokens.copy_(tokens, non_blocking=True)
+        static_targets.copy_(targets, non_blocking=True)
+        graph.replay()
+        ext().count_launches(launches)
+        self.step_count += 1
+        self.dense_opt.step_count += 1
+        self.expert_opt.step_count += 1
+        return loss.clone()
+
+    def drop_graph(self) -> None:
+        """Forget the recorded step (before changing the model, the optimizers or the batch shape)."""
+        self._graph = None
+        self._eager_steps = 0
+        if isinstance(self.dense_opt, FusedAdam):
+            self.dense_opt.hyper = None
+        if isinstance(self.expert_opt, FusedAdam):
+            self.expert_opt.hyper = None
+
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Forward, backward, gradient reduction, clipping and the optimizer update.
 
         ``tokens`` / ``targets`` hold this rank's whole share of the step: ``grad_accum_steps``
         micro-batches stacked along dimension 0.  Returns the language-model loss as a device
         scalar (no host sync, except under fp16 loss scaling, which reads one overflow flag).
+
+        With ``cfg.cuda_graph`` the first ``graph_warmup_steps`` calls run kernel by kernel, the next
+        one records the step in a CUDA graph, and every call from then on copies the batch into the
+        graph's input buffers and replays it.
         """
+        if self._graph_eligible():
+            if self._graph is not None:
+                _, static_tokens, _, _, _ = self._graph
+                if static_tokens.shape != tokens.shape:
+                    self.drop_graph()
+            if self._graph is None and self._eager_steps >= self.cfg.graph_warmup_steps:
+                try:
+                    self._capture(tokens, targets)
+                except RuntimeError as err:      # something in the step cannot be recorded: stay kernel by kernel
+                    import warnings
+                    warnings.warn(f'CUDA-graph capture of the training step failed, continuing without: {err}')
+                    self.drop_graph()
+                    self.cfg = dataclasses.replace(self.cfg, cuda_graph=False)
+                    self._zero_grad()
+                    return self._step_eager(tokens, targets)
+            if self._graph is not None:
+                return self._graph_replay(tokens, targets)
+            self._eager_steps += 1
+        elif self._graph is not None:
+            self.drop_graph()        # past the end of the schedule table: back to plain launches
+        return self._step_eager(tokens, targets)
+
+    def _step_eager(self, tokens: torch.Tensor, targets: torch.Tensor, zero_grad: bool = True) -> torch.Tensor:
         cfg = self.cfg
         self.model.train()
-        self._zero_grad()
+        if zero_grad:
+            self._zero_grad()
         lm = self._forward_backward(tokens, targets)
         with nvtx_range('grad_reduce_wait'):
             if self.reducer is not None:
@@ -351,6 +452,7 @@ class Trainer:
 
     def load_state_dict(self, state):
         self.flush()
+        self.drop_graph()            # the recorded step counts from the old step number
         self.model.load_state_dict(state['model'])
         if 'dense_opt' in state and 'expert_opt' in state:
             self.dense_opt.load_state_dict(state['dense_opt'])

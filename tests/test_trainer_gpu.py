@@ -36,3 +36,61 @@ def test_deferred_expert_update_matches_inline_update():
     for name in params_a:
         torch.testing.assert_close(params_a[name], params_b[name], rtol=0, atol=2e-3, msg=name)
     assert losses_a[-1] < losses_a[0] + 1.0   # the run trained (no NaN, no blow-up)
+
+
+def _run_graph(graph: bool, steps: int = 8):
+    from megablocks_b200._ext import ext
+    dev = torch.device('cuda', 0)
+    torch.manual_seed(11)
+    cfg = preset('tiny', device=dev)
+    model = MoETransformer(cfg)
+    # A short schedule, so that warm-up, peak and decay all fall inside the run.
+    trainer = Trainer(model, TrainerConfig(lr=2e-3, min_lr=2e-4, total_steps=8, warmup_fraction=0.25, cuda_graph=graph,
+                                           graph_warmup_steps=2))
+    gen = torch.Generator().manual_seed(5)
+    losses, launches = [], []
+    for _ in range(steps):
+        batch = torch.randint(0, cfg.vocab_size, (4, 65), generator=gen).to(dev)
+        before = ext().launch_count()
+        losses.append(trainer.step(batch[:, :-1], batch[:, 1:]))
+        launches.append(ext().launch_count() - before)
+    torch.cuda.synchronize()
+    params = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
+    return [float(l) for l in losses], params, launches, trainer
+
+
+@pytest.mark.gpu
+def test_step_replayed_from_a_cuda_graph_matches_the_step_run_kernel_by_kernel():
+    losses_a, params_a, launches_a, eager = _run_graph(False)
+    losses_b, params_b, launches_b, graphed = _run_graph(True)
+    assert eager._graph is None and graphed._graph is not None          # the third step recorded, 3..8 replayed
+    # Same kernels on the same data: what differs is the order of a few atomics.  The batches
+    # differ per step, so equal losses show that every replay read its own batch; equal weights
+    # after a schedule of 8 different learning rates show that the replays followed the schedule.
+    torch.testing.assert_close(torch.tensor(losses_a), torch.tensor(losses_b), rtol=1e-4, atol=1e-4)
+    for name in params_a:
+        torch.testing.assert_close(params_a[name], params_b[name], rtol=0, atol=2e-3, msg=name)
+    assert len(set(round(l, 3) for l in losses_b)) > 4
+    # Host-side counters follow the replays; a replay reports the launches it recorded.
+    assert graphed.step_count == 8 and graphed.dense_opt.step_count == 8 and graphed.expert_opt.step_count == 8
+    assert launches_b[-1] == launches_a[-1] > 0
+    # One more step than the schedule table has rows for: the trainer goes back to plain launches.
+    batch = torch.randint(0, 512, (4, 65)).to('cuda:0')
+    graphed.step(batch[:, :-1], batch[:, 1:])
+    extra = graphed.step(batch[:, :-1], batch[:, 1:])
+    assert torch.isfinite(extra) and graphed.step_count == 10
+
+
+@pytest.mark.gpu
+def test_graph_is_recorded_again_after_a_checkpoint_is_loaded():
+    _, _, _, trainer = _run_graph(True, steps=4)
+    state = {k: (v if not isinstance(v, dict) else dict(v)) for k, v in trainer.state_dict().items()}
+    state['model'] = {k: v.clone() for k, v in state['model'].items()}
+    for key in ('dense_opt', 'expert_opt'):
+        state[key] = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in state[key].items()}
+    batch = torch.randint(0, 512, (4, 65), generator=torch.Generator().manual_seed(9)).to('cuda:0')
+    want = float(trainer.step(batch[:, :-1], batch[:, 1:]))             # step 5, replayed
+    trainer.load_state_dict(state)                                      # back to the state after step 4
+    assert trainer._graph is None and trainer.step_count == 4
+    got = float(trainer.step(batch[:, :-1], batch[:, 1:]))              # step 5 again, kernel by kernel
+    assert abs(got - want) < 1e-3
