@@ -44,6 +44,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--dp-comm', choices=['auto', 'peer', 'nccl'], default='auto')
     ap.add_argument('--ep-comm', choices=['auto', 'fused', 'nccl'], default='auto')
+    ap.add_argument('--gap-rows', dest='gap_rows', type=int, default=25)
     ap.add_argument('--rows', type=int, default=40)
     args = ap.parse_args()
     rank = int(os.environ.get('RANK', '0'))
@@ -111,13 +112,19 @@ def main():
         comm_names = ('dp_allreduce', 'ncclDevKernel', 'nccl')
         comm_intervals = [(s, e) for s, e, n in kernels if any(c in n for c in comm_names)]
         other = [(s, e) for s, e, n in kernels if not any(c in n for c in comm_names)]
-        for s, e, _ in kernels:
+        gaps = defaultdict(lambda: [0.0, 0])     # (kernel before, kernel after) -> [idle us, count]
+        last_name = None
+        for s, e, n in kernels:
             if cur_e is None or s > cur_e:
                 if cur_e is not None:
                     busy += cur_e - cur_s
-                cur_s, cur_e = s, e
+                    key = (_short(last_name)[:44], _short(n)[:44])
+                    gaps[key][0] += s - cur_e
+                    gaps[key][1] += 1
+                cur_s, cur_e, last_name = s, e, n
             else:
-                cur_e = max(cur_e, e)
+                if e > cur_e:
+                    cur_e, last_name = e, n
         if cur_e is not None:
             busy += cur_e - cur_s
         span = (kernels[-1][1] - kernels[0][0]) if kernels else 0.0
@@ -150,6 +157,11 @@ def main():
         total = sum(v[0] for v in by_name.values())
         for name, (ms, n) in sorted(by_name.items(), key=lambda kv: -kv[1][0])[:args.rows]:
             print(f'{name:82s} {ms / steps:9.3f} {ms / total:7.1%} {n / steps:14.1f}')
+        # Where the GPU sat idle: gaps between the end of one kernel and the start of the next
+        # (over all streams), summed per pair of neighbours.
+        print(f'\n{"idle after kernel":46s} {"before kernel":46s} {"ms/step":>8s} {"gaps/step":>10s}')
+        for (a, b), (us, n) in sorted(gaps.items(), key=lambda kv: -kv[1][0])[:args.gap_rows]:
+            print(f'{a:46s} {b:46s} {us / 1e3 / steps:8.3f} {n / steps:10.1f}')
     if world > 1:
         dist.destroy_process_group()
 

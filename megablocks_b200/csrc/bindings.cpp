@@ -50,7 +50,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
                                      const std::vector<int64_t>& scatter_args, double alpha,
-                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2);
+                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2,
+                                     const c10::optional<at::Tensor>& sqnorm);
 int64_t read_status(bool clear);
 int64_t launch_count();
 void count_launches(int64_t n);
@@ -90,7 +91,8 @@ void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const
                              const c10::optional<at::Tensor>& scale, double scale_mul);
 std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma,
                                           const c10::optional<at::Tensor>& beta, double eps,
-                                          const c10::optional<at::Tensor>& res);
+                                          const c10::optional<at::Tensor>& res,
+                                          const c10::optional<at::Tensor>& res_bias);
 std::vector<at::Tensor> layernorm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
                                            const at::Tensor& mean, const at::Tensor& rstd,
                                            const c10::optional<at::Tensor>& dres, bool rms);

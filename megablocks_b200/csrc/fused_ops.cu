@@ -323,7 +323,8 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                          int64_t rows, int cols, float eps, T* __restrict__ y, float* __restrict__ mean_out,
-                         float* __restrict__ rstd_out, const T* __restrict__ res, T* __restrict__ sum_out, int rms) {
+                         float* __restrict__ rstd_out, const T* __restrict__ res, const T* __restrict__ res_bias,
+                         T* __restrict__ sum_out, int rms) {
   constexpr int VEC = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   Pack<T, VEC> pg[MAXV], pb[MAXV];
@@ -371,8 +372,17 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
         const int c = (j * 32 + lane) * VEC;
         if (c < cols) {
           const Pack<T, VEC> pr = *reinterpret_cast<const Pack<T, VEC>*>(res + r * cols + c);
+          if (res_bias != nullptr) {
+            // A per-column vector that belongs to `res` (the bias of the layer that produced it):
+            // re-read per row, it stays in L1 and costs no registers between rows.
+            const Pack<T, VEC> pv = *reinterpret_cast<const Pack<T, VEC>*>(res_bias + c);
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]));
+            for (int k = 0; k < VEC; ++k)
+              px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]) + to_float(pv.v[k]));
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]));
+          }
           *reinterpret_cast<Pack<T, VEC>*>(sum_out + r * cols + c) = px[j];
         }
       }
@@ -490,15 +500,16 @@ __global__ void colsum_reduce_kernel(const float* __restrict__ partial, int slic
 
 template <typename T>
 bool launch_layernorm_fwd(const T* x, const T* gamma, const T* beta, int64_t rows, int cols, float eps, T* y,
-                          float* mean, float* rstd, const T* res, T* sum_out, int rms, int sms, cudaStream_t stream) {
+                          float* mean, float* rstd, const T* res, const T* res_bias, T* sum_out, int rms, int sms,
+                          cudaStream_t stream) {
   constexpr int kVec = 16 / sizeof(T);
   const int grid = max(1, min(ceil_div(rows, kLnWarps), sms * 6));
   const int packs = ceil_div(cols, 32 * kVec);
   switch (packs) {
-    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
-    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
-    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
-    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, sum_out, rms); break;
+    case 1: layernorm_fwd_reg_kernel<T, 1><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, res_bias, sum_out, rms); break;
+    case 2: layernorm_fwd_reg_kernel<T, 2><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, res_bias, sum_out, rms); break;
+    case 3: layernorm_fwd_reg_kernel<T, 3><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, res_bias, sum_out, rms); break;
+    case 4: layernorm_fwd_reg_kernel<T, 4><<<grid, kLnWarps * 32, 0, stream>>>(x, gamma, beta, rows, cols, eps, y, mean, rstd, res, res_bias, sum_out, rms); break;
     default:
       if (res != nullptr) return false;   // the wide-row kernel has no fused add
       layernorm_fwd_kernel<T><<<max(1, min(ceil_div(rows, kLnWarps), sms * 2)), kLnWarps * 32, 0, stream>>>(
@@ -556,14 +567,14 @@ bool layernorm_fusable(DType type, int cols) {
 }
 
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, bool rms,
-                          int sms, cudaStream_t stream) {
+                          float eps, void* y, float* mean, float* rstd, const void* res, const void* res_bias,
+                          void* sum_out, bool rms, int sms, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   MB_SWITCH_FLOAT(type, T, {
     if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
     if (!launch_layernorm_fwd<T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),
                                  rows, cols, eps, static_cast<T*>(y), mean, rstd, static_cast<const T*>(res),
-                                 static_cast<T*>(sum_out), rms ? 1 : 0, sms, stream))
+                                 static_cast<const T*>(res_bias), static_cast<T*>(sum_out), rms ? 1 : 0, sms, stream))
       return cudaErrorInvalidValue;
   })
   return cudaGetLastError();

@@ -911,6 +911,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    float2 sq_sum = make_float2(0.f, 0.f);      // sum of squares of what this thread stored (p.sqnorm)
     MB_T_DECL(t_acc);
     MB_T_DECL(t_epi);
     MB_T_DECL(t_ld);
@@ -1046,6 +1047,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * p.alpha);
           }
+          if constexpr (LAYOUT == kTN) {
+            // Weight gradients: their squared norm (the clip needs it) is taken here, from the
+            // fp32 values on their way out, instead of by a pass that reads the gradients back.
+            if (p.sqnorm != nullptr && lane < rows_ok) {
+              const int cols = p.N - col;       // even: rows are a multiple of 16 bytes
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 v = make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+                if (i < cols) sq_sum = __ffma2_rn(v, v, sq_sum);
+              }
+            }
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) raw[i] = 0u;
@@ -1099,6 +1112,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
     if (p.store_tma && lane == 0) bulk_wait_all();   // bulk stores complete before the CTA retires
+    if constexpr (LAYOUT == kTN) {
+      if (p.sqnorm != nullptr) {                     // one atomic per warp and launch
+        float total = sq_sum.x + sq_sum.y;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+        if (lane == 0 && ok) atomicAdd(p.sqnorm, total);
+      }
+    }
     MB_T_END(role0, t_epi);
     if (threadIdx.x == 0) {
       MB_T_WRITE(4, t_acc);

@@ -88,12 +88,13 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
                               cudaStream_t stream);
 int layernorm_grid(int64_t rows, int sms);   // CTAs (= rows of `partial`) the backward uses
 // Optional fusions (rows short enough for the register kernels, see layernorm_fusable): forward
-// normalises x + res and writes the sum to sum_out; backward adds dres to dx.  `rms`: RMS norm
+// normalises x + res (+ res_bias, a vector of `cols` values, when given) and writes the sum to
+// sum_out; backward adds dres to dx.  `rms`: RMS norm
 // (y = x * rsqrt(mean(x^2) + eps) * gamma; beta may be null, dbeta is then meaningless).
 bool layernorm_fusable(DType type, int cols);
 cudaError_t layernorm_fwd(DType type, const void* x, const void* gamma, const void* beta, int64_t rows, int cols,
-                          float eps, void* y, float* mean, float* rstd, const void* res, void* sum_out, bool rms,
-                          int sms, cudaStream_t stream);
+                          float eps, void* y, float* mean, float* rstd, const void* res, const void* res_bias,
+                          void* sum_out, bool rms, int sms, cudaStream_t stream);
 cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
                           float* partial, const void* dres, bool rms, int sms, cudaStream_t stream);
@@ -254,6 +255,9 @@ struct GemmParams {
   int band_n;      // NT / NN: column tiles per band of the tile walk (0 = the kernel's default)
   CUtensorMap a2_map;
   CUtensorMap b2_map;
+  // TN only, nullable: one fp32 accumulator in device memory that receives the sum of squares of
+  // everything the launch stores (the squared norm of a weight gradient, taken in the epilogue).
+  float* sqnorm;
   // Diagnostics for roofline experiments (results are meaningless): bit 0 = the producer issues no
   // operand loads, bit 1 = the MMA warp issues no MMAs.  Set from MB200_GEMM_DIAG; 0 in normal use.
   int diag;

@@ -494,7 +494,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      int64_t wait_stride, int64_t wait_seq, int64_t rows_hint, int64_t pair_mode,
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
                                      const std::vector<int64_t>& scatter_args, double alpha,
-                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2) {
+                                     const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2,
+                                     const c10::optional<at::Tensor>& sqnorm) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -534,6 +535,12 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   p.epilogue = int(epilogue);
   p.act = int(act);
   p.alpha = float(alpha);
+  if (sqnorm.has_value()) {
+    TORCH_CHECK(layout == kTN && pair_mode != 1 && sqnorm->is_cuda() && sqnorm->scalar_type() == at::kFloat &&
+                    sqnorm->numel() >= 1,
+                "sqnorm: a CUDA float32 accumulator, weight-gradient (TN) launches of the single-CTA kernel only");
+    p.sqnorm = sqnorm->data_ptr<float>();
+  }
   if (epilogue == kEpiDAct || epilogue == kEpiGlu || epilogue == kEpiDGlu || epilogue == kEpiAdd) {
     check_aux(aux1, "aux1");
     p.aux1 = aux1->data_ptr();
@@ -893,11 +900,13 @@ bool layernorm_can_fuse(const at::Tensor& x) {
   return x.is_cuda() && x.dim() == 2 && layernorm_fusable(float_code(x.scalar_type()), int(x.size(1)));
 }
 
-// Returns {y, mean, rstd, s}: s = x + res (or x itself without res) is the tensor that was normalised.
+// Returns {y, mean, rstd, s}: s = x + res [+ res_bias] (or x itself without res) is the tensor that
+// was normalised.
 // `beta` absent = RMS norm (no centring, no bias); the returned mean is then all zeros.
 std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma,
                                           const c10::optional<at::Tensor>& beta, double eps,
-                                          const c10::optional<at::Tensor>& res) {
+                                          const c10::optional<at::Tensor>& res,
+                                          const c10::optional<at::Tensor>& res_bias) {
   MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x); MB_CHECK_CONTIG(gamma);
   const bool rms = !beta.has_value();
   TORCH_CHECK(x.dim() == 2 && gamma.numel() == x.size(1) && gamma.scalar_type() == x.scalar_type() &&
@@ -913,13 +922,20 @@ std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor&
                 "layernorm: the fused residual needs a tensor like x and rows the register kernel holds");
     sum = at::empty_like(x);
   }
+  const void* res_bias_ptr = nullptr;
+  if (res_bias.has_value()) {
+    TORCH_CHECK(res.has_value() && res_bias->is_cuda() && res_bias->is_contiguous() &&
+                    res_bias->numel() == x.size(1) && res_bias->scalar_type() == x.scalar_type(),
+                "layernorm: res_bias goes with res and holds one value per column in the dtype of x");
+    res_bias_ptr = res_bias->data_ptr();
+  }
   auto fopts = x.options().dtype(at::kFloat);
   at::Tensor mean = at::empty({x.size(0)}, fopts), rstd = at::empty({x.size(0)}, fopts);
   MB_CUDA_OK(layernorm_fwd(float_code(x.scalar_type()), x.data_ptr(), gamma.data_ptr(),
                            rms ? nullptr : beta->data_ptr(), x.size(0), int(x.size(1)), float(eps), y.data_ptr(),
                            mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                           res.has_value() ? res->data_ptr() : nullptr, res.has_value() ? sum.data_ptr() : nullptr,
-                           rms, sm_count(), stream()));
+                           res.has_value() ? res->data_ptr() : nullptr, res_bias_ptr,
+                           res.has_value() ? sum.data_ptr() : nullptr, rms, sm_count(), stream()));
   MB_LAUNCHED(1);
   return {y, mean, rstd, sum};
 }

@@ -73,10 +73,12 @@ def mlp_backward(dy, x, w1, w2, v1, bins, act: int, saved, needs, wait=None, zer
         h = h_new
     dx = dw1 = dw2 = dv1 = None
     if needs[2]:
-        dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)
+        dw2, _, _ = G.grouped_gemm(h, dy, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale,
+                                   grad_norm=True)
     def wgrad(dz):      # [E, f, h] = dz^T x, or [E, h, f] = x^T dz for the [E, h, f] layout
         a, b = (x, dz) if w1_kn else (dz, x)
-        return G.grouped_gemm(a, b, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale)[0]
+        return G.grouped_gemm(a, b, bins, trans_a=True, num_groups=num_experts, alpha=wgrad_scale,
+                              grad_norm=True)[0]
 
     if needs[1]:
         dw1 = wgrad(dz1)

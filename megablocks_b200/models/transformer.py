@@ -72,7 +72,7 @@ class TransformerConfig:
             ffn_hidden_size=self.ffn_hidden_size,
             num_layers=self.num_layers,
             bias=not glu,
-            return_bias=False,
+            return_bias=True,      # the bias add rides in the next norm kernel (Block.forward)
             activation_fn=F.silu if glu else partial(F.gelu, approximate='tanh'),
             moe_num_experts=self.moe_num_experts,
             moe_top_k=self.moe_top_k,
@@ -165,12 +165,13 @@ class Attention(nn.Module):
         return self.proj(out.transpose(1, 2).reshape(b, s, -1))
 
 
-def _add_norm(norm: nn.Module, x: torch.Tensor, delta):
-    """``(x + delta, norm(x + delta))``."""
+def _add_norm(norm: nn.Module, x: torch.Tensor, delta, delta_bias=None):
+    """``(x + delta [+ delta_bias], norm(...))``; ``delta_bias`` is the per-column output bias of the
+    layer that produced ``delta``."""
     if hasattr(norm, 'add_forward'):
-        return norm.add_forward(x, delta)
+        return norm.add_forward(x, delta, delta_bias)
     if delta is not None:
-        x = x + delta
+        x = x + delta if delta_bias is None else x + delta + delta_bias
     return x, norm(x)
 
 
@@ -185,14 +186,18 @@ class Block(nn.Module):
         self.ln2 = norm(cfg.hidden_size, **kw)
         self.moe = (dMoE if cfg.dropless else MoE)(moe_args)
 
-    def forward(self, x: torch.Tensor, delta, rope):
-        """The residual stream arrives as ``x + delta`` (``delta`` may be ``None``) and leaves the same
-        way, so every residual add rides in the following norm's kernels."""
-        x, normed = _add_norm(self.ln1, x, delta)
+    def forward(self, x: torch.Tensor, delta, delta_bias, rope):
+        """The residual stream arrives as ``x + delta + delta_bias`` (``delta`` may be ``None``;
+        ``delta_bias`` is the previous MoE layer's output bias, one value per column, or ``None``)
+        and leaves the same way, so every residual add rides in the following norm's kernels."""
+        x, normed = _add_norm(self.ln1, x, delta, delta_bias)
         x, normed = _add_norm(self.ln2, x, self.attn(normed, rope))
         # The MoE layer is token-wise: it flattens every leading dimension, so the
         # [batch, seq, hidden] activations go in as they are (no transpose copy).
-        return x, self.moe(normed)
+        out = self.moe(normed)
+        if isinstance(out, tuple):        # return_bias: (output without the bias, bias vector)
+            return x, out[0], out[1]
+        return x, out, None
 
 
 class MoETransformer(nn.Module):
@@ -244,20 +249,20 @@ class MoETransformer(nn.Module):
         return x
 
     def _run_blocks(self, x: torch.Tensor):
-        """Residual stream through this process's blocks; returns ``(x, delta)`` with the last
-        block's output still to be added."""
+        """Residual stream through this process's blocks; returns ``(x, delta, delta_bias)`` with the
+        last block's output (and its bias vector, if any) still to be added."""
         rope = self._rope_for(x.shape[1], x.device)
-        delta = None
+        delta = delta_bias = None
         for block in self.blocks:
             if self.cfg.activation_checkpointing and self.training:
-                x, delta = checkpoint(block, x, delta, rope, use_reentrant=False)
+                x, delta, delta_bias = checkpoint(block, x, delta, delta_bias, rope, use_reentrant=False)
             else:
-                x, delta = block(x, delta, rope)
-        return x, delta
+                x, delta, delta_bias = block(x, delta, delta_bias, rope)
+        return x, delta, delta_bias
 
     def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
-        x, delta = self._run_blocks(self._embed(tokens))
-        return _add_norm(self.ln_f, x, delta)[1]
+        x, delta, delta_bias = self._run_blocks(self._embed(tokens))
+        return _add_norm(self.ln_f, x, delta, delta_bias)[1]
 
     def _aux_loss(self):
         """This stage's auxiliary losses of the forward pass just run (``None`` when there are none);
@@ -277,8 +282,10 @@ class MoETransformer(nn.Module):
         """One pipeline stage: token ids (first stage) or the previous stage's activations in,
         ``(activations for the next stage, auxiliary loss of this stage or None)`` out.  The last
         stage returns the un-normalised residual stream for :meth:`stage_loss`."""
-        x, delta = self._run_blocks(self._embed(inp) if self.is_first_stage else inp)
-        return (x if delta is None else x + delta), self._aux_loss()
+        x, delta, delta_bias = self._run_blocks(self._embed(inp) if self.is_first_stage else inp)
+        if delta is not None:
+            x = x + delta if delta_bias is None else x + delta + delta_bias
+        return x, self._aux_loss()
 
     def stage_loss(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Last stage: final norm, LM head and cross entropy."""

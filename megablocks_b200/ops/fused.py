@@ -59,7 +59,7 @@ class _LayerNorm(torch.autograd.Function):
     def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).contiguous()
-        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, bias, eps, None)
+        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, bias, eps, None, None)
         ctx.save_for_backward(x2, weight, mean, rstd)
         ctx.shape = shape
         return y.view(shape)
@@ -72,27 +72,33 @@ class _LayerNorm(torch.autograd.Function):
 
 
 class _AddLayerNorm(torch.autograd.Function):
-    """``s = a + b; y = LayerNorm(s)`` in one pass; the backward adds ``ds`` while it writes ``dx``."""
+    """``s = a + b [+ b_bias]; y = LayerNorm(s)`` in one pass; the backward adds ``ds`` while it writes
+    ``dx``.  ``b_bias`` is a per-column vector that belongs to ``b`` (the output bias of the layer that
+    produced it): its add rides in the forward kernel and its gradient is one column sum of ``dx``."""
 
     @staticmethod
-    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, b_bias, weight: torch.Tensor, bias: torch.Tensor,
+                eps: float):
         shape = a.shape
         a2 = a.reshape(-1, shape[-1]).contiguous()
         b2 = b.reshape(-1, shape[-1]).contiguous()
-        y, mean, rstd, s = ext().layernorm_forward(a2, weight, bias, eps, b2)
+        y, mean, rstd, s = ext().layernorm_forward(a2, weight, bias, eps, b2, b_bias)
         ctx.save_for_backward(s, weight, mean, rstd)
         ctx.shape = shape
+        ctx.bias_grad = b_bias is not None and ctx.needs_input_grad[2]
         return s.view(shape), y.view(shape)
 
     @staticmethod
     def backward(ctx: Any, ds, dy):
         s, weight, mean, rstd = ctx.saved_tensors
         if dy is None:
-            return ds, ds, None, None, None
+            d2 = ds.reshape(s.shape).contiguous()
+            return ds, ds, (ext().column_sum(d2) if ctx.bias_grad else None), None, None, None
         dres = ds.reshape(s.shape).contiguous() if ds is not None else None
         dx, dw, db = ext().layernorm_backward(dy.reshape(s.shape).contiguous(), s, weight, mean, rstd, dres, False)
+        dbias = ext().column_sum(dx) if ctx.bias_grad else None
         dx = dx.view(ctx.shape)
-        return dx, dx, dw, db, None
+        return dx, dx, dbias, dw, db, None
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -104,17 +110,21 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: f
     return F.layer_norm(x, (cols,), weight, bias, eps)
 
 
-def add_layer_norm(a: torch.Tensor, b, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
-    """``(a + b, LayerNorm(a + b))``; ``b`` may be ``None``.  On CUDA the add rides in the norm's kernels."""
+def add_layer_norm(a: torch.Tensor, b, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5, b_bias=None):
+    """``(a + b, LayerNorm(a + b))``; ``b`` may be ``None``.  On CUDA the add rides in the norm's kernels.
+
+    ``b_bias`` (optional, one value per column) is added to ``b`` in the same pass."""
     if b is None:
         return a, layer_norm(a, weight, bias, eps)
     cols = a.shape[-1]
+    if b_bias is not None and not (b_bias.is_cuda and b_bias.dtype == a.dtype and b_bias.numel() == cols):
+        b, b_bias = b + b_bias, None
     fused = (a.is_cuda and b.is_cuda and a.dtype == b.dtype == weight.dtype and bias is not None
              and a.shape == b.shape and a.dtype in (torch.bfloat16, torch.float16, torch.float32)
              and ext().layernorm_can_fuse(a.reshape(-1, cols)))
     if fused:
-        return _AddLayerNorm.apply(a, b, weight, bias, eps)
-    s = a + b
+        return _AddLayerNorm.apply(a, b, b_bias, weight, bias, eps)
+    s = a + b if b_bias is None else a + b + b_bias
     return s, layer_norm(s, weight, bias, eps)
 
 
@@ -124,9 +134,9 @@ class LayerNorm(torch.nn.LayerNorm):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return layer_norm(x, self.weight, self.bias, self.eps)
 
-    def add_forward(self, a: torch.Tensor, b):
-        """``(a + b, self(a + b))`` with the add fused into the kernels; ``b`` may be ``None``."""
-        return add_layer_norm(a, b, self.weight, self.bias, self.eps)
+    def add_forward(self, a: torch.Tensor, b, b_bias=None):
+        """``(a + b [+ b_bias], self(...))`` with the adds fused into the kernels; ``b`` may be ``None``."""
+        return add_layer_norm(a, b, self.weight, self.bias, self.eps, b_bias)
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -136,7 +146,7 @@ class _RMSNorm(torch.autograd.Function):
     def forward(ctx: Any, x: torch.Tensor, weight: torch.Tensor, eps: float):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).contiguous()
-        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, None, eps, None)
+        y, mean, rstd, _ = ext().layernorm_forward(x2, weight, None, eps, None, None)
         ctx.save_for_backward(x2, weight, mean, rstd)
         ctx.shape = shape
         return y.view(shape)
@@ -156,7 +166,7 @@ class _AddRMSNorm(torch.autograd.Function):
         shape = a.shape
         a2 = a.reshape(-1, shape[-1]).contiguous()
         b2 = b.reshape(-1, shape[-1]).contiguous()
-        y, mean, rstd, s = ext().layernorm_forward(a2, weight, None, eps, b2)
+        y, mean, rstd, s = ext().layernorm_forward(a2, weight, None, eps, b2, None)
         ctx.save_for_backward(s, weight, mean, rstd)
         ctx.shape = shape
         return s.view(shape), y.view(shape)
@@ -209,7 +219,9 @@ class RMSNorm(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return rms_norm(x, self.weight, self.eps)
 
-    def add_forward(self, a: torch.Tensor, b):
+    def add_forward(self, a: torch.Tensor, b, b_bias=None):
+        if b is not None and b_bias is not None:
+            b = b + b_bias
         return add_rms_norm(a, b, self.weight, self.eps)
 
 

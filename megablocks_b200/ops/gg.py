@@ -178,13 +178,53 @@ def _cpu_epilogue(acc, epilogue, act, aux1, aux2, dtype):
 # ----------------------------------------------------------------------------
 # Raw (non-autograd) entry point.
 # ----------------------------------------------------------------------------
+class GradNormSink:
+    """Squared norms of weight gradients, taken by the GEMMs that produce them.
+
+    While a sink is installed (:func:`set_grad_norm_sink`), every weight-gradient launch that asks
+    for it (``grouped_gemm(..., trans_a=True, grad_norm=True)``) adds the sum of squares of its
+    output to a float32 slot of its own and the sink remembers ``output address -> slot``.  The
+    trainer later looks its gradient tensors up by address: a tensor it finds needs no second pass
+    over its elements for the clipping norm; one it does not find (autograd copied or accumulated
+    it) is summed the ordinary way, so nothing is ever counted twice.
+    """
+
+    def __init__(self, device, slots: int = 1024):
+        self.slots = torch.zeros(slots, dtype=torch.float32, device=device)
+        self._by_address = {}
+
+    def begin(self) -> None:
+        self.slots.zero_()
+        self._by_address.clear()
+
+    def _next(self):
+        i = len(self._by_address)
+        return (i, self.slots[i:i + 1]) if i < self.slots.numel() else (None, None)
+
+    def _record(self, out: torch.Tensor, slot: int) -> None:
+        self._by_address[out.data_ptr()] = (slot, out.numel())
+
+    def lookup(self, grad: torch.Tensor):
+        """Slot index of the launch that wrote exactly this tensor, or ``None``."""
+        hit = self._by_address.get(grad.data_ptr())
+        return hit[0] if hit is not None and hit[1] == grad.numel() else None
+
+
+_GRAD_NORM_SINK: Optional[GradNormSink] = None
+
+
+def set_grad_norm_sink(sink: Optional[GradNormSink]) -> None:
+    global _GRAD_NORM_SINK
+    _GRAD_NORM_SINK = sink
+
+
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_a: bool = False,
                  trans_b: bool = False, epilogue: int = EPI_NONE, act: int = ACT_IDENTITY,
                  aux1: Optional[torch.Tensor] = None, aux2: Optional[torch.Tensor] = None,
                  want_out2: bool = True, want_out3: bool = True, num_groups: Optional[int] = None,
                  c: Optional[torch.Tensor] = None, zero_tail: bool = True, wait=None,
                  rows_hint: int = 0, scatter=None, alpha: float = 1.0, pair: Optional[int] = None,
-                 a2: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None):
+                 a2: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None, grad_norm: bool = False):
     """Run one grouped GEMM; returns ``(c, out2, out3)`` (unused outputs are ``None``).
 
     ``bins`` may describe fewer rows than ``a`` has (the block-padded layout
@@ -209,18 +249,26 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
     gradient in one launch).
     ``pair`` overrides the kernel choice for this call: 1 = CTA pairs (``cta_group::2``, 256-row
     tiles) whenever the problem allows, 0 = single-CTA kernel, ``None`` = the module default.
+    ``grad_norm`` (with ``trans_a``): the output is a weight gradient; if a :class:`GradNormSink` is
+    installed the epilogue also adds the output's sum of squares to a slot of the sink.
     """
     if num_groups is None:
         num_groups = bins.numel()
     debug.check_groups(bins, a.shape[0])
     if a.is_cuda and ext().grouped_gemm_supported(a, b, bool(trans_a), bool(trans_b), int(num_groups)):
         flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
-        return ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
+        pair_mode = _PAIR_MODE if pair is None else int(pair)
+        sink, slot, slot_view = _GRAD_NORM_SINK, None, None
+        if grad_norm and sink is not None and trans_a and pair_mode != 1:
+            slot, slot_view = sink._next()
+        outs = ext().grouped_gemm(a, b, bins, bool(trans_a), bool(trans_b), int(epilogue), int(act), aux1, aux2,
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
-                                  int(count), int(stride), int(seq), int(rows_hint),
-                                  _PAIR_MODE if pair is None else int(pair),
+                                  int(count), int(stride), int(seq), int(rows_hint), pair_mode,
                                   scatter[0] if scatter is not None else None,
-                                  scatter[1] if scatter is not None else [], float(alpha), a2, b2)
+                                  scatter[1] if scatter is not None else [], float(alpha), a2, b2, slot_view)
+        if slot is not None:
+            sink._record(outs[0], slot)
+        return outs
     if scatter is not None:
         raise RuntimeError('grouped_gemm: the fused combine needs the CUDA kernel (unsupported shape or dtype)')
     if wait is not None:

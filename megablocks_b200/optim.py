@@ -114,18 +114,31 @@ class FusedAdam:
             out.append(p.grad)
         return out
 
-    def add_sqnorm(self, accum: torch.Tensor, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
-        """Add this group's weighted squared gradient norm to the fp32 scalar tensor ``accum[0]``."""
+    def add_sqnorm(self, accum: torch.Tensor, grads: Optional[Sequence[torch.Tensor]] = None,
+                   skip: Optional[Sequence[bool]] = None) -> None:
+        """Add this group's weighted squared gradient norm to the fp32 scalar tensor ``accum[0]``.
+
+        ``skip[i]`` leaves tensor ``i`` out (its norm is already known from elsewhere)."""
         if not self.params:
             return
         grads = self.grads() if grads is None else grads
         if self.device.type == 'cuda':
             self._upload_table(grads)
-            ext().grad_sqnorm(self._table, self._blocks, _CHUNK, _CODES[grads[0].dtype], accum)
             self._table_fresh = True
+            blocks = self._blocks
+            if skip is not None and any(skip):
+                key = tuple(bool(s) for s in skip)
+                if getattr(self, '_skip_key', None) != key:       # the same tensors every step: built once
+                    host = self._blocks.cpu()
+                    keep = ~torch.tensor(key, dtype=torch.bool)[host[:, 0].long()]
+                    self._skip_key, self._skip_blocks = key, host[keep].contiguous().to(self.device)
+                blocks = self._skip_blocks
+            if blocks.shape[0]:
+                ext().grad_sqnorm(self._table, blocks, _CHUNK, _CODES[grads[0].dtype], accum)
         else:
-            for g, w in zip(grads, self.norm_weights):
-                accum[0] += w * g.float().square().sum()
+            for i, (g, w) in enumerate(zip(grads, self.norm_weights)):
+                if skip is None or not skip[i]:
+                    accum[0] += w * g.float().square().sum()
 
     def step(self, grad_scale: Optional[torch.Tensor] = None, grads: Optional[Sequence[torch.Tensor]] = None) -> None:
         """One update.  ``grad_scale`` is an optional fp32 device scalar multiplied into every gradient."""

@@ -15,6 +15,7 @@ One process drives one GPU; ``torch.distributed`` (NCCL) connects them.
 """
 
 import dataclasses
+import os
 import time
 from typing import Optional
 
@@ -65,6 +66,10 @@ class TrainerConfig:
     # fused Adam, fixed batch shape; anything else keeps running step by step.
     cuda_graph: bool = False
     graph_warmup_steps: int = 3
+    # Take the squared norm of the expert weight gradients in the epilogue of the GEMMs that
+    # produce them instead of reading the gradients back for it (one optimizer step per backward
+    # pass only: no gradient accumulation, no pipeline).
+    fuse_grad_norm: bool = True
 
 
 class Trainer:
@@ -126,6 +131,11 @@ class Trainer:
         self.step_count = 0
         self.last_grad_norm = None
         self._h2d = None
+        self._norm_sink = None
+        if (cfg.fuse_grad_norm and os.environ.get('MB200_FUSE_GRAD_NORM', '1') != '0' and self.device.type == 'cuda' and isinstance(self.expert_opt, FusedAdam)
+                and self.expert_params and max(1, int(cfg.grad_accum_steps)) == 1 and pipeline is None):
+            from megablocks_b200.ops.gg import GradNormSink
+            self._norm_sink = GradNormSink(self.device)
         self._graph = None           # (CUDAGraph, tokens, targets, loss, kernel launches per replay)
         self._eager_steps = 0
 
@@ -357,7 +367,17 @@ class Trainer:
         self.model.train()
         if zero_grad:
             self._zero_grad()
-        lm = self._forward_backward(tokens, targets)
+        sink = self._norm_sink
+        if sink is not None:
+            from megablocks_b200.ops import gg
+            sink.begin()
+            gg.set_grad_norm_sink(sink)
+            try:
+                lm = self._forward_backward(tokens, targets)
+            finally:
+                gg.set_grad_norm_sink(None)
+        else:
+            lm = self._forward_backward(tokens, targets)
         with nvtx_range('grad_reduce_wait'):
             if self.reducer is not None:
                 self.reducer.finish()
@@ -370,7 +390,26 @@ class Trainer:
         with nvtx_range('grad_norm'):
             self._sqnorm.zero_()
             self.dense_opt.add_sqnorm(self._sqnorm, dense_grads)
-            self.expert_opt.add_sqnorm(self._sqnorm)
+            if sink is not None:
+                # Gradients that are exactly the output of a weight-gradient GEMM already have their
+                # sum of squares in a slot of the sink; the rest is summed by the kernel.
+                slots = [sink.lookup(g) if w == 1.0 else None
+                         for g, w in zip(self.expert_opt.grads(), self.expert_opt.norm_weights)]
+                self.expert_opt.add_sqnorm(self._sqnorm, skip=[s is not None for s in slots])
+                found = [s for s in slots if s is not None]
+                self.fused_norm_tensors = len(found)
+                if found:
+                    lo, hi = min(found), max(found) + 1
+                    if hi - lo == len(set(found)) == len(found):       # a run of slots, in any order
+                        self._sqnorm += sink.slots[lo:hi].sum()
+                    else:
+                        key = tuple(found)
+                        if getattr(self, '_slot_key', None) != key:    # the same launches every step: built once
+                            self._slot_key = key
+                            self._slot_index = torch.tensor(found, dtype=torch.int64, device=self.device)
+                        self._sqnorm += sink.slots.index_select(0, self._slot_index).sum()
+            else:
+                self.expert_opt.add_sqnorm(self._sqnorm)
             if self.world > 1:
                 dist.all_reduce(self._sqnorm, group=self.dp_group)
             if self.pipeline is not None and self.pipeline.world > 1:

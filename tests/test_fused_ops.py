@@ -84,6 +84,38 @@ def test_add_layer_norm(device, rows, cols, dtype):
 
 
 @pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,cols', [(1000, 768), (333, 1024), (64, 4096)])   # last: too wide to fuse, falls back
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_add_layer_norm_with_the_bias_of_the_added_tensor(device, rows, cols, dtype):
+    """``s = a + b + v`` (``v`` one value per column), ``LN(s)``, and the gradient of ``v`` (a column sum
+    of the gradient of ``s``), against the unfused fp32 chain."""
+    ln = fused.LayerNorm(cols).to(device=device, dtype=dtype)
+    with torch.no_grad():
+        ln.weight.copy_(torch.randn(cols) * 0.5 + 1)
+        ln.bias.copy_(torch.randn(cols) * 0.5)
+    a = torch.randn(rows, cols).to(dtype).to(device).requires_grad_(True)
+    b = (torch.randn(rows, cols) * 0.5).to(dtype).to(device).requires_grad_(True)
+    v = (torch.randn(cols) * 0.5).to(dtype).to(device).requires_grad_(True)
+    p1 = (torch.randn(rows, cols) / rows**0.5).to(dtype).to(device)
+    p2 = (torch.randn(rows, cols) / rows**0.5).to(dtype).to(device)
+    s, y = ln.add_forward(a, b, v)
+    ((y.float() * p1.float()).sum() + (s.float() * p2.float()).sum()).backward()
+    ar, br, vr = (t.detach().float().cpu().requires_grad_(True) for t in (a, b, v))
+    exact = ar + br + vr
+    sr = exact + ((exact.to(dtype).float() if dtype == torch.bfloat16 else exact) - exact).detach()
+    yr = F.layer_norm(sr, (cols,), ln.weight.detach().float().cpu(), ln.bias.detach().float().cpu(), ln.eps)
+    ((yr * p1.float().cpu()).sum() + (sr * p2.float().cpu()).sum()).backward()
+    tol = dict(rtol=2e-2, atol=4e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(s.detach().float().cpu(), sr.detach(), **tol)
+    torch.testing.assert_close(y.detach().float().cpu(), yr.detach(), **tol)
+    gtol = dict(rtol=2e-2, atol=4e-2 / rows**0.5) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(a.grad.float().cpu(), ar.grad, **gtol)
+    torch.testing.assert_close(b.grad.float().cpu(), br.grad, **gtol)
+    vtol = dict(rtol=3e-2, atol=3e-2 * float(vr.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(v.grad.float().cpu(), vr.grad, **vtol)
+
+
+@pytest.mark.parametrize('device', DEVICES)
 @pytest.mark.parametrize('rows,cin,cout', [(1000, 64, 768), (4099, 128, 2304), (7, 32, 8)])
 def test_linear_bias_gradient(device, rows, cin, cout):
     """``fused.Linear`` against ``nn.Linear`` in fp32: outputs and all three gradients."""

@@ -309,3 +309,35 @@ def test_two_operand_pairs_in_one_contraction(device, z, m, k, n):
     out, _, _ = G.grouped_gemm(a, b, bins, a2=a2, b2=b2)
     ref = _ref_gmm(a.cpu(), b.cpu(), counts, False) + _ref_gmm(a2.cpu(), b2.cpu(), counts, False)
     _close(out, ref, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('z,rows,m,n', [(4, 700, 128, 256), (8, 4096, 3072, 768), (5, 900, 200, 72), (64, 8192, 768, 3072)])
+def test_weight_gradient_launch_reports_its_squared_norm(z, rows, m, n):
+    """With a sink installed, a TN launch adds the sum of squares of what it stores to a slot of its own
+    (odd shapes: clipped rows and columns must not contribute; empty groups store zeros)."""
+    dtype = torch.bfloat16
+    idx = torch.randint(0, z, (rows,))
+    if z > 2:
+        idx[idx == 1] = 0
+    counts = torch.bincount(idx, minlength=z)
+    bins = torch.cumsum(counts, 0).int().cuda()
+    a = (torch.randn(rows, m) * 0.5).to(dtype).cuda()
+    b = (torch.randn(rows, n) * 0.5).to(dtype).cuda()
+    sink = G.GradNormSink(torch.device('cuda', 0), slots=8)
+    sink.begin()
+    G.set_grad_norm_sink(sink)
+    try:
+        first, _, _ = G.grouped_gemm(a, b, bins, trans_a=True, num_groups=z, alpha=0.5, grad_norm=True)
+        unasked, _, _ = G.grouped_gemm(a, b, bins, trans_a=True, num_groups=z)               # no slot taken
+        second, _, _ = G.grouped_gemm(b, a, bins, trans_a=True, num_groups=z, grad_norm=True)
+    finally:
+        G.set_grad_norm_sink(None)
+    after, _, _ = G.grouped_gemm(a, b, bins, trans_a=True, num_groups=z, grad_norm=True)     # no sink: ignored
+    assert sink.lookup(first) == 0 and sink.lookup(second) == 1
+    assert sink.lookup(unasked) is None and sink.lookup(after) is None and sink.lookup(first[0]) is None
+    got = sink.slots.cpu()
+    for slot, out in ((0, first), (1, second)):
+        want = float(out.float().square().sum())
+        assert abs(float(got[slot]) - want) <= 4e-3 * want       # fp32 values before their rounding to bf16
+    assert float(got[2:].abs().sum()) == 0.0

@@ -190,8 +190,8 @@ def test_pipeline_stage_checks_its_load_balancing_terms():
     hidden, aux = model.stage_forward(tokens)
     assert aux is not None and hidden.shape == (2, 32, cfg.hidden_size)
     # Two forwards without clearing in between: twice the terms a stage may hold.
-    x, delta = model._run_blocks(model._embed(tokens))
-    x, delta = model._run_blocks(model._embed(tokens))
+    model._run_blocks(model._embed(tokens))
+    model._run_blocks(model._embed(tokens))
     with pytest.raises(ValueError, match='Expected 1 token_per_experts'):
         batched_load_balancing_loss(model.moe_args)
     clear_load_balancing_loss()

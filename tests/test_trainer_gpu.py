@@ -7,6 +7,18 @@ from megablocks_b200.models.transformer import MoETransformer, preset
 from megablocks_b200.train import Trainer, TrainerConfig
 
 
+def _assert_same_training(params_a, params_b, lr: float, steps: int):
+    """Two runs that differ only in the order of a few atomics.  Parameters whose true gradient is
+    zero (the key part of the attention bias: softmax does not see it) carry pure rounding noise,
+    and Adam's normalised update turns noise into steps of the full learning rate, so single
+    elements may end up to ``2 * steps * lr`` apart; a real difference between the runs (a missed
+    batch, a wrong schedule, a stale weight) moves every element and shows in the mean."""
+    for name in params_a:
+        diff = (params_a[name] - params_b[name]).abs()
+        assert float(diff.mean()) <= 0.1 * lr and float(diff.max()) <= 2 * steps * lr + 1e-6, \
+            (name, float(diff.mean()), float(diff.max()))
+
+
 def _run(overlap: bool, steps: int = 4):
     dev = torch.device('cuda', 0)
     torch.manual_seed(7)
@@ -33,8 +45,7 @@ def test_deferred_expert_update_matches_inline_update():
     # order of a few shared-memory atomics (LayerNorm weight gradients): last-bit noise.
     torch.testing.assert_close(torch.tensor(losses_a), torch.tensor(losses_b), rtol=1e-4, atol=1e-4)
     assert abs(m_a - m_b) <= 1e-3 * max(1.0, abs(m_a))
-    for name in params_a:
-        torch.testing.assert_close(params_a[name], params_b[name], rtol=0, atol=2e-3, msg=name)
+    _assert_same_training(params_a, params_b, lr=1e-3, steps=4)
     assert losses_a[-1] < losses_a[0] + 1.0   # the run trained (no NaN, no blow-up)
 
 
@@ -68,8 +79,7 @@ def test_step_replayed_from_a_cuda_graph_matches_the_step_run_kernel_by_kernel()
     # differ per step, so equal losses show that every replay read its own batch; equal weights
     # after a schedule of 8 different learning rates show that the replays followed the schedule.
     torch.testing.assert_close(torch.tensor(losses_a), torch.tensor(losses_b), rtol=1e-4, atol=1e-4)
-    for name in params_a:
-        torch.testing.assert_close(params_a[name], params_b[name], rtol=0, atol=2e-3, msg=name)
+    _assert_same_training(params_a, params_b, lr=2e-3, steps=8)
     assert len(set(round(l, 3) for l in losses_b)) > 4
     # Host-side counters follow the replays; a replay reports the launches it recorded.
     assert graphed.step_count == 8 and graphed.dense_opt.step_count == 8 and graphed.expert_opt.step_count == 8
