@@ -65,7 +65,7 @@ def main():
             counts, recv_bins, done = ws.exchange_counts(tpe, seq)
             ws.push(x, indices, None, bins, counts, 0, seq, 1, done[0])
             flags, count, stride, _ = ws.arrival(0, seq)
-            ext().ep_wait_flags(flags, count * stride, seq, 19)
+            ext().ep_wait_flags(flags, count * stride, seq, 19, None)
             ws.release_receive_buffer(seq)
 
         push_ms = _time(push, world)

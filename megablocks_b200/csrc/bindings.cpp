@@ -51,7 +51,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
                                      const std::vector<int64_t>& scatter_args, double alpha,
                                      const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2,
-                                     const c10::optional<at::Tensor>& sqnorm);
+                                     const c10::optional<at::Tensor>& sqnorm,
+                                     const c10::optional<at::Tensor>& seq_base);
 int64_t read_status(bool clear);
 int64_t launch_count();
 void count_launches(int64_t n);
@@ -67,23 +68,27 @@ void symm_close(int64_t ptr);
 void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
                            int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
                            int64_t off_count_flags, int64_t seq, int64_t expert_capacity, at::Tensor counts_out,
-                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch);
+                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch,
+                           const c10::optional<at::Tensor>& seq_base);
 void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
                      const at::Tensor& bins, const at::Tensor& counts, const at::Tensor& peer_base, int64_t world,
                      int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                      int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
                      int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done,
-                     const c10::optional<at::Tensor>& dropped_rows);
+                     const c10::optional<at::Tensor>& dropped_rows, const c10::optional<at::Tensor>& seq_base);
 void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::Tensor& raw_counts,
                        const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
-                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done);
-void ep_set_flag_op(at::Tensor flag, int64_t value);
+                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done,
+                       const c10::optional<at::Tensor>& seq_base);
+void ep_set_flag_op(at::Tensor flag, int64_t value, const c10::optional<at::Tensor>& seq_base);
 void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_t world, int64_t rank,
                      int64_t off_grad, int64_t off_ready, int64_t off_done, int64_t start, int64_t count,
-                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas);
-void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code);
+                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas,
+                     const c10::optional<at::Tensor>& seq_base);
+void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code,
+                      const c10::optional<at::Tensor>& seq_base);
 
 // torch_glue.cpp: fused row-wise ops
 std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at::Tensor& targets);

@@ -79,6 +79,7 @@ dp_allreduce_kernel(DpLayout L, int64_t start, int64_t count, int bucket, int se
                     int* __restrict__ ticket, int* status) {
   constexpr int VEC = 16 / sizeof(T);
   const int W = L.world;
+  if (L.seq_base != nullptr) seq += *L.seq_base;
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = *reinterpret_cast<volatile int*>(status) == 0;
   __syncthreads();

@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(1024)
 exchange_counts_kernel(const int* __restrict__ tpe, EpLayout L, int seq, int expert_capacity,
                        int* __restrict__ counts_out, int* __restrict__ kept_out, int* __restrict__ recv_bins,
                        int* __restrict__ scratch_zero, int scratch_ints, int* status) {
+  if (L.seq_base != nullptr) seq += *L.seq_base;
   const int parity = seq & 1;
   const int64_t counts_off = L.off_counts + int64_t(parity) * L.world * L.num_experts * 4;
   // (a) my counts -> row `me` of every peer's matrix.
@@ -158,6 +159,7 @@ push_rows_kernel(const T* __restrict__ x, const int* __restrict__ indices, const
                  int seq, int top_k, int n, int cols, int* __restrict__ done, int* status,
                  T* __restrict__ dropped_rows) {
   extern __shared__ int smem[];
+  if (L.seq_base != nullptr) seq += *L.seq_base;
   int* dst_start = smem;                    // [E] first row of (me, e) in the owner's buffer
   int* src_start = smem + L.num_experts;    // [E] first sorted position of e here
   const int E = L.num_experts, W = L.world, epr = L.experts_per_rank;
@@ -262,6 +264,7 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, cons
                    const uint64_t* __restrict__ data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
                    int rows_bound, int ret_rows, int* __restrict__ done, const int* status) {
   extern __shared__ int smem[];
+  if (L.seq_base != nullptr) seq += *L.seq_base;
   const int E = L.num_experts, W = L.world, epr = L.experts_per_rank;
   if (*reinterpret_cast<const volatile int*>(status) != 0) return;   // inert after a recorded failure
   int* seg_end = smem;                 // [epr * W] inclusive end row of segment (j, s) here
@@ -349,11 +352,14 @@ return_rows_kernel(const T* __restrict__ y, const int* __restrict__ counts, cons
   }
 }
 
-__global__ void wait_flags_kernel(const int* flags, int count, int seq, int* status, int code) {
+__global__ void wait_flags_kernel(const int* flags, int count, int seq, const int* seq_base, int* status, int code) {
+  if (seq_base != nullptr) seq += *seq_base;
   if (threadIdx.x < count) wait_flag(flags + threadIdx.x, seq, status, code);
 }
 
-__global__ void set_flag_kernel(int* flag, int value) { st_release_sys(flag, value); }
+__global__ void set_flag_kernel(int* flag, int value, const int* seq_base) {
+  st_release_sys(flag, value + (seq_base != nullptr ? *seq_base : 0));
+}
 
 }  // namespace
 
@@ -401,14 +407,15 @@ cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const i
   return cudaGetLastError();
 }
 
-cudaError_t ep_wait_flags(const int* flags, int count, int seq, int* status, int code, cudaStream_t stream) {
+cudaError_t ep_wait_flags(const int* flags, int count, int seq, const int* seq_base, int* status, int code,
+                          cudaStream_t stream) {
   if (count > 1024) return cudaErrorInvalidValue;
-  wait_flags_kernel<<<1, 1024, 0, stream>>>(flags, count, seq, status, code);
+  wait_flags_kernel<<<1, 1024, 0, stream>>>(flags, count, seq, seq_base, status, code);
   return cudaGetLastError();
 }
 
-cudaError_t ep_set_flag(int* flag, int value, cudaStream_t stream) {
-  set_flag_kernel<<<1, 1, 0, stream>>>(flag, value);
+cudaError_t ep_set_flag(int* flag, int value, const int* seq_base, cudaStream_t stream) {
+  set_flag_kernel<<<1, 1, 0, stream>>>(flag, value, seq_base);
   return cudaGetLastError();
 }
 

@@ -57,6 +57,12 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Status codes written on an abandoned wait.
 constexpr int kErrProducer = 1, kErrMmaFull = 2, kErrMmaTmem = 3, kErrEpilogue = 4, kErrPeerRows = 18;
 
+// Sequence number of a launch: the host's value plus the device counter, when there is one (a
+// launch recorded in a CUDA graph takes a fresh number at every replay).
+__device__ __forceinline__ int seq_with_base(int seq, const int* base) {
+  return base != nullptr ? seq + __ldg(base) : seq;
+}
+
 template <int BLOCK_N>
 struct Config {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
@@ -675,7 +681,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       // A source that gets nothing back still needs its flag.
       if (blockIdx.x == 0 && acc == 0)
         st_release_sys_s32(reinterpret_cast<int*>(p.scatter_flag_base[s2] + p.scatter_flag_off) + p.scatter_rank,
-                           p.scatter_seq);
+                           seq_with_base(p.scatter_seq, p.seq_base));
     }
   }
   tcgen05_fence_before();
@@ -755,7 +761,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int* flag = p.wait_flags + s * p.wait_stride + tile.group;
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
-            while (ld_acquire_sys_s32(flag) < p.wait_seq) {
+            const int wait_seq = seq_with_base(p.wait_seq, p.seq_base);
+            while (ld_acquire_sys_s32(flag) < wait_seq) {
               if ((++spins & 63u) == 0u) {
                 if (*abort_flag != 0) { ok = false; break; }
                 if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -1105,7 +1112,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (atomicAdd(p.scatter_done + s2, cnt) + cnt == s_per_source[s2] * num_nb) {
               __threadfence_system();
               st_release_sys_s32(reinterpret_cast<int*>(p.scatter_flag_base[s2] + p.scatter_flag_off) +
-                                     p.scatter_rank, p.scatter_seq);
+                                     p.scatter_rank, seq_with_base(p.scatter_seq, p.seq_base));
             }
           }
         }

@@ -201,7 +201,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const int* flag = p.wait_flags + s * p.wait_stride + tile.group;
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
-            while (ld_acquire_sys_s32(flag) < p.wait_seq) {
+            while (ld_acquire_sys_s32(flag) < seq_with_base(p.wait_seq, p.seq_base)) {
               if ((++spins & 63u) == 0u) {
                 if (*abort_flag != 0) { ok = false; break; }
                 if (globaltimer_ns() - t0 > kWaitLimitNs) {

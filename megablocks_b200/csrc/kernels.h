@@ -139,6 +139,10 @@ struct EpLayout {
   int capacity_rows;        // rows the receive buffers can hold (stores past it are skipped)
   int64_t off_counts;       // int32 [2][world][num_experts]
   int64_t off_count_flags;  // int32 [world]
+  // Nullable: a counter in this GPU's memory whose value every kernel adds to the `seq` it was
+  // launched with.  The host then keeps `seq` constant and bumps the counter with a stream-ordered
+  // add, so a recorded launch (CUDA graph) takes a fresh sequence number at every replay.
+  const int* seq_base;
 };
 constexpr int kEpErrCounts = 16, kEpErrOverflow = 17, kEpErrGemmWait = 18, kEpErrReturnWait = 19,
               kEpErrBufferBusy = 20;
@@ -163,8 +167,9 @@ cudaError_t ep_return_rows(DType type, const void* y, const int* counts, const i
                            const uint64_t* data_base, int64_t off_ret, int64_t off_flags, int seq, int cols,
                            int rows_bound, int ret_rows, int* done, const int* status, int sms,
                            cudaStream_t stream);
-cudaError_t ep_set_flag(int* flag, int value, cudaStream_t stream);
-cudaError_t ep_wait_flags(const int* flags, int count, int seq, int* status, int code, cudaStream_t stream);
+cudaError_t ep_set_flag(int* flag, int value, const int* seq_base, cudaStream_t stream);
+cudaError_t ep_wait_flags(const int* flags, int count, int seq, const int* seq_base, int* status, int code,
+                          cudaStream_t stream);
 
 // ---- dp_comm.cu ---------------------------------------------------------------
 // Geometry of the data-parallel gradient heap: `peer_base[r]` is where rank r's symmetric heap is
@@ -177,6 +182,7 @@ struct DpLayout {
   int64_t off_grad;
   int64_t off_ready;
   int64_t off_done;
+  const int* seq_base;   // nullable device counter added to `seq` (see EpLayout::seq_base)
 };
 constexpr int kDpErrReady = 32, kDpErrDone = 33;
 // All-reduce (or, with `scatter_only`, reduce-scatter into this rank's slice) of elements
@@ -255,6 +261,8 @@ struct GemmParams {
   int band_n;      // NT / NN: column tiles per band of the tile walk (0 = the kernel's default)
   CUtensorMap a2_map;
   CUtensorMap b2_map;
+  // Nullable device counter added to wait_seq and scatter_seq (see EpLayout::seq_base).
+  const int* seq_base;
   // TN only, nullable: one fp32 accumulator in device memory that receives the sum of squares of
   // everything the launch stores (the squared norm of a weight gradient, taken in the epilogue).
   float* sqnorm;

@@ -106,7 +106,10 @@ __global__ void inverse_map_kernel(const int* __restrict__ indices, const int* _
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int e = upper_bound_i32(bins, num_bins, i);
-  if (e >= num_bins) return;
+  if (e >= num_bins) {            // a position past the last bin: its copy belongs to no expert
+    inverse[__ldg(indices + i)] = -1;
+    return;
+  }
   const int off = i - (e ? __ldg(bins + e - 1) : 0);
   int row;
   if (capacity < 0) row = (e ? __ldg(padded_bins + e - 1) : 0) + off;

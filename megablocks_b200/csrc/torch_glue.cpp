@@ -86,11 +86,19 @@ void check_weights(const c10::optional<at::Tensor>& weights, const at::Tensor& x
 
 const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 
+// A device counter added to every sequence number of a launch (see EpLayout::seq_base); null when absent.
+const int* seq_base_ptr(const c10::optional<at::Tensor>& t) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->numel() >= 1, "seq_base must be a CUDA int32 tensor");
+  return t->data_ptr<int>();
+}
+
 at::Tensor build_inverse(const at::Tensor& indices, const at::Tensor& bins, const at::Tensor& padded_bins,
                          int capacity) {
   const int n = int(indices.numel());
-  // Copies absent from every bin (possible only for malformed input) stay -1.
-  at::Tensor inverse = at::full({n}, -1, indices.options());
+  // `indices` is a permutation of the copies, so the kernel writes every entry (-1 for a copy
+  // that no bin holds or that exceeds the capacity): no fill beforehand.
+  at::Tensor inverse = at::empty({n}, indices.options());
   if (n == 0) return inverse;
   MB_CUDA_OK(inverse_map(indices.data_ptr<int>(), bins.data_ptr<int>(), padded_bins.data_ptr<int>(),
                          int(bins.numel()), n, capacity, inverse.data_ptr<int>(), stream()));
@@ -145,9 +153,13 @@ std::vector<at::Tensor> route_plan(const at::Tensor& top_experts, int64_t num_ex
   const int64_t n = top_experts.numel();
   auto iopts = top_experts.options().dtype(at::kInt);
   at::Tensor indices = at::empty({n}, iopts), bin_ids = at::empty({n}, iopts);
-  at::Tensor bins = at::zeros({num_experts}, iopts), padded_bins = at::zeros({num_experts}, iopts);
-  at::Tensor tpe = at::zeros({num_experts}, iopts);
-  if (n == 0) return {indices, bin_ids, bins, padded_bins, tpe};
+  if (n == 0) {
+    at::Tensor zero = at::zeros({num_experts}, iopts);
+    return {indices, bin_ids, zero, zero.clone(), zero.clone()};
+  }
+  // The scan kernel of the sort writes all three per-expert arrays in full.
+  at::Tensor bins = at::empty({num_experts}, iopts), padded_bins = at::empty({num_experts}, iopts);
+  at::Tensor tpe = at::empty({num_experts}, iopts);
   // torch.topk yields int64 ids: narrow once, then a single counting-sort pass.
   at::Tensor e32 = top_experts.scalar_type() == at::kInt ? top_experts : top_experts.to(at::kInt);
   if (num_experts <= kMaxSortBins) {
@@ -495,7 +507,8 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
                                      const c10::optional<std::vector<at::Tensor>>& scatter,
                                      const std::vector<int64_t>& scatter_args, double alpha,
                                      const c10::optional<at::Tensor>& a2, const c10::optional<at::Tensor>& b2,
-                                     const c10::optional<at::Tensor>& sqnorm) {
+                                     const c10::optional<at::Tensor>& sqnorm,
+                                     const c10::optional<at::Tensor>& seq_base) {
   using namespace gemm;
   MB_CHECK_CUDA(a); MB_CHECK_CUDA(b); MB_CHECK_CUDA(bins);
   MB_CHECK_CONTIG(a); MB_CHECK_CONTIG(b); MB_CHECK_CONTIG(bins);
@@ -535,6 +548,7 @@ std::vector<at::Tensor> grouped_gemm(const at::Tensor& a, const at::Tensor& b, c
   p.epilogue = int(epilogue);
   p.act = int(act);
   p.alpha = float(alpha);
+  p.seq_base = seq_base_ptr(seq_base);
   if (sqnorm.has_value()) {
     TORCH_CHECK(layout == kTN && pair_mode != 1 && sqnorm->is_cuda() && sqnorm->scalar_type() == at::kFloat &&
                     sqnorm->numel() >= 1,
@@ -1090,7 +1104,8 @@ void symm_close(int64_t ptr) { C10_CUDA_CHECK(cudaIpcCloseMemHandle(reinterpret_
 namespace {
 
 EpLayout make_layout(const at::Tensor& peer_base, int64_t world, int64_t rank, int64_t num_experts,
-                     int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts, int64_t off_count_flags) {
+                     int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts, int64_t off_count_flags,
+                     const c10::optional<at::Tensor>& seq_base = c10::nullopt) {
   TORCH_CHECK(peer_base.is_cuda() && peer_base.scalar_type() == at::kLong && peer_base.numel() == world,
               "peer_base must be a CUDA int64 tensor with one address per rank");
   EpLayout L;
@@ -1102,6 +1117,7 @@ EpLayout make_layout(const at::Tensor& peer_base, int64_t world, int64_t rank, i
   L.capacity_rows = int(capacity_rows);
   L.off_counts = off_counts;
   L.off_count_flags = off_count_flags;
+  L.seq_base = seq_base_ptr(seq_base);
   return L;
 }
 
@@ -1112,7 +1128,8 @@ int* status_ptr(const at::Tensor& t) { return status_word(t.device()).data_ptr<i
 void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, int64_t world, int64_t rank,
                            int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows, int64_t off_counts,
                            int64_t off_count_flags, int64_t seq, int64_t expert_capacity, at::Tensor counts_out,
-                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch) {
+                           at::Tensor kept_out, at::Tensor recv_bins, at::Tensor scratch,
+                           const c10::optional<at::Tensor>& seq_base) {
   check_index(tpe, "tokens_per_expert");
   c10::cuda::CUDAGuard guard(tpe.device());
   TORCH_CHECK(tpe.numel() == num_experts && counts_out.numel() == world * num_experts &&
@@ -1121,7 +1138,7 @@ void ep_exchange_counts_op(const at::Tensor& tpe, const at::Tensor& peer_base, i
                   recv_bins.scalar_type() == at::kInt && scratch.scalar_type() == at::kInt && expert_capacity >= 0,
               "bad ep_exchange_counts arguments");
   const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
-                                 off_count_flags);
+                                 off_count_flags, seq_base);
   MB_CUDA_OK(ep_exchange_counts(tpe.data_ptr<int>(), L, int(seq), int(expert_capacity), counts_out.data_ptr<int>(),
                                 kept_out.data_ptr<int>(), recv_bins.data_ptr<int>(), scratch.data_ptr<int>(),
                                 int(scratch.numel()), status_ptr(tpe), stream()));
@@ -1133,7 +1150,7 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
                      int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                      int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_recv,
                      int64_t off_flags, int64_t off_free, int64_t seq, int64_t top_k, at::Tensor done,
-                     const c10::optional<at::Tensor>& dropped_rows) {
+                     const c10::optional<at::Tensor>& dropped_rows, const c10::optional<at::Tensor>& seq_base) {
   MB_CHECK_CUDA(x); MB_CHECK_CONTIG(x);
   void* dropped = nullptr;
   if (dropped_rows.has_value()) {
@@ -1147,7 +1164,7 @@ void ep_push_rows_op(const at::Tensor& x, const at::Tensor& indices, const c10::
   check_weights(weights, x, indices.numel());
   c10::cuda::CUDAGuard guard(x.device());
   const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
-                                 off_count_flags);
+                                 off_count_flags, seq_base);
   TORCH_CHECK(data_base.is_cuda() && data_base.scalar_type() == at::kLong && data_base.numel() == world,
               "data_base must be a CUDA int64 tensor with one address per rank");
   MB_CUDA_OK(ep_push_rows(float_code(x.scalar_type()), x.data_ptr(), indices.data_ptr<int>(), opt_ptr(weights),
@@ -1162,11 +1179,12 @@ void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::
                        const at::Tensor& peer_base, int64_t world,
                        int64_t rank, int64_t num_experts, int64_t experts_per_rank, int64_t capacity_rows,
                        int64_t off_counts, int64_t off_count_flags, const at::Tensor& data_base, int64_t off_ret,
-                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done) {
+                       int64_t off_flags, int64_t seq, int64_t ret_rows, at::Tensor done,
+                       const c10::optional<at::Tensor>& seq_base) {
   MB_CHECK_CUDA(y); MB_CHECK_CONTIG(y);
   c10::cuda::CUDAGuard guard(y.device());
   const EpLayout L = make_layout(peer_base, world, rank, num_experts, experts_per_rank, capacity_rows, off_counts,
-                                 off_count_flags);
+                                 off_count_flags, seq_base);
   TORCH_CHECK(data_base.is_cuda() && data_base.scalar_type() == at::kLong && data_base.numel() == world,
               "data_base must be a CUDA int64 tensor with one address per rank");
   TORCH_CHECK(raw_counts.is_cuda() && raw_counts.scalar_type() == at::kInt && raw_counts.numel() == counts.numel(),
@@ -1179,17 +1197,19 @@ void ep_return_rows_op(const at::Tensor& y, const at::Tensor& counts, const at::
   MB_LAUNCHED(1);
 }
 
-void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code) {
+void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64_t code,
+                      const c10::optional<at::Tensor>& seq_base) {
   TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= count, "bad flags tensor");
   c10::cuda::CUDAGuard guard(flags.device());
-  MB_CUDA_OK(ep_wait_flags(flags.data_ptr<int>(), int(count), int(seq), status_ptr(flags), int(code), stream()));
+  MB_CUDA_OK(ep_wait_flags(flags.data_ptr<int>(), int(count), int(seq), seq_base_ptr(seq_base), status_ptr(flags),
+                           int(code), stream()));
   MB_LAUNCHED(1);
 }
 
-void ep_set_flag_op(at::Tensor flag, int64_t value) {
+void ep_set_flag_op(at::Tensor flag, int64_t value, const c10::optional<at::Tensor>& seq_base) {
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && flag.numel() >= 1, "bad flag tensor");
   c10::cuda::CUDAGuard guard(flag.device());
-  MB_CUDA_OK(ep_set_flag(flag.data_ptr<int>(), int(value), stream()));
+  MB_CUDA_OK(ep_set_flag(flag.data_ptr<int>(), int(value), seq_base_ptr(seq_base), stream()));
   MB_LAUNCHED(1);
 }
 
@@ -1197,7 +1217,8 @@ void ep_set_flag_op(at::Tensor flag, int64_t value) {
 // the element type of the gradient buffer that lives at `off_grad` in the symmetric heap.
 void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_t world, int64_t rank,
                      int64_t off_grad, int64_t off_ready, int64_t off_done, int64_t start, int64_t count,
-                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas) {
+                     int64_t bucket, int64_t seq, double scale, bool scatter_only, at::Tensor ticket, int64_t ctas,
+                     const c10::optional<at::Tensor>& seq_base) {
   MB_CHECK_CUDA(like);
   TORCH_CHECK(peer_base.is_cuda() && peer_base.scalar_type() == at::kLong && peer_base.numel() == world,
               "peer_base must be a CUDA int64 tensor with one address per rank");
@@ -1210,6 +1231,7 @@ void dp_allreduce_op(const at::Tensor& like, const at::Tensor& peer_base, int64_
   L.off_grad = off_grad;
   L.off_ready = off_ready;
   L.off_done = off_done;
+  L.seq_base = seq_base_ptr(seq_base);
   MB_CUDA_OK(dp_allreduce(float_code(like.scalar_type()), L, start, count, int(bucket), int(seq), float(scale),
                           scatter_only, ticket.data_ptr<int>(), status_ptr(like), int(ctas), stream()));
   MB_LAUNCHED(1);

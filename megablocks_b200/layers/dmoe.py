@@ -128,7 +128,7 @@ class ParallelDroplessMLP(moe.ParallelMLP):
                                     expert_capactiy, top_k):
         x = x.reshape(-1, x.shape[-1])
         x = ops.gather(x, indices, bin_ids, bins, top_k)
-        x = self.mlp(x, tokens_per_expert)
+        x = self.mlp(x, tokens_per_expert, bins=bins)      # bins = prefix sum of tokens_per_expert
         return ops.scatter(x, indices, bin_ids, expert_weights, bins, top_k)
 
     # -- expert parallel over peer memory ----------------------------------------

@@ -54,9 +54,10 @@ class SparseGLU(SparseMLP):
 
 class GroupedGLU(SparseGLU):
 
-    def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor, bins=None) -> torch.Tensor:
         w1, v1, w2 = self._raw_glu_weights()
-        bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
+        if bins is None:
+            bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
         return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), bins, self.args.activation_fn,
                           self.args.memory_optimized_mlp, v1=self._grouped_view(v1), wgrad_scale=self.wgrad_scale())
 

@@ -203,10 +203,12 @@ class SparseMLP(_ExpertWeights):
 class GroupedMLP(SparseMLP):
     """dMoE experts on the unpadded expert-ordered layout."""
 
-    def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
-        """``tokens_per_expert`` is the per-expert row count (device tensor; no host copy is made)."""
+    def forward(self, x: torch.Tensor, tokens_per_expert: torch.Tensor, bins=None) -> torch.Tensor:
+        """``tokens_per_expert`` is the per-expert row count (device tensor; no host copy is made);
+        ``bins`` its inclusive prefix sum when the caller already has it."""
         w1, w2 = self._raw_weights()
-        bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
+        if bins is None:
+            bins = torch.cumsum(tokens_per_expert, 0, dtype=torch.int32)
         return expert_mlp(x, self._grouped_view(w1), self._grouped_view(w2), bins, self.args.activation_fn,
                           self.args.memory_optimized_mlp, wgrad_scale=self.wgrad_scale())
 

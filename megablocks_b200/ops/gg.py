@@ -256,7 +256,10 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
         num_groups = bins.numel()
     debug.check_groups(bins, a.shape[0])
     if a.is_cuda and ext().grouped_gemm_supported(a, b, bool(trans_a), bool(trans_b), int(num_groups)):
-        flags, count, stride, seq = wait if wait is not None else (None, 0, 0, 0)
+        flags, count, stride, seq = wait[:4] if wait is not None else (None, 0, 0, 0)
+        # Optional device counter that the kernel adds to the sequence numbers of `wait` / `scatter`.
+        seq_base = wait[4] if wait is not None and len(wait) > 4 else (
+            scatter[2] if scatter is not None and len(scatter) > 2 else None)
         pair_mode = _PAIR_MODE if pair is None else int(pair)
         sink, slot, slot_view = _GRAD_NORM_SINK, None, None
         if grad_norm and sink is not None and trans_a and pair_mode != 1:
@@ -265,7 +268,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, bins: torch.Tensor, *, trans_
                                   bool(want_out2), bool(want_out3), int(num_groups), c, bool(zero_tail), flags,
                                   int(count), int(stride), int(seq), int(rows_hint), pair_mode,
                                   scatter[0] if scatter is not None else None,
-                                  scatter[1] if scatter is not None else [], float(alpha), a2, b2, slot_view)
+                                  scatter[1] if scatter is not None else [], float(alpha), a2, b2, slot_view,
+                                  seq_base)
         if slot is not None:
             sink._record(outs[0], slot)
         return outs

@@ -137,6 +137,9 @@ class GradReducer:
         flat.grad = new_grad
         flat.zero_grad()                       # re-attaches every p.grad view to the new storage
         self._tickets = torch.zeros(len(self.buckets), dtype=torch.int32, device=flat.grad.device)
+        # Added by the kernel to the step number it is launched with; the trainer's CUDA-graph step
+        # (whose recorded launches carry a frozen `seq`) adds one to it at the end of every replay.
+        self.seq_dev = torch.zeros(1, dtype=torch.int32, device=flat.grad.device)
         torch.cuda.synchronize(flat.grad.device)
         dist.barrier(self.group)               # nobody launches before every heap is zeroed
 
@@ -145,7 +148,7 @@ class GradReducer:
         s, e = self.buckets[bi][:2]
         ext().dp_allreduce(self.flat.grad, self._heap.peer_base, self.world, self.rank, self._off_grad,
                            self._off_ready, self._off_done, s, e - s, bi, self.seq, 1.0 / self.world, self.shard,
-                           self._tickets[bi:bi + 1], self.ctas)
+                           self._tickets[bi:bi + 1], self.ctas, self.seq_dev)
 
     # -- shard geometry (ZeRO-1) --------------------------------------------------
     def shard_range(self, bucket: int):

@@ -29,6 +29,7 @@ that :func:`megablocks_b200.utils.status.check` turns into an exception.
 from typing import Any, Dict, Optional, Tuple
 
 import os
+import weakref
 
 import torch
 import torch.distributed as dist
@@ -77,6 +78,14 @@ class SymmetricHeap:
         for ptr in self._opened:
             ext().symm_close(ptr)
         self._opened = []
+
+
+_LIVE_WORKSPACES = weakref.WeakSet()
+
+
+def live_workspaces():
+    """Every workspace of this process (the trainer's CUDA-graph step advances their device counters)."""
+    return list(_LIVE_WORKSPACES)
 
 
 class EpWorkspace:
@@ -128,6 +137,12 @@ class EpWorkspace:
         self.ret_dx = self.bwd_heap.view(self.off_ret_dx, (copies, hidden), dtype)
         self.seq = 0
         self.released_seq = 0
+        # Added by every kernel to the sequence number it is launched with.  Zero as long as the
+        # host counts the uses; when the training step is replayed from a CUDA graph (where `seq` is
+        # frozen into the recorded launches) the graph adds this workspace's uses per step to it at
+        # the end of every replay.
+        self.seq_dev = torch.zeros(1, dtype=torch.int32, device=device)
+        _LIVE_WORKSPACES.add(self)
 
     # -- geometry passed to the kernels -------------------------------------------------
     def _layout(self):
@@ -155,7 +170,8 @@ class EpWorkspace:
         kept = torch.empty(W * E, dtype=torch.int32, device=self.device)
         recv_bins = torch.empty(self.epr, dtype=torch.int32, device=self.device)
         scratch = torch.empty(2 * E + 2 * W, dtype=torch.int32, device=self.device)
-        ext().ep_exchange_counts(tpe, *self._layout(), seq, int(expert_capacity), routed, kept, recv_bins, scratch)
+        ext().ep_exchange_counts(tpe, *self._layout(), seq, int(expert_capacity), routed, kept, recv_bins, scratch,
+                                 self.seq_dev)
         done = (scratch[:E], scratch[2 * E:2 * E + W], scratch[E:2 * E], scratch[2 * E + W:])
         return (kept, routed), recv_bins, done
 
@@ -170,43 +186,46 @@ class EpWorkspace:
         if direction == 0:
             ext().ep_push_rows(x, indices, weights, bins, kept, *self._layout(), self.heap.peer_base,
                                self.off_recv_x, self.off_disp_flags[0], self.off_free, seq, top_k, done,
-                               self.ret_y if drops else None)
+                               self.ret_y if drops else None, self.seq_dev)
         else:
             ext().ep_push_rows(x, indices, weights, bins, kept, *self._layout(), self.bwd_heap.peer_base,
                                self.off_recv_dy, self.off_disp_flags[1], -1, seq, top_k, done,
-                               self.ret_dx if drops else None)
+                               self.ret_dx if drops else None, self.seq_dev)
 
     def return_rows(self, y, counts, direction: int, seq: int, done):
         """Store my expert-ordered rows ``y`` back into the sources' sorted order."""
         if direction == 0:
             ext().ep_return_rows(y, counts[0], counts[1], *self._layout(), self.heap.peer_base, self.off_ret_y,
-                                 self.off_ret_flags[0], seq, self.copies, done)
+                                 self.off_ret_flags[0], seq, self.copies, done, self.seq_dev)
         else:
             ext().ep_return_rows(y, counts[0], counts[1], *self._layout(), self.bwd_heap.peer_base, self.off_ret_dx,
-                                 self.off_ret_flags[1], seq, self.copies, done)
+                                 self.off_ret_flags[1], seq, self.copies, done, self.seq_dev)
 
     def scatter_args(self, counts, direction: int, seq: int, done):
         """``scatter`` argument of the grouped GEMM: return the output rows to their sources from the epilogue."""
         heap = self.heap if direction == 0 else self.bwd_heap
         off = self.off_ret_y if direction == 0 else self.off_ret_dx
         return ([heap.peer_base, self.heap.peer_base, counts[0], done, counts[1]],
-                [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq, self.copies])
+                [off, self.off_ret_flags[direction], self.world, self.rank, self.num_experts, seq, self.copies],
+                self.seq_dev)
 
     def fuse_combine(self) -> bool:
         """Whether the kernel's segment tables can hold this workspace's (expert, rank) pairs."""
         return self.epr * self.world <= 512 and os.environ.get('MB200_EP_FUSED_COMBINE', '1') != '0'
 
     def wait_return(self, direction: int, seq: int) -> None:
-        ext().ep_wait_flags(self.flags(self.off_ret_flags[direction], self.world), self.world, seq, ERR_RETURN_WAIT)
+        ext().ep_wait_flags(self.flags(self.off_ret_flags[direction], self.world), self.world, seq, ERR_RETURN_WAIT,
+                            self.seq_dev)
 
     def arrival(self, direction: int, seq: int):
         """``wait`` argument of the grouped GEMM: per-expert arrival flags of the receive buffer."""
-        return (self.flags(self.off_disp_flags[direction], self.world * self.epr), self.world, self.epr, seq)
+        return (self.flags(self.off_disp_flags[direction], self.world * self.epr), self.world, self.epr, seq,
+                self.seq_dev)
 
     def release_receive_buffer(self, seq: int) -> None:
         """Publish that every read of the forward receive buffer of use ``seq`` has been issued."""
         if seq > self.released_seq:
-            ext().ep_set_flag(self.flags(self.off_free, 1), seq)
+            ext().ep_set_flag(self.flags(self.off_free, 1), seq, self.seq_dev)
             self.released_seq = seq
 
     def close(self) -> None:

@@ -267,7 +267,12 @@ class Trainer:
 
     # -- whole-step CUDA graph ---------------------------------------------------------
     def _graph_eligible(self) -> bool:
-        return (self.cfg.cuda_graph and self.device.type == 'cuda' and self.world == 1 and self.pipeline is None
+        # Several ranks: the kernels of the fused expert-parallel exchange and of the peer-memory
+        # gradient reducer take their sequence numbers from device counters that the recorded step
+        # advances itself; NCCL-backed reducers and ZeRO-1 keep host-side state per step.
+        multi_ok = self.world == 1 or (self.reducer is not None and self.reducer.backend == 'peer'
+                                       and not self.cfg.zero1)
+        return (self.cfg.cuda_graph and self.device.type == 'cuda' and multi_ok and self.pipeline is None
                 and self.scaler is None and self._update_stream is None
                 and isinstance(self.dense_opt, FusedAdam) and isinstance(self.expert_opt, FusedAdam)
                 and self.step_count <= max(int(self.cfg.total_steps), 1))     # rows of the schedule table
@@ -297,14 +302,37 @@ class Trainer:
         graph = torch.cuda.CUDAGraph()
         before = ext().launch_count()
         counters = (self.step_count, self.dense_opt.step_count, self.expert_opt.step_count)
+        # Sequence numbers of the peer-memory exchanges: the recorded launches keep the numbers the
+        # host hands out now, and the step ends by adding "uses per step" to each user's device
+        # counter, which every kernel adds to its number: replay r runs with the numbers the r-th
+        # step after this one would have had.
+        from megablocks_b200.parallel.ep import live_workspaces
+        users = [u for u in live_workspaces() + [self.reducer] if u is not None and hasattr(u, 'seq_dev')]
+        marks = [(u, u.seq, getattr(u, 'released_seq', None)) for u in users]
         try:
-            with torch.cuda.graph(graph):
+            # Other threads (a process group's watchdog polling its events) must stay free to make
+            # CUDA calls that are not part of the recording.
+            mode = dict(capture_error_mode='thread_local') if self.world > 1 else {}
+            with torch.cuda.graph(graph, **mode):
                 torch.index_select(self._table, 0, self._graph_step, out=self._hyper.view(1, 3))
                 self._graph_step.add_(1)
+                if self.flat is not None:
+                    self.flat.zero_grad()
                 loss = self._step_eager(static_tokens, static_targets, zero_grad=False)
+                for user, seq, _ in marks:
+                    if user.seq != seq:
+                        user.seq_dev.add_(user.seq - seq)
         finally:
             # Recording advanced the host-side counters without running anything: take that back.
+            # (Also the sequence numbers: replay r runs with "recorded number + r - 1", so a step
+            # launched kernel by kernel after R replays must get "recorded number + R", which is
+            # what the host's next number plus the device counter gives once the host is back at
+            # its value from before the recording.)
             self.step_count, self.dense_opt.step_count, self.expert_opt.step_count = counters
+            for user, seq, released in marks:
+                user.seq = seq
+                if released is not None:
+                    user.released_seq = released
         launches = ext().launch_count() - before
         self._graph = (graph, static_tokens, static_targets, loss, launches)
 

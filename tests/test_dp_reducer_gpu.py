@@ -122,3 +122,62 @@ def test_trainer_with_peer_reducer_matches_nccl(tmp_path):
     for r in range(1, world):
         assert torch.equal(res[0]['peer'], res[r]['peer'])       # replicas stay bitwise in sync
     torch.testing.assert_close(res[0]['peer'], res[0]['nccl'], rtol=2e-2, atol=2e-3)
+
+
+def _graph_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    from megablocks_b200.models.transformer import MoETransformer, preset
+    from megablocks_b200.train import Trainer, TrainerConfig
+    from megablocks_b200.utils import status
+    try:
+        result = {}
+        for graph in (False, True):
+            torch.manual_seed(0)
+            cfg = preset('tiny', device=dev, expert_parallel_group=dist.group.WORLD, moe_num_experts=8)
+            trainer = Trainer(MoETransformer(cfg), TrainerConfig(lr=1e-3, min_lr=1e-4, total_steps=8, warmup_fraction=0.25,
+                                                                 bucket_mb=1, dp_backend='peer', cuda_graph=graph,
+                                                                 graph_warmup_steps=2),
+                              dp_group=dist.group.WORLD)
+            gen = torch.Generator().manual_seed(10 + rank)
+            losses = []
+            for _ in range(7):
+                batch = torch.randint(0, cfg.vocab_size, (4, cfg.max_seq_len + 1), generator=gen).to(dev)
+                losses.append(trainer.step(batch[:, :-1], batch[:, 1:]))
+            torch.cuda.synchronize()
+            status.check()
+            recorded = trainer._graph is not None
+            # Back to plain launches after the replays: the sequence numbers must still line up.
+            trainer.drop_graph()
+            trainer.cfg.cuda_graph = False
+            batch = torch.randint(0, cfg.vocab_size, (4, cfg.max_seq_len + 1), generator=gen).to(dev)
+            losses.append(trainer.step(batch[:, :-1], batch[:, 1:]))
+            torch.cuda.synchronize()
+            status.check()
+            result[graph] = {'losses': [float(l) for l in losses], 'recorded': recorded,
+                             'dense': torch.cat([p.detach().float().reshape(-1) for p in trainer.dense_params]).cpu(),
+                             'expert': torch.cat([p.detach().float().reshape(-1) for p in trainer.expert_params]).cpu()}
+        torch.save(result, os.path.join(out_dir, f'g{rank}.pt'))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_multi_rank_step_replayed_from_a_cuda_graph(tmp_path):
+    """Expert parallelism over peer memory + the peer-memory gradient reducer, recorded once and replayed:
+    the same losses and weights as the step launched kernel by kernel, on every rank."""
+    world = _world()
+    if world < 2:
+        pytest.skip('needs at least two GPUs')
+    mp.spawn(_graph_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(os.path.join(tmp_path, f'g{r}.pt')) for r in range(world)]
+    for r in range(world):
+        assert res[r][True]['recorded'] and not res[r][False]['recorded']
+        torch.testing.assert_close(torch.tensor(res[r][True]['losses']), torch.tensor(res[r][False]['losses']),
+                                   rtol=2e-4, atol=2e-4)
+        for part in ('dense', 'expert'):
+            diff = (res[r][True][part] - res[r][False][part]).abs()
+            assert float(diff.median()) <= 1e-4 and float(diff.max()) <= 2 * 8 * 1e-3 + 1e-6, (r, part)
+        assert torch.equal(res[0][True]['dense'], res[r][True]['dense'])        # replicas stay bitwise in sync

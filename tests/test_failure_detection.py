@@ -86,7 +86,7 @@ def test_device_wait_runs_into_its_bound_and_reports():
     status.read(clear=True)
     flags = torch.zeros(8, dtype=torch.int32, device=dev)      # nobody will ever set these
     t0 = time.monotonic()
-    ext().ep_wait_flags(flags, 2, 5, 19)
+    ext().ep_wait_flags(flags, 2, 5, 19, None)
     torch.cuda.synchronize()
     assert 1.0 < time.monotonic() - t0 < 20.0
     with pytest.raises(status.DeviceWaitTimeout, match='never returned'):
@@ -133,7 +133,7 @@ def test_expert_parallel_exchange_fails_closed():
     recv_bins = torch.full((epr,), 999999, dtype=torch.int32, device=dev)
     scratch = torch.empty(2 * experts + 2 * world, dtype=torch.int32, device=dev)
     t0 = time.monotonic()
-    ext().ep_exchange_counts(tpe, *layout, 1, 0, counts, kept, recv_bins, scratch)
+    ext().ep_exchange_counts(tpe, *layout, 1, 0, counts, kept, recv_bins, scratch, None)
     torch.cuda.synchronize()
     assert 1.0 < time.monotonic() - t0 < 20.0
     assert status.read(clear=False) == 16                       # the peer never published its counts
@@ -145,8 +145,9 @@ def test_expert_parallel_exchange_fails_closed():
     bins = torch.tensor([64, 128, 192, 256], dtype=torch.int32, device=dev)
     done = torch.zeros(experts, dtype=torch.int32, device=dev)
     before = [h.clone() for h in heaps]
-    ext().ep_push_rows(x, indices, None, bins, kept, *layout, peer_base, off_recv, off_flags, -1, 1, 1, done, None)
-    ext().ep_return_rows(x, kept, counts, *layout, peer_base, off_ret, off_flags, 1, copies, done)
+    ext().ep_push_rows(x, indices, None, bins, kept, *layout, peer_base, off_recv, off_flags, -1, 1, 1, done, None,
+                       None)
+    ext().ep_return_rows(x, kept, counts, *layout, peer_base, off_ret, off_flags, 1, copies, done, None)
     flags = torch.zeros(8, dtype=torch.int32, device=dev)
     w = torch.randn(epr, 128, hidden, device=dev, dtype=torch.bfloat16)
     out = torch.full((copies, 128), 7.0, device=dev, dtype=torch.bfloat16)
