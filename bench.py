@@ -236,9 +236,11 @@ def run_ours(args):
     cfg = preset('dmoe-125m', device=torch.device('cuda', local), expert_parallel_group=group,
                  mlp_impl=args.mlp_impl, memory_optimized_mlp=args.memory_optimized_mlp, ep_fused_comm=fused)
     model = MoETransformer(cfg)
-    # One process: the whole step is recorded in a CUDA graph during the warm-up steps (two plain
-    # steps, then the recording) and the timed steps replay it.
-    use_graph = args.cuda_graph == 'on' or (args.cuda_graph == 'auto' and world == 1 and args.warmup >= 3)
+    # The whole step is recorded in a CUDA graph during the warm-up steps (two plain steps, then
+    # the recording) and the timed steps replay it.  On several ranks the peer-memory kernels of
+    # the exchange and of the gradient reduction take their sequence numbers from device counters,
+    # and no library collective is left in the step.
+    use_graph = args.cuda_graph == 'on' or (args.cuda_graph == 'auto' and args.warmup >= 3)
     trainer = Trainer(model, TrainerConfig(lr=6e-4, total_steps=20000, cuda_graph=use_graph, graph_warmup_steps=2),
                       dp_group=group)
     from megablocks_b200.utils.metrics import comm_timer
@@ -300,7 +302,7 @@ def main():
     ap.add_argument('--ep-comm', dest='ep_comm', choices=['auto', 'fused', 'nccl'], default='auto',
                     help='expert-parallel exchange: peer-memory kernels (auto/fused) or NCCL all-to-all')
     ap.add_argument('--cuda-graph', dest='cuda_graph', choices=['auto', 'on', 'off'], default='auto',
-                    help='replay the training step from one CUDA graph (auto: on for a single process)')
+                    help='replay the training step from one CUDA graph (auto: on when there are at least 3 warm-up steps)')
     ap.add_argument('--ref-gmm', dest='ref_gmm', choices=['loop', 'grouped_mm'], default='loop',
                     help="reference arm only: its grouped_gemm dependency as the package's default per-expert "
                          'cuBLAS loop, or as one torch._grouped_mm launch per GEMM (the analogue of the '

@@ -38,6 +38,39 @@ def _align(n: int, to: int) -> int:
     return (n + to - 1) // to * to
 
 
+class PeerScalarSum:
+    """Sum of one fp32 value over the group by the peer-memory reducer kernel (no NCCL call).
+
+    Used for the squared gradient norm: rank 0 of the group adds the ranks' values in rank order and
+    stores the sum into every rank's buffer, so all ranks clip with bitwise the same coefficient.
+    The kernel's closing handshake guarantees that no peer still reads this rank's buffer when the
+    call returns on the stream, so the next call may overwrite it.
+    """
+
+    def __init__(self, group: dist.ProcessGroup, device):
+        from megablocks_b200.parallel.ep import SymmetricHeap
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        flag_bytes = _align(self.world * 4, 256)
+        self._off_ready, self._off_done = 256, 256 + flag_bytes
+        self._heap = SymmetricHeap(group, 256 + 2 * flag_bytes, device)
+        self._heap.local.zero_()
+        self.buf = self._heap.view(0, (4,), torch.float32)
+        self._ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq = 0
+        self.seq_dev = torch.zeros(1, dtype=torch.int32, device=device)   # see GradReducer.seq_dev
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def __call__(self, value: torch.Tensor) -> None:
+        """``value`` (one fp32 element on this device) becomes the sum over the group, in place."""
+        from megablocks_b200._ext import ext
+        self.buf[:1].copy_(value.reshape(1))
+        self.seq += 1
+        ext().dp_allreduce(self.buf, self._heap.peer_base, self.world, self.rank, 0, self._off_ready, self._off_done,
+                           0, 4, 0, self.seq, 1.0, False, self._ticket, 1, self.seq_dev)
+        value.reshape(1).copy_(self.buf[:1])
+
+
 class FlatBuffer:
     """Contiguous parameter and gradient storage for a list of same-dtype parameters."""
 

@@ -114,6 +114,12 @@ class Trainer:
             self.flat = FlatBuffer(self.dense_params, granule=self.world * 8)
             self.reducer = GradReducer(self.flat, dp_group, cfg.bucket_mb << 20, shard=cfg.zero1,
                                        backend=cfg.dp_backend)
+        # The squared gradient norm is summed over the group by the same peer-memory kernel when the
+        # gradients are (one launch, no library collective in the step).
+        self._scalar_sum = None
+        if self.reducer is not None and self.reducer.backend == 'peer':
+            from megablocks_b200.parallel.dp import PeerScalarSum
+            self._scalar_sum = PeerScalarSum(dp_group, self.device)
         if self.world > 1 and cfg.zero1:
             # One optimizer "tensor" per owned bucket slice; disjoint across ranks.
             self._shard_params, self._shard_grads = [], []
@@ -307,7 +313,8 @@ class Trainer:
         # counter, which every kernel adds to its number: replay r runs with the numbers the r-th
         # step after this one would have had.
         from megablocks_b200.parallel.ep import live_workspaces
-        users = [u for u in live_workspaces() + [self.reducer] if u is not None and hasattr(u, 'seq_dev')]
+        users = [u for u in live_workspaces() + [self.reducer, self._scalar_sum]
+                 if u is not None and hasattr(u, 'seq_dev')]
         marks = [(u, u.seq, getattr(u, 'released_seq', None)) for u in users]
         try:
             # Other threads (a process group's watchdog polling its events) must stay free to make
@@ -439,7 +446,10 @@ class Trainer:
             else:
                 self.expert_opt.add_sqnorm(self._sqnorm)
             if self.world > 1:
-                dist.all_reduce(self._sqnorm, group=self.dp_group)
+                if self._scalar_sum is not None:
+                    self._scalar_sum(self._sqnorm)
+                else:
+                    dist.all_reduce(self._sqnorm, group=self.dp_group)
             if self.pipeline is not None and self.pipeline.world > 1:
                 dist.all_reduce(self._sqnorm, group=self.pipeline.group)
         extra = 1.0
