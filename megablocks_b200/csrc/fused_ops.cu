@@ -4,6 +4,8 @@
 // shared memory and one small second pass).  The reference has no model code; these
 // serve this library's own training model (models/transformer.py), where the eager
 // PyTorch versions cost more HBM traffic than the whole MoE stack.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace mb {
@@ -317,6 +319,137 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) out[c] = acc[c];
 }
 
+// Backward with a row split over several warps: every thread owns ONE 16-byte pack of a row (its
+// columns are fixed for the whole kernel, so the weight / bias gradients still accumulate in
+// registers), `tpr` threads (a multiple of 32) cover a row and a CTA works on `rpc` rows at a time.
+// About 40 registers per thread instead of 128: four to five times as many rows in flight per SM as
+// the one-row-per-warp kernel, whose rate was set by the latency of that loop, not by HBM.  The two
+// row statistics cross the row's warps through shared memory (one CTA barrier per iteration,
+// buffers alternating so that a fast warp never overwrites what a slow one still reads).
+constexpr int kLnSplitThreads = 384;
+
+// Element pair `j` of a 16-byte pack as two fp32 values, and back.  The arithmetic of the kernel
+// below runs on such pairs (f32x2 instructions: two elements per issue slot), which is what
+// keeps it bound by memory instead of by instruction issue.
+template <typename T, int VEC>
+__device__ __forceinline__ float2 pack_pair(const Pack<T, VEC>& p, int j) {
+  if constexpr (std::is_same<T, float>::value) {
+    return make_float2(p.v[2 * j], p.v[2 * j + 1]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(&p)[j];
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    return __half22float2(reinterpret_cast<const __half2*>(&p)[j]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void set_pack_pair(Pack<T, VEC>& p, int j, float2 v) {
+  if constexpr (std::is_same<T, float>::value) {
+    p.v[2 * j] = v.x;
+    p.v[2 * j + 1] = v.y;
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    reinterpret_cast<__nv_bfloat162*>(&p)[j] = __floats2bfloat162_rn(v.x, v.y);
+  } else {
+    reinterpret_cast<__half2*>(&p)[j] = __floats2half2_rn(v.x, v.y);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLnSplitThreads, 3)
+layernorm_bwd_split_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                           const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int cols,
+                           T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dres, int rms,
+                           int tpr, int rpc) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int PAIRS = VEC / 2;
+  constexpr int kWarps = kLnSplitThreads / 32;
+  extern __shared__ float acc[];          // [2][cols] gradient sums, then [2][kWarps][2] row statistics
+  float* red = acc + 2 * cols;
+  for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) acc[i] = 0.f;
+  const int slot = threadIdx.x / tpr;
+  const int c = (threadIdx.x - slot * tpr) * VEC;
+  const bool col_ok = slot < rpc && c < cols;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpr = tpr >> 5;
+  Pack<T, VEC> pg;
+  float2 dg_acc[PAIRS], db_acc[PAIRS];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) pg.v[k] = from_float<T>(0.f);
+#pragma unroll
+  for (int j = 0; j < PAIRS; ++j) {
+    dg_acc[j] = make_float2(0.f, 0.f);
+    db_acc[j] = make_float2(0.f, 0.f);
+  }
+  if (col_ok) pg = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+  __syncthreads();
+  const float inv_cols = 1.f / cols;
+  int parity = 0;
+  for (int64_t r0 = int64_t(blockIdx.x) * rpc; r0 < rows; r0 += int64_t(gridDim.x) * rpc, parity ^= 1) {
+    const int64_t r = r0 + slot;
+    const bool ok = col_ok && r < rows;
+    Pack<T, VEC> px, pd;
+    float rs = 0.f, nmurs = 0.f;          // xhat = x * rs + nmurs
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+    if (ok) {
+      px = *reinterpret_cast<const Pack<T, VEC>*>(x + r * cols + c);
+      pd = *reinterpret_cast<const Pack<T, VEC>*>(dy + r * cols + c);
+      // Needed only after the barrier: ask for the line now, load it there (four registers less).
+      if (dres != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(dres + r * cols + c));
+      rs = rstd[r];
+      nmurs = -mean[r] * rs;
+      const float2 rs2 = make_float2(rs, rs), nm2 = make_float2(nmurs, nmurs);
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        const float2 xh = __ffma2_rn(pack_pair(px, j), rs2, nm2);
+        const float2 d = pack_pair(pd, j);
+        const float2 dg = __fmul2_rn(d, pack_pair(pg, j));
+        s1 = __ffma2_rn(dg, xh, s1);
+        s2 = __fadd2_rn(s2, dg);
+        dg_acc[j] = __ffma2_rn(d, xh, dg_acc[j]);
+        db_acc[j] = __fadd2_rn(db_acc[j], d);
+      }
+    }
+    const float w1 = warp_sum(s1.x + s1.y);
+    const float w2 = warp_sum(s2.x + s2.y);
+    float* mine = red + (parity * kWarps + warp) * 2;
+    if (lane == 0) { mine[0] = w1; mine[1] = w2; }
+    __syncthreads();
+    if (ok) {
+      const float* row_red = red + (parity * kWarps + slot * wpr) * 2;
+      float t1 = 0.f, t2 = 0.f;
+      for (int w = 0; w < wpr; ++w) { t1 += row_red[2 * w]; t2 += row_red[2 * w + 1]; }
+      t1 *= inv_cols;
+      t2 = rms ? 0.f : t2 * inv_cols;
+      // dx = rs * (dg - t2 - xhat * t1) [+ dres]
+      const float2 rs2 = make_float2(rs, rs), nm2 = make_float2(nmurs, nmurs);
+      const float2 nt1 = make_float2(-t1, -t1), nt2 = make_float2(-t2, -t2);
+      Pack<T, VEC> po, pr;
+      if (dres != nullptr) pr = *reinterpret_cast<const Pack<T, VEC>*>(dres + r * cols + c);
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        const float2 xh = __ffma2_rn(pack_pair(px, j), rs2, nm2);
+        const float2 dg = __ffma2_rn(pack_pair(pd, j), pack_pair(pg, j), nt2);     // dg - t2
+        float2 out = __fmul2_rn(__ffma2_rn(xh, nt1, dg), rs2);
+        if (dres != nullptr) out = __fadd2_rn(out, pack_pair(pr, j));
+        set_pack_pair(po, j, out);
+      }
+      *reinterpret_cast<Pack<T, VEC>*>(dx + r * cols + c) = po;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      atomicAdd(&acc[c + 2 * j], dg_acc[j].x);
+      atomicAdd(&acc[c + 2 * j + 1], dg_acc[j].y);
+      atomicAdd(&acc[cols + c + 2 * j], db_acc[j].x);
+      atomicAdd(&acc[cols + c + 2 * j + 1], db_acc[j].y);
+    }
+  }
+  __syncthreads();
+  float* out = partial + int64_t(blockIdx.x) * 2 * cols;
+  for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) out[i] = acc[i];
+}
+
 // Forward for rows of at most 32 * MAXV * VEC elements: the row is read once and stays in
 // registers between the statistics and the normalisation; weight and bias are loaded once per warp.
 template <typename T, int MAXV>
@@ -425,8 +558,19 @@ layernorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials,
   const int col_lane = threadIdx.x & 31, part_lane = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + col_lane;
   float s = 0.f;
-  if (c < 2 * cols)
-    for (int p = part_lane; p < num_partials; p += 8) s += partial[int64_t(p) * 2 * cols + c];
+  if (c < 2 * cols) {
+    // Four independent loads in flight per thread: the loop is a chain of dependent latencies otherwise.
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int p = part_lane;
+    for (; p + 24 < num_partials; p += 32) {
+      s += partial[int64_t(p) * 2 * cols + c];
+      s1 += partial[int64_t(p + 8) * 2 * cols + c];
+      s2 += partial[int64_t(p + 16) * 2 * cols + c];
+      s3 += partial[int64_t(p + 24) * 2 * cols + c];
+    }
+    for (; p < num_partials; p += 8) s += partial[int64_t(p) * 2 * cols + c];
+    s += s1 + s2 + s3;
+  }
   red[part_lane][col_lane] = s;
   __syncthreads();
   if (part_lane == 0 && c < 2 * cols) {
@@ -559,7 +703,8 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
   return cudaGetLastError();
 }
 
-int layernorm_grid(int64_t rows, int sms) { return max(1, min(ceil_div(rows, kLnWarps), sms * 2)); }
+// Upper bound of the CTAs any backward path launches (= rows of `partial` the caller allocates).
+int layernorm_grid(int64_t rows, int sms) { return max(1, min(ceil_div(rows, 1), sms * 6)); }
 
 bool layernorm_fusable(DType type, int cols) {
   const int vec = type == kF32 ? 4 : 8;
@@ -584,12 +729,23 @@ cudaError_t layernorm_bwd(DType type, const void* dy, const void* x, const void*
                           const float* rstd, int64_t rows, int cols, void* dx, void* dgamma, void* dbeta,
                           float* partial, const void* dres, bool rms, int sms, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
-  const int grid = layernorm_grid(rows, sms);
+  int grid = max(1, min(ceil_div(rows, kLnWarps), sms * 2));
   const size_t smem = size_t(2) * cols * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   MB_SWITCH_FLOAT(type, T, {
-    if (cols % (16 / sizeof(T)) != 0) return cudaErrorInvalidValue;
-    if (!launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
+    constexpr int kVec = 16 / sizeof(T);
+    if (cols % kVec != 0) return cudaErrorInvalidValue;
+    // Rows that a few warps cover with one pack per thread take the split kernel.
+    const int tpr = ceil_div(cols / kVec, 32) * 32;
+    static const bool split_off = std::getenv("MB200_LN_SPLIT") != nullptr && std::getenv("MB200_LN_SPLIT")[0] == '0';
+    if (tpr <= kLnSplitThreads && !split_off) {
+      const int rpc = kLnSplitThreads / tpr;
+      grid = max(1, min(ceil_div(rows, rpc), sms * 3));   // three CTAs per SM are resident: one wave
+      const size_t smem2 = smem + size_t(2) * (kLnSplitThreads / 32) * 2 * sizeof(float);
+      layernorm_bwd_split_kernel<T><<<grid, kLnSplitThreads, smem2, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd, rows, cols,
+          static_cast<T*>(dx), partial, static_cast<const T*>(dres), rms ? 1 : 0, tpr, rpc);
+    } else if (!launch_layernorm_bwd<T>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
                                  mean, rstd, rows, cols, static_cast<T*>(dx), partial, static_cast<const T*>(dres),
                                  rms ? 1 : 0, grid, smem, stream))
       return cudaErrorInvalidValue;
