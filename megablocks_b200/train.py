@@ -350,6 +350,9 @@ class Trainer:
         static_targets.copy_(targets, non_blocking=True)
         graph.replay()
         ext().count_launches(launches)
+        cfg = self.cfg        # the kernels read the rate from the device table; keep the host's copy for logs
+        self.dense_opt.lr = self.expert_opt.lr = cosine_lr(
+            self.step_count, cfg.total_steps, cfg.lr, cfg.min_lr, cfg.warmup_fraction) if cfg.schedule else cfg.lr
         self.step_count += 1
         self.dense_opt.step_count += 1
         self.expert_opt.step_count += 1
