@@ -143,9 +143,20 @@ def _graph_worker(rank, world, port, out_dir):
                               dp_group=dist.group.WORLD)
             gen = torch.Generator().manual_seed(10 + rank)
             losses = []
-            for _ in range(7):
+            norm_ok = True
+            for it in range(7):
                 batch = torch.randint(0, cfg.vocab_size, (4, cfg.max_seq_len + 1), generator=gen).to(dev)
                 losses.append(trainer.step(batch[:, :-1], batch[:, 1:]))
+                if it in (0, 5):
+                    # The clipping norm (taken in the GEMM epilogues for the expert weights, summed over
+                    # the ranks by the peer-memory kernel) against a plain sum over the gradients:
+                    # replicated tensors count once, expert shards once per rank.
+                    local = sum(p.grad.float().square().sum() for p in trainer.dense_params) / world + \
+                        sum(p.grad.float().square().sum() for p in trainer.expert_params)
+                    dist.all_reduce(local)
+                    want = float(local.sqrt())
+                    norm_ok &= abs(float(trainer.last_grad_norm) - want) <= 3e-3 * want
+            assert norm_ok
             torch.cuda.synchronize()
             status.check()
             recorded = trainer._graph is not None

@@ -104,3 +104,24 @@ def test_graph_is_recorded_again_after_a_checkpoint_is_loaded():
     assert trainer._graph is None and trainer.step_count == 4
     got = float(trainer.step(batch[:, :-1], batch[:, 1:]))              # step 5 again, kernel by kernel
     assert abs(got - want) < 1e-3
+
+
+@pytest.mark.gpu
+def test_gradient_norm_taken_in_the_gemm_epilogues_matches_the_norm_kernel():
+    """Adam hides a wrong clip coefficient (its update is scale free), so the norm itself is compared:
+    the sum the weight-gradient GEMMs report, the norm kernel's, and a plain fp32 sum over ``.grad``."""
+    dev = torch.device('cuda', 0)
+    norms, fused_tensors = {}, {}
+    for fuse in (True, False):
+        torch.manual_seed(3)
+        cfg = preset('tiny', device=dev)
+        model = MoETransformer(cfg)
+        trainer = Trainer(model, TrainerConfig(lr=1e-3, total_steps=100, fuse_grad_norm=fuse, max_grad_norm=1e9))
+        batch = torch.randint(0, cfg.vocab_size, (4, 65), generator=torch.Generator().manual_seed(4)).to(dev)
+        trainer.step(batch[:, :-1], batch[:, 1:])
+        norms[fuse] = float(trainer.last_grad_norm)
+        fused_tensors[fuse] = getattr(trainer, 'fused_norm_tensors', 0)
+        plain = torch.sqrt(sum(p.grad.float().square().sum() for p in model.parameters() if p.grad is not None))
+        assert abs(norms[fuse] - float(plain)) <= 2e-3 * float(plain), (fuse, norms[fuse], float(plain))
+    assert fused_tensors[True] >= 2 * cfg.num_layers and fused_tensors[False] == 0
+    assert abs(norms[True] - norms[False]) <= 2e-3 * norms[False]
