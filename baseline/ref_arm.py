@@ -265,3 +265,24 @@ class RefTrainer:
     def step_from_host(self, batch):
         dev = batch.to(self.device, non_blocking=True)
         return float(self.step(dev[:, :-1], dev[:, 1:]).item())
+
+    def run_from_host(self, batches):
+        """The same training loop as the library arm's ``Trainer.run_from_host``: one step per pinned
+        host batch, every loss copied back to pinned memory and read after the next step is queued."""
+        losses, pending = [], None
+        ring = [torch.empty(1, dtype=torch.float32, pin_memory=True) for _ in range(2)]
+        events = [torch.cuda.Event() for _ in range(2)]
+        for i, batch in enumerate(batches):
+            dev = batch.to(self.device, non_blocking=True)
+            loss = self.step(dev[:, :-1], dev[:, 1:])
+            slot = i & 1
+            ring[slot].copy_(loss.detach().float().reshape(1), non_blocking=True)
+            events[slot].record()
+            if pending is not None:
+                events[pending].synchronize()
+                losses.append(float(ring[pending][0]))
+            pending = slot
+        if pending is not None:
+            events[pending].synchronize()
+            losses.append(float(ring[pending][0]))
+        return losses

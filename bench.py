@@ -17,9 +17,10 @@ RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment.
 Two numbers are measured back to back, both with CUDA events between a barrier +
 device synchronisation on each side and reduced with MAX over ranks:
 ``value`` with inputs already on the device and no host synchronisation inside the
-timed region, and ``e2e`` through ``Trainer.step_from_host`` where every step copies
-its token batch from pinned host memory and reads the loss back.  Rank 0 prints one
-JSON line.
+timed region, and ``e2e`` through ``Trainer.run_from_host`` (the training-loop call) where
+every step copies its token batch from pinned host memory and every step's loss is read
+back to the host (the loop waits for the loss of step k once step k + 1 is queued; all
+losses are on the host before the timed region ends).  Rank 0 prints one JSON line.
 """
 
 import argparse
@@ -154,9 +155,12 @@ def _measure(trainer, world, rank, local, steps, warmup, launch_counter, comm_ti
     barrier()
     start2, end2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start2.record()
-    last = None
-    for i in range(steps):
-        last = trainer.step_from_host(host_batches[i % len(host_batches)])
+    # The training-loop call of the public API: every step copies its batch from pinned host memory
+    # and every step's loss comes back to the host; the loop waits for the loss of step k after it
+    # has queued step k + 1.  All K losses are on the host before the region ends.
+    losses = trainer.run_from_host(host_batches[i % len(host_batches)] for i in range(steps))
+    assert len(losses) == steps
+    last = losses[-1]
     _flush(trainer)
     end2.record()
     barrier()

@@ -487,6 +487,40 @@ class Trainer:
         loss = self.step(dev[:, :-1], dev[:, 1:])
         return float(loss.item())
 
+    def run_from_host(self, batches) -> list:
+        """Train one step per pinned host batch (``[micro_batch, seq + 1]`` int64 each) and return
+        every step's loss as a Python float, in order.
+
+        Each step copies its own batch to the device and its loss is copied back to pinned host
+        memory; the host waits for the loss of step ``k`` only after it has queued step ``k + 1``,
+        so the device never idles while the host reads a number and prepares the next launch.
+        """
+        losses, pending = [], None
+        pinned = self.device.type == 'cuda'
+        if self._h2d is None:       # allocated once: pinning memory is slow and synchronises the device
+            self._h2d = ([torch.empty(1, dtype=torch.float32, pin_memory=pinned) for _ in range(2)],
+                         [torch.cuda.Event() for _ in range(2)] if pinned else [None, None])
+        ring, events = self._h2d
+
+        def collect(slot):
+            if events[slot] is not None:
+                events[slot].synchronize()
+            losses.append(float(ring[slot][0]))
+
+        for i, batch in enumerate(batches):
+            dev = batch.to(self.device, non_blocking=True)
+            loss = self.step(dev[:, :-1], dev[:, 1:])
+            slot = i & 1
+            ring[slot].copy_(loss.detach().float().reshape(1), non_blocking=True)
+            if events[slot] is not None:
+                events[slot].record()
+            if pending is not None:
+                collect(pending)
+            pending = slot
+        if pending is not None:
+            collect(pending)
+        return losses
+
     def state_dict(self):
         self.flush()
         state = {'model': self.model.state_dict(), 'dense_opt': self.dense_opt.state_dict(),

@@ -195,3 +195,17 @@ def test_pipeline_stage_checks_its_load_balancing_terms():
     with pytest.raises(ValueError, match='Expected 1 token_per_experts'):
         batched_load_balancing_loss(model.moe_args)
     clear_load_balancing_loss()
+
+
+def test_run_from_host_returns_every_loss_in_order():
+    """The pipelined host loop gives the same losses as one blocking call per step."""
+    torch.manual_seed(0)
+    cfg = preset('tiny', dtype=torch.float32)
+    base = MoETransformer(cfg)
+    batches = [torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(i)) for i in range(4)]
+    a = Trainer(copy.deepcopy(base), TrainerConfig(lr=1e-2, schedule=False))
+    b = Trainer(copy.deepcopy(base), TrainerConfig(lr=1e-2, schedule=False))
+    want = [a.step_from_host(x) for x in batches]
+    got = b.run_from_host(iter(batches))
+    assert len(got) == 4 and all(abs(p - q) < 1e-6 for p, q in zip(want, got))
+    assert b.run_from_host([]) == []
