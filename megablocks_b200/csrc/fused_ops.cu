@@ -510,39 +510,48 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, c
             // re-read per row, it stays in L1 and costs no registers between rows.
             const Pack<T, VEC> pv = *reinterpret_cast<const Pack<T, VEC>*>(res_bias + c);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k)
-              px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]) + to_float(pv.v[k]));
+            for (int k = 0; k < VEC / 2; ++k)
+              set_pack_pair(px[j], k, __fadd2_rn(__fadd2_rn(pack_pair(px[j], k), pack_pair(pr, k)), pack_pair(pv, k)));
           } else {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) px[j].v[k] = from_float<T>(to_float(px[j].v[k]) + to_float(pr.v[k]));
+            for (int k = 0; k < VEC / 2; ++k)
+              set_pack_pair(px[j], k, __fadd2_rn(pack_pair(px[j], k), pack_pair(pr, k)));
           }
           *reinterpret_cast<Pack<T, VEC>*>(sum_out + r * cols + c) = px[j];
         }
       }
     }
-    float s = 0.f, ss = 0.f;
+    // Statistics and normalisation on packed fp32 pairs (two elements per instruction).
+    float2 s2 = make_float2(0.f, 0.f), ss2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) { const float v = to_float(px[j].v[k]); s += v; ss += v * v; }
+        for (int k = 0; k < VEC / 2; ++k) {
+          const float2 v = pack_pair(px[j], k);
+          s2 = __fadd2_rn(s2, v);
+          ss2 = __ffma2_rn(v, v, ss2);
+        }
       }
     }
-    s = warp_sum(s);
-    ss = warp_sum(ss);
+    const float s = warp_sum(s2.x + s2.y);
+    const float ss = warp_sum(ss2.x + ss2.y);
     const float mean = rms ? 0.f : s * inv_cols;
     const float rstd = rsqrtf(fmaxf(ss * inv_cols - mean * mean, 0.f) + eps);
     if (lane == 0) { mean_out[r] = mean; rstd_out[r] = rstd; }
     T* yr = y + r * cols;
+    const float2 rs2 = make_float2(rstd, rstd), nm2 = make_float2(-mean * rstd, -mean * rstd);
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int c = (j * 32 + lane) * VEC;
       if (c < cols) {
         Pack<T, VEC> po;
 #pragma unroll
-        for (int k = 0; k < VEC; ++k)
-          po.v[k] = from_float<T>((to_float(px[j].v[k]) - mean) * rstd * to_float(pg[j].v[k]) + to_float(pb[j].v[k]));
+        for (int k = 0; k < VEC / 2; ++k) {
+          const float2 xh = __ffma2_rn(pack_pair(px[j], k), rs2, nm2);          // (x - mean) * rstd
+          set_pack_pair(po, k, __ffma2_rn(xh, pack_pair(pg[j], k), pack_pair(pb[j], k)));
+        }
         *reinterpret_cast<Pack<T, VEC>*>(yr + c) = po;
       }
     }
