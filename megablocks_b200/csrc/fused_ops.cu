@@ -644,11 +644,30 @@ colsum_partial_kernel(const T* __restrict__ x, int64_t rows, int cols, float* __
 
 template <typename T>
 __global__ void colsum_reduce_kernel(const float* __restrict__ partial, int slices, int cols, T* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  // 32 columns x 8 slice lanes per CTA, four loads in flight per thread (same order of additions on every run).
+  __shared__ float red[8][33];
+  const int col_lane = threadIdx.x & 31, part_lane = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + col_lane;
   float s = 0.f;
-  for (int p = 0; p < slices; ++p) s += partial[int64_t(p) * cols + c];
-  out[c] = from_float<T>(s);
+  if (c < cols) {
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int p = part_lane;
+    for (; p + 24 < slices; p += 32) {
+      s += partial[int64_t(p) * cols + c];
+      s1 += partial[int64_t(p + 8) * cols + c];
+      s2 += partial[int64_t(p + 16) * cols + c];
+      s3 += partial[int64_t(p + 24) * cols + c];
+    }
+    for (; p < slices; p += 8) s += partial[int64_t(p) * cols + c];
+    s += s1 + s2 + s3;
+  }
+  red[part_lane][col_lane] = s;
+  __syncthreads();
+  if (part_lane == 0 && c < cols) {
+#pragma unroll
+    for (int l = 1; l < 8; ++l) s += red[l][col_lane];
+    out[c] = from_float<T>(s);
+  }
 }
 
 template <typename T>
@@ -781,7 +800,7 @@ cudaError_t column_sum(DType type, const void* x, int64_t rows, int cols, void* 
     if (cols % kVec != 0) return cudaErrorInvalidValue;
     const dim3 grid(ceil_div(cols, 32 * kVec), slices);
     colsum_partial_kernel<T><<<grid, 32 * kColsumRowLanes, 0, stream>>>(static_cast<const T*>(x), rows, cols, partial);
-    colsum_reduce_kernel<T><<<ceil_div(cols, 256), 256, 0, stream>>>(partial, slices, cols, static_cast<T*>(out));
+    colsum_reduce_kernel<T><<<ceil_div(cols, 32), 256, 0, stream>>>(partial, slices, cols, static_cast<T*>(out));
   })
   return cudaGetLastError();
 }

@@ -167,8 +167,9 @@ combine_rows_kernel(const T* __restrict__ x, const int* __restrict__ inverse, co
   }
 }
 
-// wgrad[copy] = <x[row(copy)], grad[copy / top_k]>, one warp per copy.
-template <typename T>
+// wgrad[copy] = <x[row(copy)], grad[copy / top_k]>, one warp per copy.  VEC > 1: both rows are read
+// in 16-byte pieces (rows of a multiple of 16 bytes at 16-byte aligned bases).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 wgrad_kernel(const T* __restrict__ x, const T* __restrict__ grad, const int* __restrict__ inverse, int top_k,
              int64_t copies, int cols, T* __restrict__ wgrad) {
@@ -180,7 +181,20 @@ wgrad_kernel(const T* __restrict__ x, const T* __restrict__ grad, const int* __r
   if (row >= 0) {
     const T* a = x + int64_t(row) * cols;
     const T* b = grad + (copy / top_k) * cols;
-    for (int c = lane; c < cols; c += 32) acc += to_float(a[c]) * to_float(b[c]);
+    if constexpr (VEC > 1) {
+      float acc2 = 0.f;
+      for (int c = lane * VEC; c < cols; c += 32 * VEC) {
+        const Pack<T, VEC> pa = load_pack<T, VEC>(a + c), pb = load_pack<T, VEC>(b + c);
+#pragma unroll
+        for (int k = 0; k < VEC; k += 2) {
+          acc = fmaf(to_float(pa.v[k]), to_float(pb.v[k]), acc);
+          acc2 = fmaf(to_float(pa.v[k + 1]), to_float(pb.v[k + 1]), acc2);
+        }
+      }
+      acc += acc2;
+    } else {
+      for (int c = lane; c < cols; c += 32) acc += to_float(a[c]) * to_float(b[c]);
+    }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
@@ -243,9 +257,16 @@ cudaError_t combine_rows(DType type, const void* x, const int* inverse, const vo
 cudaError_t scatter_wgrad(DType type, const void* x, const void* grad, const int* inverse, int top_k,
                           int64_t copies, int cols, void* wgrad, cudaStream_t stream) {
   MB_SWITCH_FLOAT(type, T, {
-    wgrad_kernel<T><<<ceil_div(copies, kWarpsPerCta), kWarpsPerCta * 32, 0, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(grad), inverse, top_k, copies, cols,
-        static_cast<T*>(wgrad));
+    constexpr int kFull = 16 / sizeof(T);
+    if (vec_width<T>(cols, x, grad) > 1) {
+      wgrad_kernel<T, kFull><<<ceil_div(copies, kWarpsPerCta), kWarpsPerCta * 32, 0, stream>>>(
+          static_cast<const T*>(x), static_cast<const T*>(grad), inverse, top_k, copies, cols,
+          static_cast<T*>(wgrad));
+    } else {
+      wgrad_kernel<T, 1><<<ceil_div(copies, kWarpsPerCta), kWarpsPerCta * 32, 0, stream>>>(
+          static_cast<const T*>(x), static_cast<const T*>(grad), inverse, top_k, copies, cols,
+          static_cast<T*>(wgrad));
+    }
   })
   return cudaGetLastError();
 }
