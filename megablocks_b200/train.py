@@ -342,6 +342,11 @@ class Trainer:
                     user.released_seq = released
         launches = ext().launch_count() - before
         self._graph = (graph, static_tokens, static_targets, loss, launches)
+        if self.world > 1:
+            # Recording takes a different time on every rank; the first replay's bounded device waits
+            # should not have to absorb that difference.
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.dp_group)
 
     def _graph_replay(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         from megablocks_b200._ext import ext
