@@ -342,11 +342,6 @@ class Trainer:
                     user.released_seq = released
         launches = ext().launch_count() - before
         self._graph = (graph, static_tokens, static_targets, loss, launches)
-        if self.world > 1:
-            # Recording takes a different time on every rank; the first replay's bounded device waits
-            # should not have to absorb that difference.
-            torch.cuda.synchronize(self.device)
-            dist.barrier(self.dp_group)
 
     def _graph_replay(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         from megablocks_b200._ext import ext
@@ -389,11 +384,20 @@ class Trainer:
                 if static_tokens.shape != tokens.shape:
                     self.drop_graph()
             if self._graph is None and self._eager_steps >= self.cfg.graph_warmup_steps:
+                failed = None
                 try:
                     self._capture(tokens, targets)
                 except RuntimeError as err:      # something in the step cannot be recorded: stay kernel by kernel
+                    failed = err
+                if self.world > 1:
+                    # Recording takes a different time on every rank (and may fail on one only): the
+                    # ranks meet here, so that the bounded device waits of the step that follows do
+                    # not have to absorb the difference.
+                    torch.cuda.synchronize(self.device)
+                    dist.barrier(self.dp_group)
+                if failed is not None:
                     import warnings
-                    warnings.warn(f'CUDA-graph capture of the training step failed, continuing without: {err}')
+                    warnings.warn(f'CUDA-graph capture of the training step failed, continuing without: {failed}')
                     self.drop_graph()
                     self.cfg = dataclasses.replace(self.cfg, cuda_graph=False)
                     self._zero_grad()
