@@ -209,3 +209,32 @@ def test_run_from_host_returns_every_loss_in_order():
     got = b.run_from_host(iter(batches))
     assert len(got) == 4 and all(abs(p - q) < 1e-6 for p, q in zip(want, got))
     assert b.run_from_host([]) == []
+
+
+def test_fused_adam_norm_can_leave_tensors_out():
+    """``add_sqnorm(skip=...)``: tensors whose norm is known from elsewhere are not summed again."""
+    from megablocks_b200.optim import FusedAdam
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(5, 3)), torch.nn.Parameter(torch.randn(7)), torch.nn.Parameter(torch.randn(2, 2))]
+    for p in params:
+        p.grad = torch.randn_like(p)
+    opt = FusedAdam(params, lr=1e-3)
+    full, part = torch.zeros(1), torch.zeros(1)
+    opt.add_sqnorm(full)
+    opt.add_sqnorm(part, skip=[False, True, False])
+    want_full = sum(float(p.grad.square().sum()) for p in params)
+    want_part = want_full - float(params[1].grad.square().sum())
+    assert abs(float(full) - want_full) < 1e-4 and abs(float(part) - want_part) < 1e-4
+
+
+def test_grad_norm_sink_lookup_is_by_address_and_size():
+    from megablocks_b200.ops.gg import GradNormSink
+    sink = GradNormSink(torch.device('cpu'), slots=4)
+    sink.begin()
+    a, b = torch.zeros(6), torch.zeros(6)
+    slot, view = sink._next()
+    assert slot == 0 and view.numel() == 1
+    sink._record(a, slot)
+    assert sink.lookup(a) == 0 and sink.lookup(b) is None and sink.lookup(a[:3]) is None
+    sink.begin()
+    assert sink.lookup(a) is None and float(sink.slots.sum()) == 0.0
