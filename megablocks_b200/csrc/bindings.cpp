@@ -92,6 +92,7 @@ void ep_wait_flags_op(const at::Tensor& flags, int64_t count, int64_t seq, int64
 
 // torch_glue.cpp: fused row-wise ops
 std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at::Tensor& targets);
+at::Tensor cross_entropy_fused_(at::Tensor logits, const at::Tensor& targets, double scale);
 void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
                              const c10::optional<at::Tensor>& scale, double scale_mul);
 std::vector<at::Tensor> layernorm_forward(const at::Tensor& x, const at::Tensor& gamma,
@@ -146,6 +147,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "Per-CTA cycle counters of the grouped GEMM roles (builds with -DMB_GEMM_TIMING)");
   m.def("cross_entropy_forward", &mb::cross_entropy_forward);
   m.def("cross_entropy_backward_", &mb::cross_entropy_backward_);
+  m.def("cross_entropy_fused_", &mb::cross_entropy_fused_,
+        "Per-row loss; the logits are overwritten with (softmax - onehot) * scale in the same launch");
   m.def("layernorm_forward", &mb::layernorm_forward);
   m.def("layernorm_backward", &mb::layernorm_backward);
   m.def("layernorm_can_fuse", &mb::layernorm_can_fuse);

@@ -111,6 +111,77 @@ cross_entropy_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict__ tar
   }
 }
 
+// Loss and gradient in one launch: the row's log-sum-exp as in the forward kernel, then
+// (exp(x - lse) - [j == target]) * scale written over the row.  The second pass reads the row a few
+// microseconds after the first, from L2 (a row is 100 KB, a few hundred CTAs are in flight), so the
+// logits cross the HBM bus once in each direction instead of twice in and once out.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_fused_kernel(T* __restrict__ logits, const int64_t* __restrict__ targets, int64_t vocab, float scale,
+                           float* __restrict__ loss_out) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float red_m[kCeThreads / 32], red_s[kCeThreads / 32];
+  __shared__ float lse_s;
+  T* row = logits + int64_t(blockIdx.x) * vocab;
+  const int64_t tgt = targets[blockIdx.x];
+  const bool valid = tgt >= 0 && tgt < vocab;
+  float m = -INFINITY, s = 0.f;
+  const bool vec_ok = (vocab % VEC == 0) && (reinterpret_cast<uintptr_t>(row) % 16 == 0);
+  if (vec_ok) {
+    for (int64_t i = int64_t(threadIdx.x) * VEC; i < vocab; i += kCeThreads * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(row + i);
+      float v[VEC], pm = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) { v[k] = to_float(p.v[k]); pm = fmaxf(pm, v[k]); }
+      if (pm > m) { s *= __expf(m - pm); m = pm; }
+      if (m != -INFINITY) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) s += __expf(v[k] - m);
+      }
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < vocab; i += kCeThreads) {
+      const float x = to_float(row[i]);
+      if (x > m) { s = s * __expf(m - x) + 1.f; m = x; } else { s += __expf(x - m); }
+    }
+  }
+  const float wm = warp_max(m);
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+  if ((threadIdx.x & 31) == 0) { red_m[threadIdx.x >> 5] = wm; red_s[threadIdx.x >> 5] = s; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float mm = threadIdx.x < kCeThreads / 32 ? red_m[threadIdx.x] : -INFINITY;
+    float ss = threadIdx.x < kCeThreads / 32 ? red_s[threadIdx.x] : 0.f;
+    const float bm = warp_max(mm);
+    ss = warp_sum(mm == -INFINITY ? 0.f : ss * __expf(mm - bm));
+    if (threadIdx.x == 0) {
+      const float lse = bm + __logf(ss);
+      lse_s = lse;
+      loss_out[blockIdx.x] = valid ? lse - to_float(row[tgt]) : 0.f;    // read before the row is overwritten
+    }
+  }
+  __syncthreads();
+  const float l = lse_s;
+  if (vec_ok) {
+    for (int64_t i = int64_t(threadIdx.x) * VEC; i < vocab; i += kCeThreads * VEC) {
+      Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(row + i);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float g = valid ? __expf(to_float(p.v[k]) - l) : 0.f;
+        if (i + k == tgt) g -= 1.f;
+        p.v[k] = from_float<T>(g * scale);
+      }
+      *reinterpret_cast<Pack<T, VEC>*>(row + i) = p;
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < vocab; i += kCeThreads) {
+      float g = valid ? __expf(to_float(row[i]) - l) : 0.f;
+      if (i == tgt) g -= 1.f;
+      row[i] = from_float<T>(g * scale);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // LayerNorm: one warp per row, rows strided over a persistent grid.
 // ---------------------------------------------------------------------------
@@ -727,6 +798,16 @@ cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, 
   MB_SWITCH_FLOAT(type, T, {
     cross_entropy_bwd_kernel<T><<<static_cast<unsigned>(rows), kCeThreads, 0, stream>>>(
         static_cast<T*>(logits), targets, lse, scale_ptr, scale_mul, vocab);
+  })
+  return cudaGetLastError();
+}
+
+cudaError_t cross_entropy_fused(DType type, void* logits, const int64_t* targets, float scale, int64_t rows,
+                                int64_t vocab, float* loss, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  MB_SWITCH_FLOAT(type, T, {
+    cross_entropy_fused_kernel<T><<<static_cast<unsigned>(rows), kCeThreads, 0, stream>>>(
+        static_cast<T*>(logits), targets, vocab, scale, loss);
   })
   return cudaGetLastError();
 }

@@ -83,6 +83,9 @@ cudaError_t clip_coeff(const float* sqnorm, float max_norm, float extra_scale, f
 cudaError_t cross_entropy_fwd(DType type, const void* logits, const int64_t* targets, int64_t rows, int64_t vocab,
                               float* lse, float* loss, cudaStream_t stream);
 // Overwrites `logits` with (softmax - onehot) * scale_ptr[0] * scale_mul.
+// Loss per row into `loss`, and (softmax - onehot) * scale written over `logits`, in one launch.
+cudaError_t cross_entropy_fused(DType type, void* logits, const int64_t* targets, float scale, int64_t rows,
+                                int64_t vocab, float* loss, cudaStream_t stream);
 cudaError_t cross_entropy_bwd(DType type, void* logits, const int64_t* targets, const float* lse,
                               const float* scale_ptr, float scale_mul, int64_t rows, int64_t vocab,
                               cudaStream_t stream);

@@ -894,6 +894,20 @@ std::vector<at::Tensor> cross_entropy_forward(const at::Tensor& logits, const at
 }
 
 // Overwrites `logits` with its gradient: (softmax - onehot) * scale[0] * scale_mul.
+// Per-row loss; `logits` is overwritten with the gradient of `scale * sum(loss)` with respect to it.
+at::Tensor cross_entropy_fused_(at::Tensor logits, const at::Tensor& targets, double scale) {
+  MB_CHECK_CUDA(logits); MB_CHECK_CONTIG(logits); MB_CHECK_CUDA(targets); MB_CHECK_CONTIG(targets);
+  TORCH_CHECK(logits.dim() == 2 && targets.dim() == 1 && targets.size(0) == logits.size(0) &&
+                  targets.scalar_type() == at::kLong,
+              "cross_entropy expects logits[rows, vocab] and int64 targets[rows]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  at::Tensor loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  MB_CUDA_OK(cross_entropy_fused(float_code(logits.scalar_type()), logits.data_ptr(), targets.data_ptr<int64_t>(),
+                                 float(scale), logits.size(0), logits.size(1), loss.data_ptr<float>(), stream()));
+  MB_LAUNCHED(1);
+  return loss;
+}
+
 void cross_entropy_backward_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse,
                              const c10::optional<at::Tensor>& scale, double scale_mul) {
   MB_CHECK_CUDA(logits); MB_CHECK_CONTIG(logits);

@@ -289,8 +289,12 @@ class MoETransformer(nn.Module):
 
     def stage_loss(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Last stage: final norm, LM head and cross entropy."""
-        logits = self.logits(self.ln_f(hidden))
-        return fused.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
+        return self._lm_loss(self.ln_f(hidden), targets)
+
+    def _lm_loss(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Language-model head and mean cross entropy (the logits are written once and read once)."""
+        weight = self.lm_head.weight if self.lm_head is not None else self.wte.weight
+        return fused.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), weight, targets.reshape(-1))
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         weight = self.lm_head.weight if self.lm_head is not None else self.wte.weight
@@ -306,9 +310,7 @@ class MoETransformer(nn.Module):
         """
         if self.cfg.pipeline_stages > 1:
             raise RuntimeError('a pipeline stage is driven through stage_forward / stage_loss')
-        hidden = self.hidden_states(tokens)
-        logits = self.logits(hidden)
-        lm = fused.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
+        lm = self._lm_loss(self.hidden_states(tokens), targets)
         aux = self._aux_loss()
         total = lm if aux is None else lm + aux
         return total, lm.detach()

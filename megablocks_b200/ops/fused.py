@@ -22,6 +22,7 @@
 All fall back to the PyTorch ops on CPU tensors.
 """
 
+import os
 from typing import Any
 
 import torch
@@ -44,6 +45,40 @@ class _CrossEntropy(torch.autograd.Function):
         scale = grad_out.detach().float().reshape(1)
         ext().cross_entropy_backward_(logits, targets, lse, scale, 1.0 / logits.shape[0])
         return logits, None
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    """``mean(cross_entropy(hidden @ weight^T, targets))`` with the loss and the gradient of the logits
+    taken in ONE pass over the logits (they are overwritten with ``(softmax - onehot) / rows``).  The
+    incoming gradient, a scalar, is then applied to the two small products of the backward pass
+    instead of to the logits."""
+
+    @staticmethod
+    def forward(ctx: Any, hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor):
+        logits = hidden @ weight.t()
+        loss = ext().cross_entropy_fused_(logits, targets, 1.0 / logits.shape[0])
+        ctx.save_for_backward(hidden, weight, logits)
+        return loss.mean()
+
+    @staticmethod
+    def backward(ctx: Any, grad_out: torch.Tensor):
+        hidden, weight, dlogits = ctx.saved_tensors
+        scale = grad_out.detach().to(hidden.dtype)
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            dh = (dlogits @ weight).mul_(scale)
+        if ctx.needs_input_grad[1]:
+            dw = (dlogits.t() @ hidden).mul_(scale)
+        return dh, dw, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Mean cross entropy of ``hidden[rows, h] @ weight[vocab, h]^T`` against ``targets[rows]``: the
+    language-model head and its loss.  On CUDA the logits are written once and read once."""
+    if (hidden.is_cuda and hidden.dtype in (torch.bfloat16, torch.float16, torch.float32) and hidden.dim() == 2
+            and weight.dtype == hidden.dtype and os.environ.get('MB200_FUSED_LM_LOSS', '1') != '0'):
+        return _LinearCrossEntropy.apply(hidden.contiguous(), weight, targets.contiguous())
+    return cross_entropy(F.linear(hidden, weight), targets)
 
 
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

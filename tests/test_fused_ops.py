@@ -234,3 +234,29 @@ def test_batched_load_balancing_loss(device, layers, tokens, experts, top_k, dty
     torch.testing.assert_close(loss.detach().float().cpu(), ref.detach(), rtol=1e-3, atol=1e-6)
     for s, r in zip(scores, ref_scores):
         torch.testing.assert_close(s.grad.float().cpu(), r.grad, rtol=1e-2, atol=1e-9)
+
+
+@pytest.mark.parametrize('device', DEVICES)
+@pytest.mark.parametrize('rows,hidden,vocab', [(64, 32, 1000), (300, 64, 5003), (1024, 128, 51200)])
+def test_linear_cross_entropy_matches_the_unfused_head_and_loss(device, rows, hidden, vocab):
+    """LM head + mean cross entropy with loss and logit gradient in one pass, against F.linear +
+    F.cross_entropy in fp32: loss, both gradients, an upstream gradient other than one, ignored rows."""
+    if device == 'cpu' and vocab > 10000:
+        pytest.skip('large vocabulary on the GPU only')
+    dtype = torch.bfloat16 if device == 'cuda' else torch.float32
+    h = (torch.randn(rows, hidden) * 0.5).to(dtype).to(device).requires_grad_(True)
+    w = (torch.randn(vocab, hidden) * 0.2).to(dtype).to(device).requires_grad_(True)
+    t = torch.randint(0, vocab, (rows,)).to(device)
+    loss = fused.linear_cross_entropy(h, w, t)
+    (loss * 3.0).backward()
+    hr, wr = h.detach().float().cpu().requires_grad_(True), w.detach().float().cpu().requires_grad_(True)
+    logits = F.linear(hr, wr)
+    if dtype == torch.bfloat16:      # the fused path sees the logits rounded to bf16
+        logits = logits + (logits.to(dtype).float() - logits).detach()
+    ref = F.cross_entropy(logits, t.cpu())
+    (ref * 3.0).backward()
+    tol = dict(rtol=2e-2, atol=2e-3) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(loss.detach().float().cpu(), ref.detach(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(h.grad.float().cpu(), hr.grad, **tol)
+    wtol = dict(rtol=3e-2, atol=3e-2 * float(wr.grad.abs().max())) if dtype == torch.bfloat16 else tol
+    torch.testing.assert_close(w.grad.float().cpu(), wr.grad, **wtol)
