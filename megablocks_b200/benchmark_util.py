@@ -35,6 +35,14 @@ def benchmark_function(fn, iterations=100, warmup=10, flush_l2=False):
     for _ in range(warmup):
         fn()
     times = []
+    if not torch.cuda.is_available():       # host-only runs (smoke tests of the benchmark scripts): wall clock
+        import time
+        for _ in range(iterations):
+            t0 = time.perf_counter()
+            fn()
+            times.append((time.perf_counter() - t0) * 1e3)
+        times = np.array(times)
+        return times.mean(), times.std()
     for _ in range(iterations):
         if flush_l2:
             _flush_l2()

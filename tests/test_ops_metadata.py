@@ -141,3 +141,15 @@ def test_repeat_and_sum(device):
     assert ops.repeat(x, (2, 1)).shape == (4, 3)
     assert ops.sum(x.view(1, 2, 3), dim=0).shape == (2, 3)
     assert torch.equal(ops.sum(x, dim=0), x.sum(0))
+
+
+def test_micro_benchmark_scripts_run_on_the_host():
+    """The sort / histogram / padded-scatter benchmark entry points (the reference ships one file each)."""
+    from megablocks_b200.benchmarks import histogram_benchmark, padded_scatter_benchmark, sort_benchmark
+    cpu = torch.device('cpu')
+    rows = sort_benchmark.run(cpu, iters=1)
+    assert len(rows) == len(sort_benchmark.SORT_CASES) and all(r['ops.sort_us'] > 0 for r in rows)
+    rows = histogram_benchmark.run(cpu, iters=1)
+    assert [r['bins'] for r in rows] == [2, 4, 8, 16, 32, 64, 128, 256]
+    rows = padded_scatter_benchmark.run(cpu, iters=1, cases=((512, 64, 8, 4), (2048, 64, 8, 1)))
+    assert len(rows) == 2 and all(r['forward_us'] > 0 and r['backward_us'] > 0 for r in rows)
