@@ -63,7 +63,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx: Any, grad_out: torch.Tensor):
         hidden, weight, dlogits = ctx.saved_tensors
-        scale = grad_out.detach().to(hidden.dtype)
+        scale = grad_out.detach().float()       # a 0-dim fp32 tensor: multiplies in fp32, result in the tensor's type
         dh = dw = None
         if ctx.needs_input_grad[0]:
             dh = (dlogits @ weight).mul_(scale)
@@ -75,7 +75,9 @@ class _LinearCrossEntropy(torch.autograd.Function):
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Mean cross entropy of ``hidden[rows, h] @ weight[vocab, h]^T`` against ``targets[rows]``: the
     language-model head and its loss.  On CUDA the logits are written once and read once."""
-    if (hidden.is_cuda and hidden.dtype in (torch.bfloat16, torch.float16, torch.float32) and hidden.dim() == 2
+    # Not for fp16: there the loss scale has to reach the logit gradient before it is rounded (the
+    # unscaled (softmax - onehot) / rows underflows), and the scale is only known in backward.
+    if (hidden.is_cuda and hidden.dtype in (torch.bfloat16, torch.float32) and hidden.dim() == 2
             and weight.dtype == hidden.dtype and os.environ.get('MB200_FUSED_LM_LOSS', '1') != '0'):
         return _LinearCrossEntropy.apply(hidden.contiguous(), weight, targets.contiguous())
     return cross_entropy(F.linear(hidden, weight), targets)
