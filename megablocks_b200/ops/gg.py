@@ -24,7 +24,7 @@ CPU they run per-group ``torch.matmul`` in fp32, which is also the oracle.
 
 import os
 from functools import partial
-from typing import Any, Callable, Optional, Tuple
+from typing import Any, Callable, Optional
 
 import torch
 import torch.nn.functional as F

@@ -16,7 +16,6 @@ from typing import Iterable, List, Optional, Sequence
 
 import numpy as np
 import torch
-import torch.distributed as dist
 
 from megablocks_b200._ext import ext
 
