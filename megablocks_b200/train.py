@@ -641,6 +641,9 @@ def main(argv=None):
     ap.add_argument('--ep-comm', choices=['auto', 'fused', 'nccl'], default='auto')
     ap.add_argument('--dp-comm', choices=['auto', 'peer', 'nccl'], default='auto',
                     help='gradient reduction of the replicated parameters: own peer-memory kernel or NCCL')
+    ap.add_argument('--cuda-graph', dest='cuda_graph', action='store_true',
+                    help='record the whole step in one CUDA graph after three ordinary steps and replay it '
+                         '(bf16 / fp32, fused Adam, no pipeline stages, no ZeRO-1, peer-memory gradient reducer)')
     ap.add_argument('--log', type=str, default=None, help='JSONL metrics file')
     ap.add_argument('--log-interval', type=int, default=10)
     ap.add_argument('--save', type=str, default=None, help='checkpoint directory')
@@ -706,7 +709,8 @@ def main(argv=None):
         stage = PipelineStage(pp_group, (args.micro_batch, cfg.max_seq_len, cfg.hidden_size), cfg.dtype, device)
     trainer = Trainer(model, TrainerConfig(lr=args.lr, min_lr=args.min_lr, total_steps=args.steps, zero1=args.zero1,
                                            overlap_expert_update=args.defer_expert_update, dp_backend=args.dp_comm,
-                                           grad_accum_steps=accum, optimizer=args.optimizer),
+                                           grad_accum_steps=accum, optimizer=args.optimizer,
+                                           cuda_graph=args.cuda_graph),
                       dp_group=group, pipeline=stage)
     if args.load:
         state = checkpoint.load(args.load, rank, world, map_location=device)
