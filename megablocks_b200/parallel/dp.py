@@ -228,6 +228,13 @@ class GradReducer:
                 dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group)
                 grad.div_(self.world)
 
+    def reset(self) -> None:
+        """Forget a step that was abandoned half way (no bucket counts as launched, none as pending)."""
+        self._works.clear()
+        self._remaining = list(self._pending)
+        self._launched = [False] * len(self.buckets)
+        self.active = True
+
     def finish(self) -> None:
         """Launch whatever backward did not trigger, then make the current stream wait for all buckets."""
         for bi in range(len(self.buckets)):

@@ -400,6 +400,14 @@ class Trainer:
                     warnings.warn(f'CUDA-graph capture of the training step failed, continuing without: {failed}')
                     self.drop_graph()
                     self.cfg = dataclasses.replace(self.cfg, cuda_graph=False)
+                    # The abandoned recording may have stopped anywhere: bring the per-step host state
+                    # back to "no step in progress".
+                    if self.reducer is not None:
+                        self.reducer.reset()
+                    from megablocks_b200.layers.moe import clear_load_balancing_loss
+                    from megablocks_b200.layers.router import clear_router_zloss
+                    clear_load_balancing_loss()
+                    clear_router_zloss()
                     self._zero_grad()
                     return self._step_eager(tokens, targets)
             if self._graph is not None:
