@@ -4,6 +4,7 @@ Adafactor, and a two-stage pipeline (gloo ranks) that must reproduce the single-
 
 import copy
 import os
+import sys
 import socket
 
 import pytest
@@ -238,3 +239,27 @@ def test_grad_norm_sink_lookup_is_by_address_and_size():
     assert sink.lookup(a) == 0 and sink.lookup(b) is None and sink.lookup(a[:3]) is None
     sink.begin()
     assert sink.lookup(a) is None and float(sink.slots.sum()) == 0.0
+
+
+def test_experiment_scripts_are_valid_shell_and_use_known_flags_and_presets():
+    """Every script under exp/ parses as bash, names an existing preset and passes only flags the trainer's
+    command line knows."""
+    import glob
+    import re
+    import subprocess
+    from megablocks_b200.models.transformer import PRESETS
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    scripts = sorted(glob.glob(os.path.join(root, 'exp', '*', '*.sh')))
+    assert len(scripts) == 17
+    help_text = subprocess.run([sys.executable, '-m', 'megablocks_b200.train', '--help'], capture_output=True, text=True,
+                               cwd=root, check=True).stdout
+    known = set(re.findall(r'(--[a-z][a-z0-9-]*)', help_text))
+    launcher = {'--nnodes', '--nproc-per-node', '--master-addr', '--master-port'}
+    for path in scripts:
+        assert subprocess.run(['bash', '-n', path]).returncode == 0, path
+        text = open(path).read()
+        command = text[text.index('python -m torch.distributed.run'):]
+        preset = re.search(r'--preset (\S+)', command).group(1)
+        assert preset in PRESETS, (path, preset)
+        for flag in set(re.findall(r'(--[a-z][a-z0-9-]*)', command)) - launcher:
+            assert flag in known, (path, flag)
